@@ -1,0 +1,274 @@
+"""Each CUDA kernel alone beside its plain PyTorch statement (tests/torch_ops.py), at sizes other
+than the engine's: odd widths, head sizes in steps of 16, every page size, windows, groups."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import torch_ops as ref
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+def close(a, b, dtype, scale=1.0):
+    t = tol(dtype)
+    torch.testing.assert_close(a.double(), b.double(), rtol=t["rtol"], atol=t["atol"] * scale)
+
+
+def rnd(*shape, dtype, seed=0, std=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype).to(dev())
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tinyinfer_b200 import ops
+    return ops
+
+
+def test_extension_is_loaded_and_cpu_is_refused(ops):
+    from tinyinfer_b200.ops import library
+    x = torch.ones(4, 8)
+    with pytest.raises(ops.KernelError):
+        ops.rmsnorm(x, torch.ones(8), 1e-6)
+    ops.add(rnd(3, dtype=torch.float32), rnd(3, dtype=torch.float32))
+    assert "core" in library.loaded_libraries() and ops.launch_count() > 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("t,h,v", [(1, 64, 256), (7, 100, 389), (33, 4096, 1000), (5, 5120, 77)])
+def test_embedding(ops, dtype, t, h, v):
+    table = rnd(v, h, dtype=dtype)
+    ids = torch.randint(0, v, (t,), dtype=torch.int32, device=dev())
+    assert torch.equal(ops.embedding(ids, table), ref.embedding(ids, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,size,eps", [(1, 16, 1e-6), (9, 96, 1e-5), (5, 100, 1e-6), (3, 4096, 1e-6),
+                                           (2, 5120, 1e-5), (300, 128, 1e-6)])
+def test_rmsnorm(ops, dtype, rows, size, eps):
+    x = rnd(rows, size, dtype=dtype, std=3.0)
+    w = 1.0 + 0.1 * rnd(size, dtype=torch.float32, seed=1)
+    close(ops.rmsnorm(x, w, eps), ref.rmsnorm(x, w, eps), dtype)
+    pick = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32, device=dev())
+    close(ops.rmsnorm(x, w, eps, rows=pick), ref.rmsnorm(x, w, eps, rows=pick), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add(ops, dtype):
+    a, b = rnd(37, 100, dtype=dtype), rnd(37, 100, dtype=dtype, seed=1)
+    assert torch.equal(ops.add(a, b), ref.add(a, b))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (5, 100, 96), (64, 64, 16), (65, 130, 50), (130, 389, 320),
+                                   (2, 1000, 4096), (300, 96, 176)])
+def test_linear(ops, dtype, m, n, k):
+    x, w = rnd(m, k, dtype=dtype), rnd(n, k, dtype=dtype, seed=1, std=k ** -0.5)
+    bias = rnd(n, dtype=torch.float32, seed=2)
+    res = rnd(m, n, dtype=dtype, seed=3)
+    close(ops.linear(x, w), ref.linear(x, w), dtype)
+    close(ops.linear(x, w, bias=bias, residual=res), ref.linear(x, w, bias=bias, residual=res), dtype)
+    out32 = ops.linear(x, w, out_float32=True)
+    assert out32.dtype == torch.float32
+    close(out32, ref.linear(x, w, out_float32=True), torch.float32, scale=10.0 if dtype == torch.bfloat16 else 1.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,inter,k", [(1, 128, 64), (7, 176, 96), (70, 448, 320), (33, 100, 50)])
+def test_gated_linear(ops, dtype, m, inter, k):
+    x, w = rnd(m, k, dtype=dtype), rnd(2 * inter, k, dtype=dtype, seed=1, std=k ** -0.5)
+    close(ops.gated_linear(x, w), ref.gated_linear(x, w), dtype)
+
+
+def linear_rows_do_not_depend_on_the_batch(ops, dtype):
+    x, w = rnd(130, 96, dtype=dtype), rnd(100, 96, dtype=dtype, seed=1)
+    whole = ops.linear(x, w)
+    assert torch.equal(whole[77:78], ops.linear(x[77:78].contiguous(), w))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_rows_do_not_depend_on_the_batch(ops, dtype):
+    linear_rows_do_not_depend_on_the_batch(ops, dtype)
+
+
+def paged_setup(dtype, lens, hq, hkv, d, page, seed=0, extra_pages=3):
+    """Random q/k/v for requests of the given lengths, laid into scattered pages."""
+    g = torch.Generator().manual_seed(seed)
+    total_pages = sum((n + page - 1) // page for n in lens) + extra_pages
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    tables, nxt = [], 0
+    for n in lens:
+        nb = (n + page - 1) // page
+        tables.append(perm[nxt:nxt + nb])
+        nxt += nb
+    width = max(len(t) for t in tables)
+    bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32, device=dev())
+    kv = torch.full((2, total_pages, hkv, page, d), float("nan"), dtype=dtype, device=dev())
+    return bt, kv
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page,rot,norm", [
+    (4, 2, 16, 4, 16, True), (6, 2, 32, 8, 32, True), (8, 2, 64, 16, 64, True), (4, 1, 128, 64, 128, True),
+    (3, 3, 48, 5, 24, False), (2, 1, 256, 32, 256, True), (5, 5, 80, 16, 0, True)])
+def test_qk_norm_rope_append(ops, dtype, hq, hkv, d, page, rot, norm):
+    lens = [9, 1, 23]
+    starts = [3, 0, 40]                       # tokens already held: this step appends lens[i] more
+    bt, kv = paged_setup(dtype, [s + n for s, n in zip(starts, lens)], hq, hkv, d, page)
+    t = sum(lens)
+    qkv = rnd(t, (hq + 2 * hkv) * d, dtype=dtype, std=2.0)
+    pos = torch.tensor([p for s, n in zip(starts, lens) for p in range(s, s + n)], dtype=torch.int32, device=dev())
+    seq = torch.tensor([i for i, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=dev())
+    qw = (1 + 0.1 * rnd(d, dtype=torch.float32, seed=5)) if norm else None
+    kw = (1 + 0.1 * rnd(d, dtype=torch.float32, seed=6)) if norm else None
+    inv = None
+    if rot:
+        inv = (1.0 / (1e6 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(dev())
+    kv_ref = kv.clone()
+    args = dict(num_heads=hq, num_kv_heads=hkv, head_dim=d, q_norm_weight=qw, k_norm_weight=kw, eps=1e-6,
+                inv_freq=inv, rotary_dim=rot, positions=pos, token_seq=seq, block_table=bt)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    q = ops.qk_norm_rope_append(qkv, kv_cache=kv, status=status, **args)
+    q_ref = ref.qk_norm_rope_append(qkv, kv_cache=kv_ref, **args)
+    assert int(status.item()) == 0
+    close(q, q_ref, dtype, scale=4.0)
+    written = ~torch.isnan(kv_ref.float())
+    assert torch.equal(written, ~torch.isnan(kv.float())), "wrote to other slots than the reference"
+    close(kv[written], kv_ref[written], dtype, scale=4.0)
+    # an entry that only reads the cache gets q and leaves the pages alone
+    kv2 = kv.clone()
+    q2 = ops.qk_norm_rope_append(qkv, kv_cache=None, **args)
+    assert torch.equal(q2, q) and torch.equal(torch.nan_to_num(kv2.float()), torch.nan_to_num(kv.float()))
+
+
+def fill_cache(kv, bt, lens, hkv, d, page, dtype, seed=0):
+    """Writes random keys and values for positions 0..len-1 of every request; returns them."""
+    ks, vs = [], []
+    for i, n in enumerate(lens):
+        k = rnd(n, hkv, d, dtype=dtype, seed=seed + 10 * i)
+        v = rnd(n, hkv, d, dtype=dtype, seed=seed + 10 * i + 1)
+        for p in range(n):
+            pg = int(bt[i, p // page])
+            kv[0, pg, :, p % page] = k[p]
+            kv[1, pg, :, p % page] = v[p]
+        ks.append(k)
+        vs.append(v)
+    return ks, vs
+
+
+ATTN_SHAPES = [
+    # hq, hkv, d, page, window, [(context, q_len)]
+    (4, 2, 16, 4, None, [(9, 9), (37, 1), (20, 5)]),
+    (6, 2, 32, 8, 11, [(50, 50), (33, 1), (64, 7)]),
+    (8, 2, 64, 16, None, [(130, 130), (129, 1), (200, 2)]),
+    (4, 1, 128, 64, 40, [(300, 44), (65, 1), (64, 1), (1, 1)]),
+    (3, 3, 48, 5, None, [(17, 17), (31, 1)]),
+    (2, 1, 256, 32, None, [(70, 3), (33, 1)]),
+    (32, 8, 128, 64, None, [(257, 257), (512, 1), (511, 1)]),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page,window,work", ATTN_SHAPES)
+def test_paged_attention(ops, dtype, hq, hkv, d, page, window, work):
+    lens = [c for c, _ in work]
+    bt, kv = paged_setup(dtype, lens, hq, hkv, d, page, seed=1)
+    fill_cache(kv, bt, lens, hkv, d, page, dtype)
+    pos = torch.tensor([p for c, n in work for p in range(c - n, c)], dtype=torch.int32, device=dev())
+    seq = torch.tensor([i for i, (c, n) in enumerate(work) for _ in range(n)], dtype=torch.int32, device=dev())
+    q = rnd(pos.shape[0], hq, d, dtype=dtype, seed=7)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    args = dict(positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5, window=window)
+    out = ops.paged_attention(q, kv, status=status, **args)
+    assert int(status.item()) == 0
+    want = ref.paged_attention(q, kv, **args)
+    assert torch.isfinite(out.float()).all()
+    close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,page,window,ctx,far", [(64, 16, None, 700, 3), (128, 64, None, 900, 64),
+                                                   (32, 8, 100, 500, 401), (128, 64, 256, 1000, 745),
+                                                   (16, 4, None, 333, 0)])
+def test_attention_finds_one_far_key(ops, dtype, d, page, window, ctx, far):
+    """One key among hundreds is made to dominate: the output must be its value, wherever in the
+    pages it lies (first key, a page's edge, the first key inside the window)."""
+    hq, hkv = 4, 2
+    bt, kv = paged_setup(dtype, [ctx], hq, hkv, d, page, seed=2)
+    ks, vs = fill_cache(kv, bt, [ctx], hkv, d, page, dtype)
+    q = rnd(1, hq, d, dtype=dtype, seed=3)
+    pg = int(bt[0, far // page])
+    for h in range(hkv):                                # key `far` points along q of its group's first head
+        kv[0, pg, h, far % page] = (q[0, h * 2].float() * 40.0).to(dtype)
+    pos = torch.tensor([ctx - 1], dtype=torch.int32, device=dev())
+    seq = torch.zeros(1, dtype=torch.int32, device=dev())
+    out = ops.paged_attention(q, kv, positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5,
+                              window=window).view(hq, d)
+    for h in range(hkv):
+        close(out[h * 2], vs[0][far, h], dtype)
+    if window is not None:                              # one key further back is outside: no trace of it
+        out_far = far - 1
+        assert ctx - 1 - out_far >= window
+        pg = int(bt[0, out_far // page])
+        kv[0, pg, :, out_far % page] = (q[0, 0].float() * 400.0).to(dtype)
+        again = ops.paged_attention(q, kv, positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5,
+                                    window=window).view(hq, d)
+        assert torch.equal(again, out)
+
+
+def test_argmax_and_ties(ops):
+    x = rnd(9, 1000, dtype=torch.float32)
+    x[3, 17] = x[3, 500] = 50.0
+    x[4, 999] = 60.0
+    got = ops.argmax(x)
+    assert got.tolist() == torch.argmax(x, dim=-1).tolist()
+    assert got[3].item() == 17 and got[4].item() == 999
+
+
+def test_sampling_matches_plain(ops):
+    n, v = 12, 389
+    logits = rnd(n, v, dtype=torch.float32, std=2.0)
+    temp = torch.tensor([1.0, 0.7, 1.3, 1.0] * 3, device=dev())
+    topk = torch.tensor([0, 5, 100, 1, 389, 400, 2, 0, 50, 0, 7, 0], dtype=torch.int32, device=dev())
+    greedy = torch.tensor([0, 0, 0, 0, 0, 0, 1, 0, 0, 1, 0, 0], dtype=torch.int32, device=dev())
+    seed = torch.tensor([11, 11, 11, 2 ** 40 + 5] * 3, dtype=torch.int64, device=dev())
+    stream = torch.arange(n, dtype=torch.int32, device=dev())
+    step = torch.tensor([0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11], dtype=torch.int32, device=dev())
+    got = ops.sample(logits, temp, topk, greedy, seed, stream, step).tolist()
+    want = ref.sample(logits.cpu(), temp.cpu(), topk.cpu(), greedy.cpu(), seed.cpu(), stream.cpu(), step.cpu()).tolist()
+    assert got == want
+    # the same row in another batch, at another place, draws the same token
+    again = ops.sample(logits[5:6].contiguous(), temp[5:6], topk[5:6], greedy[5:6], seed[5:6], stream[5:6], step[5:6])
+    assert again.item() == got[5]
+
+
+def test_sampling_distribution_and_topk(ops):
+    v, n = 64, 4000
+    row = rnd(1, v, dtype=torch.float32, std=1.5)
+    logits = row.expand(n, v).contiguous()
+    temp = torch.full((n,), 0.8, device=dev())
+    zeros = torch.zeros(n, dtype=torch.int32, device=dev())
+    seed = torch.full((n,), 99, dtype=torch.int64, device=dev())
+    step = torch.arange(n, dtype=torch.int32, device=dev())
+    draws = ops.sample(logits, temp, zeros, zeros, seed, zeros, step).cpu().numpy()
+    p = torch.softmax(row[0].cpu().double() / 0.8, dim=-1).numpy()
+    freq = np.bincount(draws, minlength=v) / n
+    assert np.abs(freq - p).max() < 4.0 * math.sqrt(p.max() / n) + 0.01
+    k = 5
+    topk = torch.full((n,), k, dtype=torch.int32, device=dev())
+    draws = ops.sample(logits, temp, topk, zeros, seed, zeros, step).cpu().numpy()
+    allowed = set(torch.topk(row[0], k).indices.tolist())
+    assert set(draws.tolist()) <= allowed and len(set(draws.tolist())) == k

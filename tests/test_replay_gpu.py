@@ -1,0 +1,117 @@
+"""The engine on the GPU against the plain implementation, in 32-bit and in bfloat16, in every
+way of cutting the work: each request alone and whole; most of it in one step and the last 32
+tokens one by one; in portions of changing size down to two tokens; and mixed, up to four live
+requests, portions of some beside decoded tokens of others, with so few pages that they are used
+again. The cache pool is poisoned with NaN so that a read outside a request's own keys shows."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+# Relative to the largest |logit| of the plain implementation. 32-bit: accumulation order only.
+# bfloat16: activations are rounded to 8 bits of mantissa about ten times a layer.
+TOL = {"float32": 5e-5, "bfloat16": 3e-2}
+LENGTHS = [1, 7, 33, 90, 61, 47, 2, 70, 18, 120, 64, 65]
+
+
+def traces_for(requests):
+    return {
+        "whole": helpers.trace_whole(requests),
+        "tail": helpers.trace_decode_tail(requests, tail=32),
+        "chunked": helpers.trace_chunked(requests, seed=1),
+        "mixed": helpers.trace_mixed(requests, seed=2),
+    }
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("C", 16), ("D", 64)])
+def test_every_cut_matches_plain(tmp_path, name, page, dtype):
+    from tinyinfer_b200.engine.replay import TraceSession
+    cfg = helpers.TINY[name]
+    folder = helpers.make_model_folder(tmp_path / name, cfg, seed=3, dtype=dtype)
+    requests = helpers.random_requests(cfg, LENGTHS, seed=5)
+    want = helpers.plain_logits(folder, requests)
+    results = {}
+    for tag, steps in traces_for(requests).items():
+        session = TraceSession(folder, dtype, helpers.peak_tokens(steps, max(64, page)), page_size=page,
+                               poison_cache=True)
+        got = helpers.collect(session, steps)
+        session.runner.check_status()
+        assert {r: len(v) for r, v in got.items()} == {r: len(t) for r, t in requests.items()}, tag
+        bad = helpers.first_bad(got, want, TOL[dtype])
+        assert bad is None, (tag, bad)
+        session.runner.manager.check_consistency()
+        if tag == "mixed":
+            stats = session.runner.manager.stats()["groups"]
+            assert all(g["pages_taken"] > g["pages"] for g in stats), "pages were not used again"
+        results[tag] = got
+    # the cuts against each other: the same position, whatever the batching
+    for tag in ("tail", "chunked", "mixed"):
+        worst = max(float(np.abs(results[tag][r][p] - results["whole"][r][p]).max())
+                    for r in requests for p in range(len(requests[r])))
+        scale = max(float(np.abs(w).max()) for w in want.values())
+        assert worst / scale <= TOL[dtype], (tag, worst / scale)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(tmp_path, dtype):
+    """A request decoded token by token from its very first token for several hundred steps."""
+    from tinyinfer_b200.engine.replay import TraceSession
+    cfg = helpers.TINY["B"]
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=9, dtype=dtype)
+    requests = helpers.random_requests(cfg, [400], seed=1)
+    want = helpers.plain_logits(folder, requests)
+    toks = requests["r0"]
+    steps = [{"step": i, "entries": [{"id": "r0", "tokens": [toks[i]], "want": [0]}],
+              "end": ["r0"] if i == len(toks) - 1 else []} for i in range(len(toks))]
+    session = TraceSession(folder, dtype, 448, page_size=8, poison_cache=True)
+    got = helpers.collect(session, steps)
+    assert helpers.first_bad(got, want, TOL[dtype]) is None
+    # the first tokens: positions 0, 1, 2 exactly where a sequence starts
+    for p in range(3):
+        err = np.abs(got["r0"][p] - want["r0"][p]).max() / np.abs(want["r0"]).max()
+        assert err <= TOL[dtype]
+
+
+def run_trace_program(folder, dtype, out, steps, max_tokens, page_size=16):
+    cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
+           "--out", str(out), "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    res = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stderr[-3000:]
+    assert [l for l in res.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """bin/trace_run as a user calls it: steps on standard input, <step>.f32 files out."""
+    cfg = helpers.TINY["B"]
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=4, dtype=dtype)
+    requests = helpers.random_requests(cfg, [40, 3, 77, 64, 20, 65], seed=8)
+    want = helpers.plain_logits(folder, requests)
+    steps = helpers.trace_mixed(requests, seed=3)
+    out = tmp_path / "out"
+    run_trace_program(folder, dtype, out, steps, helpers.peak_tokens(steps))
+    upto = {}
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    for st in steps:
+        wanted = sum(len(e["want"]) for e in st["entries"])
+        data = np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(wanted, cfg["vocab_size"])
+        row = 0
+        for e in st["entries"]:
+            s = upto.get(e["id"], 0)
+            for w in e["want"]:
+                err = np.abs(data[row] - want[e["id"]][s + w]).max() / scale
+                assert err <= TOL[dtype], (st["step"], e["id"], s + w, err)
+                row += 1
+            upto[e["id"]] = s + len(e["tokens"])

@@ -1,0 +1,55 @@
+"""Device memory behind the page ids: for every cache entry that wants pages one tensor
+[2, pages, kv_heads, page_size, head_dim] (keys then values; one (page, head) tile of
+page_size x head_dim is contiguous, which is what a tiled copy wants), and for every entry that
+wants per-request state one tensor [slots, *shape].
+
+The reference allocates [layers, 2, blocks, block_size, heads, dim] in one piece
+(tinyinfer/layers/attention.py:103-120); splitting by entry lets groups differ in every size.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .manager import CacheManager
+
+
+def bytes_per_page(needs, page_size: int, dtype: torch.dtype) -> int:
+    """Bytes one page id costs across all cache entries of all groups (they share the count)."""
+    total = 0
+    for need, _state in needs:
+        if need is not None:
+            total += 2 * need.num_kv_heads * page_size * need.head_dim * dtype.itemsize
+    return total
+
+
+class CacheStorage:
+    def __init__(self, needs, manager: CacheManager, dtype: torch.dtype, device, poison: bool = False):
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.kv: List[Optional[torch.Tensor]] = []
+        self.state: List[Optional[torch.Tensor]] = []
+        for entry, (need, state) in enumerate(needs):
+            if need is None:
+                self.kv.append(None)
+            else:
+                pages = manager.groups[manager.group_of_entry[entry]].pool.num_pages
+                shape = (2, pages, need.num_kv_heads, manager.page_size, need.head_dim)
+                t = torch.empty(shape, dtype=dtype, device=self.device)
+                # tests poison the pool: a read outside a request's own keys then shows as NaN
+                t.fill_(float("nan") if poison else 0.0)
+                self.kv.append(t)
+            if state is None:
+                self.state.append(None)
+            else:
+                self.state.append(torch.zeros((manager.max_requests, *state.shape),
+                                              dtype=state.dtype, device=self.device))
+
+    def reset_state_slot(self, slot: int) -> None:
+        for t in self.state:
+            if t is not None:
+                t[slot].zero_()
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.kv + self.state if t is not None)

@@ -1,0 +1,108 @@
+// Fused per-head RMSNorm of q and k, half-split rotary embedding, and the write of k and v into
+// the pages of the cache. One warp handles one head of one token.
+// Formulas of the reference: norm before rotation, v untouched (tinyinfer/models/qwen3.py:116-122);
+// angle = float(position) * inv_freq[j], out[j] = x[j] cos - x[j+half] sin,
+// out[j+half] = x[j+half] cos + x[j] sin (tinyinfer/csrc/rope.cu:31-74); the rotated k is what is
+// cached (tinyinfer/layers/attention.py:455-465). All arithmetic in float32, one rounding at the store.
+#include "common.cuh"
+
+constexpr int RA_WARPS = 4;
+constexpr int RA_MAX_D = 256;
+
+template <typename T>
+__global__ void qk_norm_rope_append_kernel(
+    T* __restrict__ q_out, const T* __restrict__ qkv, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const float* __restrict__ inv_freq, int rotary_dim,
+    const int* __restrict__ positions, const int* __restrict__ token_seq,
+    const int* __restrict__ block_table, int max_blocks,
+    int hq, int hkv, int d, int page_size, int num_pages, int* __restrict__ status) {
+    __shared__ float buf[RA_WARPS][RA_MAX_D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.x * RA_WARPS + warp;
+    const int t = blockIdx.y;
+    const int heads_total = hq + 2 * hkv;
+    if (head >= heads_total) return;
+    const bool is_q = head < hq;
+    const bool is_k = !is_q && head < hq + hkv;
+    if (!is_q && k_cache == nullptr) return;           // an entry that only reads the cache
+    const T* src = qkv + ((size_t)t * heads_total + head) * d;
+    float* x = buf[warp];
+
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        const float v = to_f32(src[i]);
+        x[i] = v;
+        ss += v * v;
+    }
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)d + eps);
+        for (int i = lane; i < d; i += 32) x[i] = w[i] * x[i] * inv;
+    }
+    __syncwarp();
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * hq + head) * d;
+    } else {
+        const int pos = positions[t];
+        const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0 && status) atomicExch(status, 1);   // a token without a page: never write
+            return;
+        }
+        const int kvh = is_k ? head - hq : head - hq - hkv;
+        T* base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t)page * hkv + kvh) * page_size + pos % page_size) * d;
+    }
+
+    if ((is_q || is_k) && inv_freq != nullptr) {
+        const int half = rotary_dim >> 1;
+        const float pos_f = (float)positions[t];
+        for (int i = lane; i < d; i += 32) {
+            float o;
+            if (i < rotary_dim) {
+                const int j = i < half ? i : i - half;
+                float s, c;
+                sincosf(pos_f * inv_freq[j], &s, &c);
+                o = i < half ? x[i] * c - x[i + half] * s : x[i] * c + x[i - half] * s;
+            } else {
+                o = x[i];
+            }
+            dst[i] = from_f32<T>(o);
+        }
+    } else {
+        for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(x[i]);
+    }
+}
+
+TI_API int ti_qk_norm_rope_append(
+    void* q_out, const void* qkv, void* kv_cache, const float* q_norm_w, const float* k_norm_w, float eps,
+    const float* inv_freq, int rotary_dim, const int* positions, const int* token_seq,
+    const int* block_table, int max_blocks, int num_tokens, int hq, int hkv, int d, int page_size,
+    int num_pages, int* status, int dtype, cudaStream_t stream) {
+    TI_REQUIRE(d > 0 && d <= RA_MAX_D, "qk_norm_rope_append: head_dim %d not in 1..%d", d, RA_MAX_D);
+    TI_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0,
+               "qk_norm_rope_append: rotary_dim %d must be even and at most head_dim %d", rotary_dim, d);
+    TI_REQUIRE(hq > 0 && hkv > 0 && page_size > 0 && num_tokens >= 0, "qk_norm_rope_append: bad sizes");
+    TI_REQUIRE(num_tokens <= 65535, "qk_norm_rope_append: more than 65535 tokens in one step");
+    if (num_tokens == 0) return 0;
+    const size_t v_off = (size_t)num_pages * hkv * page_size * d;
+    dim3 grid((hq + 2 * hkv + RA_WARPS - 1) / RA_WARPS, num_tokens);
+    if (dtype == TI_F32) {
+        float* kc = (float*)kv_cache;
+        qk_norm_rope_append_kernel<float><<<grid, RA_WARPS * 32, 0, stream>>>(
+            (float*)q_out, (const float*)qkv, kc, kc ? kc + v_off : nullptr, q_norm_w, k_norm_w, eps, inv_freq,
+            rotary_dim, positions, token_seq, block_table, max_blocks, hq, hkv, d, page_size, num_pages, status);
+    } else if (dtype == TI_BF16) {
+        __nv_bfloat16* kc = (__nv_bfloat16*)kv_cache;
+        qk_norm_rope_append_kernel<__nv_bfloat16><<<grid, RA_WARPS * 32, 0, stream>>>(
+            (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, kc, kc ? kc + v_off : nullptr, q_norm_w, k_norm_w,
+            eps, inv_freq, rotary_dim, positions, token_seq, block_table, max_blocks, hq, hkv, d, page_size,
+            num_pages, status);
+    } else TI_REQUIRE(false, "qk_norm_rope_append: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("qk_norm_rope_append");
+    return 0;
+}

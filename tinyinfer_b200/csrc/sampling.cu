@@ -1,0 +1,150 @@
+// Token choice from rows of float32 logits: greedy argmax, or temperature scaling, an optional
+// top-k threshold and Gumbel-max (tinyinfer/layers/sampler.py:42-43 greedy with the first index
+// winning ties; :59-63 scaled = logits / T, values below the k-th largest masked, ties at the
+// threshold kept; :69-72 argmax(scaled + G), G = -log(-log(U))).
+// U does not come from a global generator: element i of a row draws word i % 4 of the
+// Philox-4x32-10 block with counter (i / 4, step, stream, 0) and key (seed), so a row's token
+// depends only on (seed, stream, step) and its logits, whatever else is in the batch.
+#include "common.cuh"
+
+constexpr int SP_THREADS = 256;
+
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const unsigned hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        const unsigned hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+        k.x += 0x9E3779B9u;
+        k.y += 0xBB67AE85u;
+    }
+    return c;
+}
+__device__ __forceinline__ float philox_uniform(unsigned word) {   // in (0, 1), exact in float32
+    return ((float)(word >> 9) + 0.5f) * (1.0f / 8388608.0f);
+}
+__device__ __forceinline__ unsigned order_key(float v) {           // larger float -> larger key
+    const unsigned b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+struct Best { float v; int i; };
+__device__ __forceinline__ Best better(Best a, Best b) {
+    if (b.i < 0) return a;
+    if (a.i < 0) return b;
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+__device__ __forceinline__ Best block_best(Best x, Best* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best y;
+        y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+        y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+        x = better(x, y);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) sh[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        Best y = lane < SP_THREADS / 32 ? sh[lane] : Best{0.f, -1};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best z;
+            z.v = __shfl_xor_sync(0xffffffffu, y.v, o);
+            z.i = __shfl_xor_sync(0xffffffffu, y.i, o);
+            y = better(y, z);
+        }
+        if (lane == 0) sh[0] = y;
+    }
+    __syncthreads();
+    return sh[0];
+}
+
+__global__ void __launch_bounds__(SP_THREADS) sample_kernel(
+    int* __restrict__ out, const float* __restrict__ logits, int vocab,
+    const float* __restrict__ temperature, const int* __restrict__ topk, const int* __restrict__ greedy,
+    const long long* __restrict__ seed, const int* __restrict__ stream_id, const int* __restrict__ step) {
+    __shared__ Best sh_best[SP_THREADS / 32];
+    __shared__ unsigned hist[256];
+    __shared__ unsigned sel_prefix, sel_remaining;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* x = logits + (size_t)row * vocab;
+
+    if (greedy == nullptr || greedy[row]) {
+        Best b{0.f, -1};
+        for (int i = tid; i < vocab; i += SP_THREADS) {
+            const float v = x[i];
+            if (v == v) b = better(b, Best{v, i});
+        }
+        b = block_best(b, sh_best);
+        if (tid == 0) out[row] = b.i < 0 ? 0 : b.i;
+        return;
+    }
+
+    const float temp = temperature[row];
+    const int k = topk[row];
+    unsigned threshold = 0u;                              // keys below it are masked
+    if (k > 0 && k < vocab) {
+        // radix select of the k-th largest key, one byte per pass from the top
+        if (tid == 0) { sel_prefix = 0u; sel_remaining = (unsigned)k; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            hist[tid] = 0u;
+            __syncthreads();
+            const unsigned prefix = sel_prefix;
+            const unsigned mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+            for (int i = tid; i < vocab; i += SP_THREADS) {
+                const float v = x[i] / temp;
+                if (!(v == v)) continue;
+                const unsigned key = order_key(v);
+                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned remaining = sel_remaining;
+                int b = 255;
+                for (; b > 0; --b) {
+                    if (hist[b] >= remaining) break;
+                    remaining -= hist[b];
+                }
+                sel_prefix = prefix | ((unsigned)b << shift);
+                sel_remaining = remaining;
+            }
+            __syncthreads();
+        }
+        threshold = sel_prefix;
+    }
+
+    const uint2 key2 = make_uint2((unsigned)(seed[row] & 0xFFFFFFFFll), (unsigned)((unsigned long long)seed[row] >> 32));
+    const unsigned c1 = (unsigned)step[row], c2 = (unsigned)stream_id[row];
+    Best b{0.f, -1};
+    for (int blk = tid; blk * 4 < vocab; blk += SP_THREADS) {
+        const uint4 r = philox4x32_10(make_uint4((unsigned)blk, c1, c2, 0u), key2);
+        const unsigned words[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = blk * 4 + j;
+            if (i >= vocab) break;
+            const float v = x[i] / temp;
+            if (!(v == v) || v == -INFINITY) continue;
+            if (order_key(v) < threshold) continue;
+            const float u = philox_uniform(words[j]);
+            const float g = -logf(-logf(u));
+            b = better(b, Best{v + g, i});
+        }
+    }
+    b = block_best(b, sh_best);
+    if (tid == 0) out[row] = b.i < 0 ? 0 : b.i;
+}
+
+// greedy == nullptr: every row is an argmax and the other per-row arrays are not read.
+TI_API int ti_sample(int* out, const float* logits, int num_rows, int vocab, const float* temperature,
+                     const int* topk, const int* greedy, const long long* seed, const int* stream_id,
+                     const int* step, cudaStream_t stream) {
+    TI_REQUIRE(num_rows >= 0 && vocab > 0, "sample: bad sizes");
+    if (num_rows == 0) return 0;
+    sample_kernel<<<num_rows, SP_THREADS, 0, stream>>>(out, logits, vocab, temperature, topk, greedy, seed, stream_id, step);
+    TI_CHECK_LAUNCH("sample");
+    return 0;
+}

@@ -1,0 +1,146 @@
+"""One step's batch: the tokens it brings, flattened, with everything a kernel needs to know
+about whose they are. It replaces the reference's module-global Context
+(tinyinfer/utils/context.py:8-36) and the tensors of prepare_batch
+(tinyinfer/engine/model_runner.py:310-357) by one explicit object.
+
+All index arrays live in ONE int32 device buffer filled by ONE host-to-device copy from pinned
+memory; the fields below are views into it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them whose logits
+    are wanted (indices into ``tokens``)."""
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class CacheView:
+    """What a mixer sees of the cache entry it works on in this step."""
+    kv: Optional[torch.Tensor]            # [2, pages, kv_heads, page_size, head_dim] or None
+    block_table: Optional[torch.Tensor]   # int32 [S, max_blocks], -1 where no page is held
+    page_size: int
+    writes: bool                          # False: read what another entry of the run order wrote
+    state: Optional[torch.Tensor]         # [slots, *shape] or None
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_seqs: int
+    num_logit_rows: int
+    token_ids: torch.Tensor        # int32 [T]
+    positions: torch.Tensor        # int32 [T]  absolute position of each token in its request
+    token_seq: torch.Tensor        # int32 [T]  which entry of the step the token belongs to
+    cu_seqlens: torch.Tensor       # int32 [S + 1]
+    q_starts: torch.Tensor         # int32 [S]  position of each entry's first token
+    context_lens: torch.Tensor     # int32 [S]  length of each request after this step
+    state_slots: torch.Tensor      # int32 [S]
+    logit_rows: torch.Tensor       # int32 [N]  flat rows whose logits are wanted
+    block_tables: List[torch.Tensor]      # per cache group: int32 [S, max_blocks]
+    status: Optional[torch.Tensor]        # int32 [1] device word set by kernels on a bad index
+    # host copies, for choosing kernels and grids without a device read
+    q_lens: List[int] = field(default_factory=list)
+    starts: List[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_context: int = 0
+    # filled by the runner: entry of the run order -> CacheView
+    views: Dict[int, CacheView] = field(default_factory=dict)
+
+    def cache_view(self, exec_step) -> CacheView:
+        base = self.views[exec_step.cache]
+        if base.writes == exec_step.writes_cache:
+            return base
+        return CacheView(base.kv, base.block_table, base.page_size, exec_step.writes_cache, base.state)
+
+
+class BatchBuffers:
+    """Pinned host staging and the device buffer the step's index arrays are copied into."""
+
+    def __init__(self, device, max_tokens: int, max_seqs: int, max_blocks: int, num_groups: int):
+        self.device = torch.device(device)
+        self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        self.max_blocks, self.num_groups = max_blocks, num_groups
+        words = 3 * max_tokens + 4 * max_seqs + 1 + max_tokens + num_groups * max_seqs * max_blocks + 64
+        self.host = torch.empty(words, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        self.dev = torch.empty(words, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
+        self._copy_pending = False
+
+    def build(self, entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
+              tables: Sequence[Sequence[Sequence[int]]]) -> StepContext:
+        """``starts[i]``: tokens entry i's request already holds; ``slots[i]``: its state slot;
+        ``tables[g][i]``: its block table in cache group g."""
+        q_lens = [len(e.tokens) for e in entries]
+        t, s = sum(q_lens), len(entries)
+        if t > self.max_tokens or s > self.max_seqs:
+            raise ValueError(f"step of {t} tokens / {s} requests exceeds the buffers "
+                             f"({self.max_tokens} / {self.max_seqs})")
+        ids: List[int] = []
+        pos: List[int] = []
+        seq: List[int] = []
+        rows: List[int] = []
+        cu = [0]
+        for i, e in enumerate(entries):
+            n = q_lens[i]
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.request_id!r}: wanted place {w} is not among its {n} tokens")
+                rows.append(cu[-1] + w)
+            ids.extend(int(x) for x in e.tokens)
+            pos.extend(range(starts[i], starts[i] + n))
+            seq.extend([i] * n)
+            cu.append(cu[-1] + n)
+        ctx_lens = [starts[i] + q_lens[i] for i in range(s)]
+        widths = [max((len(tb) for tb in tables[g]), default=0) for g in range(self.num_groups)]
+        widths = [max(1, w) for w in widths]
+        if max(widths, default=1) > self.max_blocks:
+            raise ValueError("a block table is longer than the buffers allow")
+        flat: List[int] = []
+        offsets = {}
+
+        def put(name, values):
+            offsets[name] = (len(flat), len(values))
+            flat.extend(values)
+            flat.extend([0] * (-len(flat) % 4))             # keep every array 16-byte aligned
+
+        put("ids", ids); put("pos", pos); put("seq", seq); put("cu", cu)
+        put("starts", list(starts)); put("ctx", ctx_lens); put("slots", list(slots)); put("rows", rows)
+        for g in range(self.num_groups):
+            w = widths[g]
+            padded: List[int] = []
+            for tb in tables[g]:
+                padded.extend(tb)
+                padded.extend([-1] * (w - len(tb)))
+            put(f"bt{g}", padded)
+        n = len(flat)
+        if self._copy_pending:                 # the last step's copy may still be reading the host buffer
+            self._copied.synchronize()
+        self.host[:n] = torch.tensor(flat, dtype=torch.int32)
+        self.dev[:n].copy_(self.host[:n], non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+            self._copy_pending = True
+
+        def view(name):
+            o, ln = offsets[name]
+            return self.dev[o:o + ln]
+
+        return StepContext(
+            num_tokens=t, num_seqs=s, num_logit_rows=len(rows),
+            token_ids=view("ids"), positions=view("pos"), token_seq=view("seq"),
+            cu_seqlens=view("cu"), q_starts=view("starts"), context_lens=view("ctx"),
+            state_slots=view("slots"), logit_rows=view("rows"),
+            block_tables=[view(f"bt{g}").view(s, widths[g]) for g in range(self.num_groups)],
+            status=self.status, q_lens=q_lens, starts=list(starts), max_q_len=max(q_lens, default=0),
+            max_context=max(ctx_lens, default=0))

@@ -1,0 +1,118 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+One call runs only the tokens it is given, as one flat batch, against the cache that earlier
+calls left: portions of prompts beside single decoded tokens, cut anywhere. It is the only
+forward path of the framework: generation, the trace replay and the benchmark all go through
+``ModelRunner.step``. It corresponds to the reference's ModelRunner.run / prepare_batch
+(tinyinfer/engine/model_runner.py:310-460) without the sampling, which is a separate call on
+the returned logits.
+"""
+from __future__ import annotations
+
+from typing import Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager, CacheStorage, bytes_per_page
+from .batch import BatchBuffers, CacheView, StepContext, StepEntry
+
+
+class ModelRunner:
+    def __init__(self, model, *, page_size: int, num_pages: int, max_requests: int,
+                 max_tokens_per_step: int, max_model_len: int, poison_cache: bool = False):
+        self.model = model
+        self.device = model.device
+        needs = model.cache_needs()
+        self.manager = CacheManager(needs, page_size, num_pages, max_requests)
+        self.storage = CacheStorage(needs, self.manager, model.dtype, self.device, poison=poison_cache)
+        self.max_model_len = max_model_len
+        max_blocks = (max_model_len + page_size - 1) // page_size
+        self.buffers = BatchBuffers(self.device, max_tokens_per_step, max_requests, max_blocks,
+                                    max(1, len(self.manager.groups)))
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ requests
+    def admit(self, request_id: Hashable) -> None:
+        rc = self.manager.admit(request_id)
+        self.storage.reset_state_slot(rc.state_slot)
+
+    def release(self, request_id: Hashable) -> None:
+        self.manager.release(request_id)
+
+    def length(self, request_id: Hashable) -> int:
+        return self.manager.get(request_id).length
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries' tokens and returns float32 logits [N, V] on the device, N being the
+        number of wanted places, in the order of the entries and of each ``want``.
+        A request id not seen before is admitted. Raises CacheExhausted before anything runs
+        if the pages do not suffice."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        ids = [e.request_id for e in entries]
+        if len(set(ids)) != len(ids):
+            raise ValueError("a request may appear once in a step")
+        if not entries:
+            return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
+        for rid in ids:
+            if rid not in self.manager:
+                self.admit(rid)
+        vocab = self.model.spec.vocab_size
+        starts: List[int] = []
+        for e in entries:
+            start = self.manager.get(e.request_id).length
+            if start + len(e.tokens) > self.max_model_len:
+                raise ValueError(f"request {e.request_id!r} would reach {start + len(e.tokens)} tokens, "
+                                 f"the limit is {self.max_model_len}")
+            for tok in e.tokens:
+                if not 0 <= int(tok) < vocab:
+                    raise ValueError(f"token id {tok} is outside the vocabulary of {vocab}")
+            starts.append(start)
+        for e, start in zip(entries, starts):
+            self.manager.extend(e.request_id, start + len(e.tokens))
+        caches = [self.manager.get(rid) for rid in ids]
+        num_groups = len(self.manager.groups)
+        tables = [[rc.tables[g] for rc in caches] for g in range(num_groups)] or [[[] for _ in caches]]
+        ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables)
+        self._bind_views(ctx)
+        logits = self.model.forward(ctx)
+        for e, start in zip(entries, starts):
+            self.manager.commit(e.request_id, start + len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def _bind_views(self, ctx: StepContext) -> None:
+        for entry in range(self.model.spec.num_cache_entries):
+            g = self.manager.group_of_entry.get(entry)
+            ctx.views[entry] = CacheView(
+                kv=self.storage.kv[entry],
+                block_table=ctx.block_tables[g] if g is not None else None,
+                page_size=self.manager.page_size, writes=True, state=self.storage.state[entry])
+
+    def check_status(self) -> None:
+        """Reads the word kernels set when they met an index without a page (synchronises)."""
+        code = int(self.buffers.status.item())
+        if code:
+            self.buffers.status.zero_()
+            raise RuntimeError(f"a kernel met a token or key without a page (status {code})")
+
+
+def pages_that_fit(model, page_size: int, free_bytes: int, utilization: float,
+                   max_tokens_per_step: int, max_requests: int) -> int:
+    """Pages per group that the device can hold beside the step's activations: the reference's
+    formula (tinyinfer/engine/model_runner.py:131-176) with an analytic activation bound in
+    place of its dummy forward."""
+    spec = model.spec
+    widest = spec.hidden_size
+    for layer in spec.layers:
+        mixer, ffn = layer.mixer, layer.feed_forward
+        widest = max(widest, getattr(mixer, "q_size", 0) + 2 * getattr(mixer, "kv_size", 0),
+                     2 * getattr(ffn, "intermediate_size", 0))
+    itemsize = model.dtype.itemsize
+    activations = max_tokens_per_step * (4 * spec.hidden_size + 3 * widest) * itemsize
+    activations += max_requests * spec.vocab_size * 4 * 3
+    budget = int(free_bytes * utilization) - activations
+    per_page = bytes_per_page(model.cache_needs(), page_size, model.dtype)
+    if per_page == 0:
+        return 1
+    return max(0, budget // per_page)

@@ -1,0 +1,272 @@
+"""Python face of the CUDA kernels: one function per kernel family.
+
+Every function checks shapes and dtypes, allocates its output with torch, and calls an
+``extern "C"`` launcher of ``tinyinfer_b200/csrc`` on the current CUDA stream. There is no CPU
+path and no library attention or model code behind these names: a tensor that is not on a CUDA
+device, or a library that cannot be built, raises.
+
+Conventions: activations and matrices are bfloat16 or float32 (the model's compute dtype),
+norm weights, biases and logits are float32, indices are int32, and everything is contiguous.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import library
+
+c_int, c_float, c_void_p, c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SIGNATURES = {
+    "core": {
+        "ti_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "ti_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+        "ti_add": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p],
+        "ti_qk_norm_rope_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                   c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+        "ti_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                 c_void_p, c_int, c_void_p],
+        "ti_gemm_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                         c_int, c_int, c_int, c_void_p],
+        "ti_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_void_p],
+    },
+}
+_bound = {}
+
+
+def _fn(lib_name: str, name: str):
+    key = (lib_name, name)
+    fn = _bound.get(key)
+    if fn is None:
+        lib = library.load(lib_name)
+        fn = getattr(lib, name)
+        fn.argtypes = _SIGNATURES[lib_name][name]
+        fn.restype = c_int
+        _bound[key] = fn
+    return fn
+
+
+def _run(lib_name: str, name: str, *args) -> None:
+    rc = _fn(lib_name, name)(*args)
+    if rc != 0:
+        msg = library.load(lib_name).ti_last_error().decode(errors="replace")
+        raise KernelError(f"{name} failed ({rc}): {msg}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"compute dtype must be float32 or bfloat16, got {t.dtype}")
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, ndim: Optional[int] = None) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor: tinyinfer_b200 has no CPU path")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# ---------------------------------------------------------------------- elementwise
+def embedding(token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """rows of ``table`` [V, H] at ``token_ids`` int32 [T] -> [T, H]."""
+    _check(token_ids, "token_ids", torch.int32, 1)
+    _check(table, "table", None, 2)
+    out = torch.empty((token_ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
+    _run("core", "ti_embedding", out.data_ptr(), table.data_ptr(), token_ids.data_ptr(),
+         token_ids.shape[0], table.shape[1], table.shape[0], _dtype_code(table), _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """w * x * rsqrt(mean(x^2) + eps) over the last axis; ``rows`` int32 [N] picks input rows."""
+    _check(x, "x")
+    _check(weight, "weight", torch.float32, 1)
+    size = x.shape[-1]
+    if weight.shape[0] != size:
+        raise KernelError(f"norm weight has {weight.shape[0]} entries, rows have {size}")
+    if rows is None:
+        out = torch.empty_like(x)
+        n = x.numel() // size
+    else:
+        _check(rows, "rows", torch.int32, 1)
+        if x.dim() != 2:
+            raise KernelError("row selection needs a 2-D input")
+        n = rows.shape[0]
+        out = torch.empty((n, size), dtype=x.dtype, device=x.device)
+    _run("core", "ti_rmsnorm", out.data_ptr(), x.data_ptr(), weight.data_ptr(), _ptr(rows), n, size,
+         float(eps), _dtype_code(x), _stream())
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a + b, summed in float32 and rounded once."""
+    _check(a, "a")
+    _check(b, "b", a.dtype)
+    if a.shape != b.shape:
+        raise KernelError(f"add: shapes differ {tuple(a.shape)} vs {tuple(b.shape)}")
+    out = torch.empty_like(a)
+    _run("core", "ti_add", out.data_ptr(), a.data_ptr(), b.data_ptr(), a.numel(), _dtype_code(a), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- matrix products
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None, out_float32: bool = False) -> torch.Tensor:
+    """x [M, K] . w [N, K]^T (+ bias [N]) (+ residual [M, N]), float32 accumulation.
+    ``out_float32`` stores the accumulator unrounded (logits)."""
+    _check(x, "x", None, 2)
+    _check(w, "w", x.dtype, 2)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"linear: x has {k} columns, w has {w.shape[1]}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    if residual is not None:
+        _check(residual, "residual", x.dtype, 2)
+        if tuple(residual.shape) != (m, n):
+            raise KernelError("linear: residual shape differs from the output's")
+    out = torch.empty((m, n), dtype=torch.float32 if out_float32 else x.dtype, device=x.device)
+    _run("core", "ti_gemm_simt", out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual),
+         m, n, k, 0, int(out_float32 and x.dtype != torch.float32), _dtype_code(x), _stream())
+    return out
+
+
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x.Wg^T) * (x.Wu^T) with ``w_gate_up`` = [Wg; Wu] of shape [2I, K] -> [M, I]; the
+    activation and the product act on the float32 accumulators, one rounding."""
+    _check(x, "x", None, 2)
+    _check(w_gate_up, "w_gate_up", x.dtype, 2)
+    m, k = x.shape
+    if w_gate_up.shape[1] != k or w_gate_up.shape[0] % 2:
+        raise KernelError("gated_linear: weight must be [2I, K]")
+    inter = w_gate_up.shape[0] // 2
+    out = torch.empty((m, inter), dtype=x.dtype, device=x.device)
+    _run("core", "ti_gemm_simt", out.data_ptr(), x.data_ptr(), w_gate_up.data_ptr(), None, None,
+         m, inter, k, 1, 0, _dtype_code(x), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- attention
+def qk_norm_rope_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
+                        q_norm_weight: Optional[torch.Tensor], k_norm_weight: Optional[torch.Tensor],
+                        eps: float, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                        positions: torch.Tensor, token_seq: torch.Tensor,
+                        kv_cache: Optional[torch.Tensor], block_table: torch.Tensor,
+                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Splits ``qkv`` [T, (Hq + 2 Hkv) D] by heads; norms q and k per head, rotates them by
+    their positions, returns q [T, Hq, D] and writes k and v into the pages of
+    ``kv_cache`` [2, pages, Hkv, page, D] (None: the entry only reads the cache)."""
+    _check(qkv, "qkv", None, 2)
+    t = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError("qk_norm_rope_append: qkv width does not match the head counts")
+    _check(positions, "positions", torch.int32, 1)
+    _check(token_seq, "token_seq", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    for name, w in (("q_norm_weight", q_norm_weight), ("k_norm_weight", k_norm_weight)):
+        if w is not None:
+            _check(w, name, torch.float32, 1)
+            if w.shape[0] != head_dim:
+                raise KernelError(f"{name} must have head_dim entries")
+    if inv_freq is not None:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] * 2 != rotary_dim:
+            raise KernelError("inv_freq must have rotary_dim / 2 entries")
+    page_size = num_pages = 1
+    if kv_cache is not None:
+        _check(kv_cache, "kv_cache", qkv.dtype, 5)
+        if kv_cache.shape[0] != 2 or kv_cache.shape[2] != num_kv_heads or kv_cache.shape[4] != head_dim:
+            raise KernelError(f"kv_cache shape {tuple(kv_cache.shape)} is not [2, pages, Hkv, page, D]")
+        num_pages, page_size = kv_cache.shape[1], kv_cache.shape[3]
+    q = torch.empty((t, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    _run("core", "ti_qk_norm_rope_append", q.data_ptr(), qkv.data_ptr(), _ptr(kv_cache),
+         _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), _ptr(inv_freq),
+         rotary_dim if inv_freq is not None else 0, positions.data_ptr(), token_seq.data_ptr(),
+         block_table.data_ptr(), block_table.shape[1], t, num_heads, num_kv_heads, head_dim,
+         page_size, num_pages, _ptr(status), _dtype_code(qkv), _stream())
+    return q
+
+
+def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch.Tensor,
+                    token_seq: torch.Tensor, block_table: torch.Tensor, scale: float,
+                    window: Optional[int] = None, step=None,
+                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of q [T, Hq, D] over the pages of each token's own request.
+    Token t sees keys max(0, pos - window + 1) .. pos of request ``token_seq[t]``.
+    Returns [T, Hq * D]. ``step`` (the batch summary) lets the op pick a faster kernel."""
+    _check(q, "q", None, 3)
+    _check(kv_cache, "kv_cache", q.dtype, 5)
+    _check(positions, "positions", torch.int32, 1)
+    _check(token_seq, "token_seq", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    t, hq, d = q.shape
+    _, num_pages, hkv, page_size, d2 = kv_cache.shape
+    if d2 != d or kv_cache.shape[0] != 2:
+        raise KernelError("paged_attention: kv_cache does not match q")
+    out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
+    _run("core", "ti_attention_generic", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+         positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+         t, hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), _ptr(status),
+         _dtype_code(q), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Index of the largest logit of every row (first index on ties), int32 [N]."""
+    _check(logits, "logits", torch.float32, 2)
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    _run("core", "ti_sample", out.data_ptr(), logits.data_ptr(), logits.shape[0], logits.shape[1],
+         None, None, None, None, None, None, _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, topk: torch.Tensor, greedy: torch.Tensor,
+           seed: torch.Tensor, stream_id: torch.Tensor, step: torch.Tensor) -> torch.Tensor:
+    """One token per row of float32 logits [N, V]. Per row: ``greedy`` (int32 0/1),
+    ``temperature`` (float32 > 0), ``topk`` (int32, 0 = off), and the random stream
+    (``seed`` int64, ``stream_id`` int32, ``step`` int32)."""
+    _check(logits, "logits", torch.float32, 2)
+    n = logits.shape[0]
+    for name, t, dt in (("temperature", temperature, torch.float32), ("topk", topk, torch.int32),
+                        ("greedy", greedy, torch.int32), ("seed", seed, torch.int64),
+                        ("stream_id", stream_id, torch.int32), ("step", step, torch.int32)):
+        _check(t, name, dt, 1)
+        if t.shape[0] != n:
+            raise KernelError(f"{name} must have one entry per row")
+    out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _run("core", "ti_sample", out.data_ptr(), logits.data_ptr(), n, logits.shape[1],
+         temperature.data_ptr(), topk.data_ptr(), greedy.data_ptr(), seed.data_ptr(),
+         stream_id.data_ptr(), step.data_ptr(), _stream())
+    return out
+
+
+def launch_count() -> int:
+    return library.launch_count()
