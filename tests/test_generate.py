@@ -1,0 +1,135 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation. Greedy tokens are checked by teacher forcing: at every generated position the
+engine's token must have (up to rounding) the largest plain logit, so a tie flipped by rounding
+does not fail the test while a wrong token does."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_qwen3 as plain
+import torch_ops
+from tinyinfer_b200.sampling import SamplingParams
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def check_greedy(folder, prompt, generated, tol):
+    cfg, w = plain.read_model_folder(folder, torch.float64)
+    logits = plain.forward(cfg, w, list(prompt) + list(generated)).numpy()
+    for i, tok in enumerate(generated):
+        row = logits[len(prompt) - 1 + i]
+        assert row.max() - row[tok] <= tol * np.abs(logits).max(), (i, tok, int(row.argmax()))
+
+
+def generate_and_check(llm, folder, cfg, tol):
+    requests = helpers.random_requests(cfg, [1, 7, 16, 33, 50], seed=6)
+    prompts = list(requests.values())
+    outs = llm.generate(prompts, SamplingParams(greedy=True, max_tokens=8))
+    assert [len(o["token_ids"]) for o in outs] == [8] * 5
+    for p, o in zip(prompts, outs):
+        assert o["all_token_ids"] == p + o["token_ids"] and o["finish_reason"] == "max_tokens"
+        assert o["statistics"]["output_tokens"] == 8 and o["statistics"]["ttft"] > 0
+        check_greedy(folder, p, o["token_ids"], tol)
+    # one request at a time gives the same tokens as the batch did
+    for p, o in zip(prompts[:3], outs[:3]):
+        alone = llm.generate([p], SamplingParams(greedy=True, max_tokens=8))[0]
+        check_greedy(folder, p, alone["token_ids"], tol)
+    assert not llm.runner.manager.live_requests
+    llm.runner.manager.check_consistency()
+    return prompts, outs
+
+
+def test_generate_with_plain_ops_on_cpu(tmp_path, monkeypatch):
+    """The entry point's loop (schedule, step, sample, postprocess) with the kernels replaced by
+    their plain statements; few pages, small budgets, so portions, waiting and reuse happen."""
+    from tinyinfer_b200 import ops
+    import tinyinfer_b200.engine.llm as llm_mod
+    for name in torch_ops.ALL:
+        monkeypatch.setattr(ops, name, getattr(torch_ops, name))
+    monkeypatch.setattr(llm_mod, "require_cuda", lambda d: torch.device("cpu"))
+    cfg = helpers.TINY_A
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=3)
+    llm = llm_mod.LLM(folder, dtype="float32", device="cpu", max_num_batched_tokens=24, max_num_seqs=3,
+                      kvcache_block_size=4, num_kvcache_blocks=30, prefill_chunk=8, max_model_len=128)
+    generate_and_check(llm, folder, cfg, 1e-5)
+    assert llm.runner.manager.stats()["groups"][0]["pages_taken"] > 30
+
+
+def test_the_package_refuses_to_run_without_cuda(tmp_path):
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    from tinyinfer_b200 import LLM
+    folder = helpers.make_model_folder(tmp_path / "m", helpers.TINY_A, seed=3)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        LLM(folder, num_kvcache_blocks=8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        LLM(folder, device="cpu", num_kvcache_blocks=8)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 3e-2)])
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("D", 64)])
+def test_greedy_generation_on_the_gpu(tmp_path, name, page, dtype, tol):
+    from tinyinfer_b200 import LLM
+    cfg = helpers.TINY[name]
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=3, dtype=dtype)
+    llm = LLM(folder, dtype=dtype, max_num_batched_tokens=24, max_num_seqs=3, kvcache_block_size=page,
+              num_kvcache_blocks=max(6, 120 // page), prefill_chunk=8, max_model_len=128)
+    generate_and_check(llm, folder, cfg, tol)
+    llm.runner.check_status()
+
+
+@pytest.mark.gpu
+def test_temperature_sampling_is_reproducible_and_follows_the_plain_sampler(tmp_path):
+    from tinyinfer_b200 import LLM
+    cfg = helpers.TINY_B
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=1)
+    requests = helpers.random_requests(cfg, [2, 11, 29, 64, 100], seed=7)
+    prompts = list(requests.values())
+
+    def run():
+        llm = LLM(folder, dtype="float32", max_num_batched_tokens=64, max_num_seqs=4, kvcache_block_size=8,
+                  num_kvcache_blocks=64, prefill_chunk=16, max_model_len=256, seed=5)
+        params = [SamplingParams(temperature=1.0, topk=0, max_tokens=16, seed=77),
+                  SamplingParams(temperature=0.7, topk=20, max_tokens=16),
+                  SamplingParams(greedy=True, max_tokens=16),
+                  SamplingParams(temperature=1.0, topk=100, max_tokens=16, seed=77),
+                  SamplingParams(temperature=1.3, topk=5, max_tokens=16)]
+        return llm.generate(prompts, params), params
+    a, params = run()
+    b, _ = run()
+    assert [o["token_ids"] for o in a] == [o["token_ids"] for o in b]
+    assert len({tuple(o["token_ids"]) for o in a}) == 5
+    # teacher-forced check of every sampled token with the plain sampler on the plain logits
+    pcfg, w = plain.read_model_folder(folder, torch.float64)
+    agree = total = 0
+    for i, (p, o, sp) in enumerate(zip(prompts, a, params)):
+        logits = plain.forward(pcfg, w, p + o["token_ids"]).float().numpy()
+        for step, tok in enumerate(o["token_ids"]):
+            want = plain.sample(logits[len(p) - 1 + step], greedy=sp.greedy, temperature=sp.temperature,
+                                topk=sp.topk, seed=5 if sp.seed is None else sp.seed, stream=i, step=step)
+            agree += int(want == tok)
+            total += 1
+    assert agree >= total - 1, (agree, total)       # rounding may flip one near-tie
+
+
+@pytest.mark.gpu
+def test_command_line(tmp_path):
+    folder = helpers.make_model_folder(tmp_path / "m", helpers.TINY_A, seed=3)
+    cmd = [sys.executable, str(ROOT / "examples" / "generate.py"), "--model", str(folder), "--dtype", "fp32",
+           "--prompt-ids", "5,17,3,200", "--prompt-len", "9", "--greedy", "--max-tokens", "6",
+           "--max-num-seqs", "2", "--max-num-batched-tokens", "16", "--block-size", "4",
+           "--num-kvcache-blocks", "32", "--max-model-len", "64"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    rows = [json.loads(l) for l in res.stdout.splitlines() if l.startswith("{")]
+    assert len(rows) == 2 and all(len(r["token_ids"]) == 6 for r in rows)
+    check_greedy(folder, [5, 17, 3, 200], rows[0]["token_ids"], 5e-5)
+    bad = subprocess.run(cmd + ["--speculative"], capture_output=True, text=True, timeout=600)
+    assert bad.returncode != 0 and "does not build" in bad.stderr

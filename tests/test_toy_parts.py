@@ -1,0 +1,161 @@
+"""A mixer with state of its own, a run order that names a layer twice, and an entry that reads
+another entry's cache: all defined HERE, registered, built and stepped through the framework's
+own model, cache and step function without touching its files. The toy is no one's model."""
+import json
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_qwen3 as plain
+import torch_ops
+from tinyinfer_b200.config import (AttentionSpec, ExecStep, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec,
+                                   PositionSpec, TensorNames, register_architecture)
+from tinyinfer_b200.models import DecoderModel
+from tinyinfer_b200.parts import Mixer, StateNeed, TensorSpec, register_mixer
+
+
+# ------------------------------------------------------------------ the toy, as a user would write it
+@dataclass(frozen=True)
+class RunningMeanSpec:
+    hidden_size: int
+    kind: str = "toy_running_mean"
+
+
+class RunningMeanMixer(Mixer):
+    """out[t] = mean over the request's tokens 0..t of (x W^T). Its state, one float32 vector per
+    request, is the sum so far; it keeps no pages."""
+
+    def tensors(self):
+        h = self.spec.hidden_size
+        return {"proj.weight": TensorSpec((h, h))}
+
+    def load(self, tensors):
+        self.w = tensors["proj.weight"]
+
+    def state_need(self):
+        return StateNeed((self.spec.hidden_size,), torch.float32)
+
+    def forward(self, x, step, cache):
+        y = (x.float() @ self.w.float().T)
+        out = torch.empty_like(y)
+        row = 0
+        for i, (n, start) in enumerate(zip(step.q_lens, step.starts)):
+            slot = int(step.state_slots[i])
+            running = cache.state[slot] + torch.cumsum(y[row:row + n], dim=0)
+            counts = torch.arange(start + 1, start + n + 1, device=y.device, dtype=torch.float32)[:, None]
+            out[row:row + n] = running / counts
+            cache.state[slot] = running[-1]
+            row += n
+        return out.to(x.dtype)
+
+
+register_mixer("toy_running_mean", RunningMeanMixer)
+
+TOY = dict(architectures=["ToyForCausalLM"], vocab_size=97, hidden_size=48, heads=3, kv_heads=1, head_dim=16,
+           intermediate_size=80, eps=1e-5, theta=10000.0, max_positions=256)
+
+
+class ToyConfig:
+    def __init__(self, d):
+        self.d = dict(d)
+        self.architectures = d["architectures"]
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def to_dict(self):
+        return dict(self.d)
+
+    def model_spec(self):
+        d = self.d
+        h, eps = d["hidden_size"], d["eps"]
+        attn = AttentionSpec(h, d["heads"], d["kv_heads"], d["head_dim"], d["head_dim"] ** -0.5,
+                             PositionSpec("rope", d["theta"], d["head_dim"]), qk_norm=NormSpec(d["head_dim"], eps))
+        ffn = GatedMLPSpec(h, d["intermediate_size"])
+        norm = NormSpec(h, eps)
+        layers = (LayerSpec(attn, ffn, norm, norm), LayerSpec(RunningMeanSpec(h), ffn, norm, norm))
+        # layer 0 runs three times: with a cache of its own, again with another cache, and at the
+        # end reading the keys its first run wrote; the stateful toy layer sits in between
+        execution = (ExecStep(0, 0), ExecStep(1, 1), ExecStep(0, 2), ExecStep(0, 0, writes_cache=False))
+        return ModelSpec("ToyForCausalLM", d["vocab_size"], h, layers, execution, norm,
+                         tie_embeddings=True, max_positions=d["max_positions"], names=TensorNames())
+
+
+register_architecture("ToyForCausalLM", ToyConfig, lambda cfg, dtype, device: DecoderModel(cfg.model_spec(), dtype, device))
+
+
+# ------------------------------------------------------------------ its plain statement
+def toy_plain(w, tokens):
+    d = TOY
+    cfg = dict(num_attention_heads=d["heads"], num_key_value_heads=d["kv_heads"], head_dim=d["head_dim"],
+               rms_norm_eps=d["eps"], rope_theta=d["theta"], hidden_size=d["hidden_size"])
+    pos = list(range(len(tokens)))
+    t = len(tokens)
+
+    def attn_layer(x, kv_from=None):
+        p = "model.layers.0."
+        hn = plain.rmsnorm(x, w[p + "input_layernorm.weight"], d["eps"])
+        src = hn if kv_from is None else kv_from
+        q = (hn @ w[p + "self_attn.q_proj.weight"].T).view(t, d["heads"], d["head_dim"])
+        k = (src @ w[p + "self_attn.k_proj.weight"].T).view(t, d["kv_heads"], d["head_dim"])
+        v = (src @ w[p + "self_attn.v_proj.weight"].T).view(t, d["kv_heads"], d["head_dim"])
+        q = plain.rope(plain.rmsnorm(q, w[p + "self_attn.q_norm.weight"], d["eps"]), pos, d["theta"])
+        k = plain.rope(plain.rmsnorm(k, w[p + "self_attn.k_norm.weight"], d["eps"]), pos, d["theta"])
+        o = plain.attention(q, k, v, d["head_dim"] ** -0.5).reshape(t, -1) @ w[p + "self_attn.o_proj.weight"].T
+        x = x + o
+        hn2 = plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], d["eps"])
+        return x + plain.swiglu(hn2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                w[p + "mlp.down_proj.weight"]), hn
+
+    x = plain.embedding(tokens, w["model.embed_tokens.weight"])
+    x, first_normed = attn_layer(x)
+    p = "model.layers.1."
+    hn = plain.rmsnorm(x, w[p + "input_layernorm.weight"], d["eps"])
+    y = hn @ w[p + "self_attn.proj.weight"].T
+    x = x + torch.cumsum(y, 0) / torch.arange(1, t + 1, dtype=x.dtype)[:, None]
+    hn = plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], d["eps"])
+    x = x + plain.swiglu(hn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    x, _ = attn_layer(x)
+    x, _ = attn_layer(x, kv_from=first_normed)          # reads the keys and values of the first run
+    x = plain.rmsnorm(x, w["model.norm.weight"], d["eps"])
+    return x @ w["model.embed_tokens.weight"].T
+
+
+def run_toy(tmp_path, device, dtype_name):
+    from tinyinfer_b200.engine.replay import TraceSession
+    from tinyinfer_b200.config import load_config
+    from tinyinfer_b200.weights import load_weights, write_random_model
+    folder = write_random_model(tmp_path / "toy", ToyConfig(TOY), seed=11, std=0.08)
+    assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyForCausalLM"]
+    arch, cfg = load_config(folder)
+    model = arch.model_factory(cfg, torch.float32, torch.device(device))
+    load_weights(model, folder)
+    needs = model.cache_needs()
+    assert needs[1][0] is None and needs[1][1].shape == (48,) and needs[0][0].num_kv_heads == 1
+    _, w = plain.read_model_folder(folder, torch.float64)
+    requests = helpers.random_requests(dict(vocab_size=97), [40, 9, 70, 33, 2, 50], seed=2)
+    want = {rid: toy_plain(w, toks).numpy() for rid, toks in requests.items()}
+    for steps in (helpers.trace_whole(requests), helpers.trace_chunked(requests, seed=4),
+                  helpers.trace_mixed(requests, seed=5, max_live=3)):
+        # three state slots for six requests: slots are used again and must start from zero
+        session = TraceSession(None, dtype_name, helpers.peak_tokens(steps), page_size=8, model=model,
+                               max_live=3, poison_cache=True)
+        got = helpers.collect(session, steps)
+        assert helpers.first_bad(got, want, 5e-5) is None
+        session.runner.manager.check_consistency()
+
+
+@pytest.mark.gpu
+def test_toy_architecture_steps_on_the_gpu(tmp_path):
+    run_toy(tmp_path, "cuda:0", "float32")
+
+
+def test_toy_architecture_steps_with_plain_ops(tmp_path, monkeypatch):
+    from tinyinfer_b200 import ops
+    for name in torch_ops.ALL:
+        monkeypatch.setattr(ops, name, getattr(torch_ops, name))
+    run_toy(tmp_path, "cpu", "float32")

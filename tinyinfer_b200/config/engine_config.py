@@ -10,6 +10,7 @@ from typing import Optional
 class EngineConfig:
     max_num_batched_tokens: int = 4096      # token budget of one step
     max_num_seqs: int = 64                  # requests in one step
+    max_live_requests: int = 0              # requests that hold cache at a time; 0: 4 x max_num_seqs
     max_model_len: int = 4096               # prompt + completion of one request
     gpu_memory_utilization: float = 0.90    # share of device memory the engine may take
     kvcache_block_size: int = 64            # tokens in a page (the reference's default is 256)
@@ -34,10 +35,17 @@ class EngineConfig:
             raise ValueError("kvcache_block_size must be positive")
         if self.num_kvcache_blocks < 0:
             raise ValueError("num_kvcache_blocks must not be negative")
+        if self.max_live_requests < 0:
+            raise ValueError("max_live_requests must not be negative")
         if self.prefill_chunk < 0:
             raise ValueError("prefill_chunk must not be negative")
         if self.dtype not in ("bfloat16", "float32"):
             raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {self.dtype!r}")
+
+
+    @property
+    def live_requests(self) -> int:
+        return self.max_live_requests if self.max_live_requests > 0 else 4 * self.max_num_seqs
 
 
 def parse_dtype(name: Optional[str]) -> str:

@@ -55,7 +55,8 @@ class LLM:
                 raise RuntimeError("no device memory left for the cache")
             self.config.num_kvcache_blocks = num_pages
         self.runner = ModelRunner(
-            self.model, page_size=page, num_pages=num_pages, max_requests=self.config.max_num_seqs,
+            self.model, page_size=page, num_pages=num_pages, max_requests=self.config.live_requests,
+            max_seqs_per_step=self.config.max_num_seqs,
             max_tokens_per_step=self.config.max_num_batched_tokens,
             max_model_len=self.config.max_model_len)
         eos = self.config.eos_token_id

@@ -19,7 +19,10 @@ from .batch import BatchBuffers, CacheView, StepContext, StepEntry
 
 class ModelRunner:
     def __init__(self, model, *, page_size: int, num_pages: int, max_requests: int,
-                 max_tokens_per_step: int, max_model_len: int, poison_cache: bool = False):
+                 max_tokens_per_step: int, max_model_len: int, max_seqs_per_step: int = 0,
+                 poison_cache: bool = False):
+        """``max_requests``: requests that may hold cache at a time (state slots);
+        ``max_seqs_per_step``: requests in one step (0: the same)."""
         self.model = model
         self.device = model.device
         needs = model.cache_needs()
@@ -27,7 +30,8 @@ class ModelRunner:
         self.storage = CacheStorage(needs, self.manager, model.dtype, self.device, poison=poison_cache)
         self.max_model_len = max_model_len
         max_blocks = (max_model_len + page_size - 1) // page_size
-        self.buffers = BatchBuffers(self.device, max_tokens_per_step, max_requests, max_blocks,
+        self.buffers = BatchBuffers(self.device, max_tokens_per_step,
+                                    max_seqs_per_step or max_requests, max_blocks,
                                     max(1, len(self.manager.groups)))
         self.steps_run = 0
 
