@@ -76,6 +76,7 @@ class BatchBuffers:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
         self._copy_pending = False
+        self.bytes_copied = 0              # host-to-device bytes of all steps so far
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
               tables: Sequence[Sequence[Sequence[int]]]) -> StepContext:
@@ -128,6 +129,7 @@ class BatchBuffers:
             self._copied.synchronize()
         self.host[:n] = torch.tensor(flat, dtype=torch.int32)
         self.dev[:n].copy_(self.host[:n], non_blocking=True)
+        self.bytes_copied += 4 * n
         if self._copied is not None:
             self._copied.record()
             self._copy_pending = True
