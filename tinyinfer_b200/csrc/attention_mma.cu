@@ -1,0 +1,576 @@
+// bfloat16 paged attention on tensor cores for head sizes 64 and 128: a split-KV kernel for single
+// decoded tokens (FlashDecoding: tinyinfer/csrc/flash_decoding.cu:17-336 of the reference, here
+// batched over requests in ONE launch, with the query heads of a kv head sharing one read of its
+// keys and values) and a causal kernel for portions of prompts that reads the cached prefix
+// through the block table (tinyinfer/csrc/flash_attention.cu:5-234 plus the gather the reference
+// does on the host, tinyinfer/layers/attention.py:60-81).
+//
+// Keys and values come straight from the pages: a warp of its own issues TMA tile copies
+// (64 keys x 64 features, 128-byte swizzle) into a 3-stage ring guarded by mbarriers; four warps
+// consume them with ldmatrix + mma.sync.m16n8k16 (bf16 in, float32 out). Scores, running maximum
+// (from -inf), sums and outputs are float32; probabilities are rounded to bfloat16 for the second
+// product. Masked scores are assigned -inf (never added), and value rows that no query of the CTA
+// may see are zeroed in shared memory, so stale or unwritten pages cannot leak NaNs.
+//
+// The decode split is by position only (256 keys per split), so a request's result does not depend
+// on what else is in the batch. Partial results (unnormalised output, maximum, sum per split) go
+// to float32 scratch and a second kernel merges them.
+#include "sm100_ptx.cuh"
+
+namespace {
+
+constexpr int TK = 64;            // keys per tile
+constexpr int CHUNK = 256;        // keys per decode split
+constexpr int STAGES = 3;
+constexpr int CONSUMER_THREADS = 128;
+constexpr int THREADS = CONSUMER_THREADS + 32;
+
+struct AttnParams {
+    __nv_bfloat16* out;            // [T, Hq * D]
+    const __nv_bfloat16* q;        // [T, Hq, D]
+    float* part_o;                 // decode: [rows][Hq][max_splits][D]
+    float* part_ml;                // decode: [rows][Hq][max_splits][2]
+    const int* rows;               // decode: flat token rows; prefill: tiles as int4 {seq, row0, nrows, pos0}
+    const int* positions;
+    const int* token_seq;
+    const int* block_table;
+    int max_blocks, hq, hkv, page_size, num_pages, window, max_splits;
+    float scale_log2;              // softmax scale times log2(e)
+    int* status;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// Byte offset of (row, 16-byte chunk) inside a tile of 64-feature halves, each [TK][128 B] swizzled.
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * (TK * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+template <int D>
+struct Smem {
+    static constexpr int HALVES = D / 64;
+    static constexpr int TILE_BYTES = HALVES * TK * 128;      // keys OR values of one tile
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int BYTES = 1024 + STAGES * STAGE_BYTES + 128;
+};
+
+// Issues the copies of tile `t` (keys t*TK .. t*TK+63 of the request) into a stage. Pieces whose
+// page the request does not hold (never written, or given back by a window) are skipped.
+template <int D>
+__device__ __forceinline__ void load_tile(const CUtensorMap* map, const AttnParams& p, const int* table, int kvh,
+                                          int t, uint32_t stage_addr, uint32_t bar) {
+    using S = Smem<D>;
+    const int piece_rows = p.page_size < TK ? p.page_size : TK;
+    const int pieces = TK / piece_rows;
+    int pages[4];                                   // page_size >= 16, so at most four pieces
+    uint32_t bytes = 0;
+    for (int i = 0; i < pieces; ++i) {
+        const int tok = t * TK + i * piece_rows;
+        const int logical = tok / p.page_size;
+        int page = logical < p.max_blocks ? table[logical] : -1;
+        if (page >= p.num_pages) page = -1;
+        pages[i] = page;
+        if (page >= 0) bytes += (uint32_t)piece_rows * 128u * S::HALVES * 2u;
+    }
+    mbar_expect_tx(bar, bytes);
+    for (int i = 0; i < pieces; ++i) {
+        if (pages[i] < 0) continue;
+        const int tok = t * TK + i * piece_rows;
+        const int off = tok % p.page_size;
+        const int krow = (pages[i] * p.hkv + kvh) * p.page_size + off;
+        const int vrow = ((p.num_pages + pages[i]) * p.hkv + kvh) * p.page_size + off;
+#pragma unroll
+        for (int hh = 0; hh < S::HALVES; ++hh) {
+            const uint32_t dst = stage_addr + hh * (TK * 128) + i * piece_rows * 128;
+            tma_load_2d(dst, map, bar, hh * 64, krow);
+            tma_load_2d(dst + S::TILE_BYTES, map, bar, hh * 64, vrow);
+        }
+    }
+}
+
+// Zeroes the value rows of a tile outside [keep_lo, keep_hi) (tile-local key indices): no query of
+// this CTA may see them and what the stage holds there may be stale or unwritten. Called by the
+// `nthreads` threads that will read the tile, `tid` being the caller's index among them.
+template <int D>
+__device__ __forceinline__ void zero_value_rows(uint8_t* v_tile, int keep_lo, int keep_hi, int tid, int nthreads,
+                                                int row_begin, int row_end) {
+    constexpr int CHUNKS = D / 8;
+    for (int idx = tid; idx < (row_end - row_begin) * CHUNKS; idx += nthreads) {
+        const int row = row_begin + idx / CHUNKS, chunk = idx % CHUNKS;
+        if (row >= keep_lo && row < keep_hi) continue;
+        *reinterpret_cast<uint4*>(v_tile + tile_off(row, chunk)) = make_uint4(0, 0, 0, 0);
+    }
+}
+
+// ------------------------------------------------------------------------------------ decode
+template <int D>
+__global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
+                                                                   const AttnParams p) {
+    using S = Smem<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+    const uint32_t bar0 = smem_u32(bars);
+    __shared__ int abort_sh;
+    volatile int* abort_flag = &abort_sh;
+
+    const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+    const int row = p.rows[r];
+    const int ctx = p.positions[row] + 1;
+    const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int k_begin = max(split * CHUNK, lo), k_end = min(ctx, (split + 1) * CHUNK);
+    if (k_begin >= k_end) return;                       // this split holds no visible key
+    const int* table = p.block_table + (size_t)p.token_seq[row] * p.max_blocks;
+    const int tile0 = k_begin / TK, tile1 = (k_end + TK - 1) / TK;
+    const int group = p.hq / p.hkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        abort_sh = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(bar0 + 8u * s, 1); mbar_init(bar0 + 8u * (STAGES + s), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int t = tile0; t < tile1; ++t, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(bar0 + 8u * (STAGES + s), ((it / STAGES) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+                load_tile<D>(&kv_map, p, table, kvh, t, smem_u32(smem + s * S::STAGE_BYTES), bar0 + 8u * s);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers: the 16 rows of the MMA are the query heads of this kv head (rows >= group are zero)
+    const int g = lane >> 2, c = (lane & 3) * 2;
+    uint32_t qa[D / 16][4];
+    {
+        const __nv_bfloat16* q0 = p.q + ((size_t)row * p.hq + (size_t)kvh * group) * D;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qa[ks][0] = g < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + ks * 16 + c) : 0u;
+            qa[ks][1] = g + 8 < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + ks * 16 + c) : 0u;
+            qa[ks][2] = g < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + ks * 16 + c + 8) : 0u;
+            qa[ks][3] = g + 8 < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + ks * 16 + c + 8) : 0u;
+        }
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int id = lane >> 3, rr = lane & 7;
+    bool ok = true;
+
+    uint32_t it = 0;
+    for (int t = tile0; t < tile1; ++t, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(bar0 + 8u * s, (it / STAGES) & 1u, abort_flag, p.status, 22)) { ok = false; break; }
+        uint8_t* k_tile = smem + s * S::STAGE_BYTES;
+        uint8_t* v_tile = k_tile + S::TILE_BYTES;
+        const int w0 = warp * 16;                         // this warp's 16 keys of the tile
+        const int tok0 = t * TK + w0;
+        if (tok0 < k_end && tok0 + 16 > k_begin) {
+            float sc[2][4] = {};
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t b[4];
+                const int krow = w0 + (id >> 1) * 8 + rr;
+                ldmatrix_x4(b, smem_u32(k_tile) + tile_off(krow, ks * 2 + (id & 1)));
+                mma_bf16(sc[0], qa[ks], b[0], b[1]);
+                mma_bf16(sc[1], qa[ks], b[2], b[3]);
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int tok = tok0 + nb * 8 + c + (j & 1);
+                    const float v = (tok >= k_begin && tok < k_end) ? sc[nb][j] * p.scale_log2 : -INFINITY;
+                    sc[nb][j] = v;
+                    mx[j >> 1] = fmaxf(mx[j >> 1], v);
+                }
+            float corr[2], m_use[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_run[h], mx[h]);
+                m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+                corr[h] = exp2f(m_run[h] - m_use[h]);
+                m_run[h] = m_new;
+                l_run[h] *= corr[h];
+            }
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float pv = exp2f(sc[nb][j] - m_use[j >> 1]);
+                    sc[nb][j] = pv;
+                    l_run[j >> 1] += pv;
+                }
+            uint32_t pa[4] = {pack_bf16(sc[0][0], sc[0][1]), pack_bf16(sc[0][2], sc[0][3]),
+                              pack_bf16(sc[1][0], sc[1][1]), pack_bf16(sc[1][2], sc[1][3])};
+            if (tok0 < k_begin || tok0 + 16 > k_end) {    // warp-local: only this warp reads these rows
+                zero_value_rows<D>(v_tile, k_begin - t * TK, k_end - t * TK, lane, 32, w0, w0 + 16);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // a later TMA copy overwrites these rows
+                __syncwarp();
+            }
+#pragma unroll
+            for (int nb = 0; nb < D / 8; nb += 2) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    o[nb][j] *= corr[j >> 1];
+                    o[nb + 1][j] *= corr[j >> 1];
+                }
+                uint32_t b[4];
+                const int vrow = w0 + (id & 1) * 8 + rr;
+                ldmatrix_x4_trans(b, smem_u32(v_tile) + tile_off(vrow, nb + (id >> 1)));
+                mma_bf16(o[nb], pa, b[0], b[1]);
+                mma_bf16(o[nb + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8u * (STAGES + s));
+    }
+
+    // ---- merge the four warps (each saw a quarter of the keys) and write the split's partial
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");       // every consumer is done with the stages
+    if (!ok) return;
+    float* mbuf = reinterpret_cast<float*>(smem);         // [4 warps][16 rows][D + 2]
+    constexpr int LD = D + 2;
+#pragma unroll
+    for (int nb = 0; nb < D / 8; ++nb) {
+        float* base = mbuf + ((size_t)warp * 16) * LD + nb * 8 + c;
+        base[(size_t)g * LD] = o[nb][0];
+        base[(size_t)g * LD + 1] = o[nb][1];
+        base[(size_t)(g + 8) * LD] = o[nb][2];
+        base[(size_t)(g + 8) * LD + 1] = o[nb][3];
+    }
+    if ((lane & 3) == 0) {
+        mbuf[((size_t)warp * 16 + g) * LD + D] = m_run[0];
+        mbuf[((size_t)warp * 16 + g) * LD + D + 1] = l_run[0];
+        mbuf[((size_t)warp * 16 + g + 8) * LD + D] = m_run[1];
+        mbuf[((size_t)warp * 16 + g + 8) * LD + D + 1] = l_run[1];
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    for (int idx = threadIdx.x; idx < group * D; idx += CONSUMER_THREADS) {
+        const int hrow = idx / D, d = idx % D;
+        float mw[4], m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { mw[w] = mbuf[((size_t)w * 16 + hrow) * LD + D]; m_all = fmaxf(m_all, mw[w]); }
+        const float m_use = m_all == -INFINITY ? 0.f : m_all;
+        float acc = 0.f, l_all = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(mw[w] - m_use);
+            acc += f * mbuf[((size_t)w * 16 + hrow) * LD + d];
+            l_all += f * mbuf[((size_t)w * 16 + hrow) * LD + D + 1];
+        }
+        const size_t slot = ((size_t)r * p.hq + (size_t)kvh * group + hrow) * p.max_splits + split;
+        p.part_o[slot * D + d] = acc;
+        if (d == 0) { p.part_ml[slot * 2] = m_all; p.part_ml[slot * 2 + 1] = l_all; }
+    }
+}
+
+// One block per (decode row, query head): merges the splits that hold visible keys.
+template <int D>
+__global__ void decode_merge_kernel(const AttnParams p) {
+    const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    const int row = p.rows[r];
+    const int ctx = p.positions[row] + 1;
+    const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int s0 = lo / CHUNK, s1 = (ctx - 1) / CHUNK;
+    const size_t base = ((size_t)r * p.hq + h) * p.max_splits;
+    float m_all = -INFINITY;
+    for (int s = s0; s <= s1; ++s) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
+    const float m_use = m_all == -INFINITY ? 0.f : m_all;
+    float acc = 0.f, l_all = 0.f;
+    for (int s = s0; s <= s1; ++s) {
+        const float f = exp2f(p.part_ml[(base + s) * 2] - m_use);
+        acc += f * p.part_o[(base + s) * D + d];
+        l_all += f * p.part_ml[(base + s) * 2 + 1];
+    }
+    p.out[((size_t)row * p.hq + h) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+}
+
+// ------------------------------------------------------------------------------------ prefill
+// One CTA per (tile of up to 64 consecutive query tokens of one request, query head); warp w owns
+// query rows 16w .. 16w+15 of the tile.
+template <int D>
+__global__ void __launch_bounds__(THREADS) prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
+                                                                    const AttnParams p) {
+    using S = Smem<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+    const uint32_t bar0 = smem_u32(bars);
+    __shared__ int abort_sh;
+    volatile int* abort_flag = &abort_sh;
+
+    const int4 td = reinterpret_cast<const int4*>(p.rows)[blockIdx.x];
+    const int seq = td.x, row0 = td.y, nrows = td.z, pos0 = td.w;
+    const int head = blockIdx.y;
+    const int kvh = head / (p.hq / p.hkv);
+    const int hi = pos0 + nrows;                                   // one past the last key any query sees
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0; // first key the first query sees
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+    const int tile0 = lo / TK, tile1 = (hi + TK - 1) / TK;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        abort_sh = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(bar0 + 8u * s, 1); mbar_init(bar0 + 8u * (STAGES + s), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int t = tile0; t < tile1; ++t, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(bar0 + 8u * (STAGES + s), ((it / STAGES) & 1u) ^ 1u, abort_flag, p.status, 23)) break;
+                load_tile<D>(&kv_map, p, table, kvh, t, smem_u32(smem + s * S::STAGE_BYTES), bar0 + 8u * s);
+            }
+        }
+        return;
+    }
+
+    const int g = lane >> 2, c = (lane & 3) * 2;
+    const int lr0 = warp * 16 + g, lr1 = lr0 + 8;                  // this thread's two query rows (tile-local)
+    const int qpos0 = pos0 + lr0, qpos1 = pos0 + lr1;
+    const int warp_qmin = pos0 + warp * 16, warp_qmax = min(pos0 + warp * 16 + 15, hi - 1);
+    const bool warp_active = warp * 16 < nrows;
+    uint32_t qa[D / 16][4];
+    {
+        const __nv_bfloat16* q0 = p.q + ((size_t)(row0 + lr0) * p.hq + head) * D;
+        const __nv_bfloat16* q1 = p.q + ((size_t)(row0 + lr1) * p.hq + head) * D;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qa[ks][0] = lr0 < nrows ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c) : 0u;
+            qa[ks][1] = lr1 < nrows ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c) : 0u;
+            qa[ks][2] = lr0 < nrows ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c + 8) : 0u;
+            qa[ks][3] = lr1 < nrows ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c + 8) : 0u;
+        }
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int id = lane >> 3, rr = lane & 7;
+    bool ok = true;
+
+    uint32_t it = 0;
+    for (int t = tile0; t < tile1; ++t, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(bar0 + 8u * s, (it / STAGES) & 1u, abort_flag, p.status, 24)) { ok = false; break; }
+        uint8_t* k_tile = smem + s * S::STAGE_BYTES;
+        uint8_t* v_tile = k_tile + S::TILE_BYTES;
+        const int tk0 = t * TK;
+        if (tk0 < lo || tk0 + TK > hi) {                  // CTA-uniform: the first or the last tile
+            zero_value_rows<D>(v_tile, lo - tk0, hi - tk0, threadIdx.x, CONSUMER_THREADS, 0, TK);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // a later TMA copy overwrites these rows
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        // a warp whose queries all lie before the tile, or whose windows all ended before it, skips it
+        const bool sees = warp_active && tk0 <= warp_qmax && (p.window == 0 || tk0 + TK - 1 > warp_qmin - p.window);
+        if (sees) {
+            float sc[TK / 8][4];
+#pragma unroll
+            for (int nb = 0; nb < TK / 8; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+                for (int np = 0; np < TK / 16; ++np) {
+                    uint32_t b[4];
+                    const int krow = np * 16 + (id >> 1) * 8 + rr;
+                    ldmatrix_x4(b, smem_u32(k_tile) + tile_off(krow, ks * 2 + (id & 1)));
+                    mma_bf16(sc[2 * np], qa[ks], b[0], b[1]);
+                    mma_bf16(sc[2 * np + 1], qa[ks], b[2], b[3]);
+                }
+            }
+            const bool need_mask = tk0 + TK - 1 > warp_qmin || (p.window > 0 && tk0 <= warp_qmax - p.window);
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nb = 0; nb < TK / 8; ++nb)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float v = sc[nb][j] * p.scale_log2;
+                    if (need_mask) {
+                        const int tok = tk0 + nb * 8 + c + (j & 1);
+                        const int qp = (j >> 1) ? qpos1 : qpos0;
+                        const bool keep = tok <= qp && (p.window == 0 || tok > qp - p.window);
+                        v = keep ? v : -INFINITY;
+                    }
+                    sc[nb][j] = v;
+                    mx[j >> 1] = fmaxf(mx[j >> 1], v);
+                }
+            float corr[2], m_use[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_run[h], mx[h]);
+                m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+                corr[h] = exp2f(m_run[h] - m_use[h]);
+                m_run[h] = m_new;
+                l_run[h] *= corr[h];
+            }
+#pragma unroll
+            for (int nb = 0; nb < TK / 8; ++nb)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float pv = exp2f(sc[nb][j] - m_use[j >> 1]);
+                    sc[nb][j] = pv;
+                    l_run[j >> 1] += pv;
+                }
+#pragma unroll
+            for (int nb = 0; nb < D / 8; ++nb)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o[nb][j] *= corr[j >> 1];
+#pragma unroll
+            for (int kk = 0; kk < TK / 16; ++kk) {
+                const uint32_t pa[4] = {pack_bf16(sc[2 * kk][0], sc[2 * kk][1]), pack_bf16(sc[2 * kk][2], sc[2 * kk][3]),
+                                        pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]),
+                                        pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3])};
+#pragma unroll
+                for (int nb = 0; nb < D / 8; nb += 2) {
+                    uint32_t b[4];
+                    const int vrow = kk * 16 + (id & 1) * 8 + rr;
+                    ldmatrix_x4_trans(b, smem_u32(v_tile) + tile_off(vrow, nb + (id >> 1)));
+                    mma_bf16(o[nb], pa, b[0], b[1]);
+                    mma_bf16(o[nb + 1], pa, b[2], b[3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8u * (STAGES + s));
+    }
+    if (!ok) return;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+    __nv_bfloat16* out0 = p.out + ((size_t)(row0 + lr0) * p.hq + head) * D;
+    __nv_bfloat16* out1 = p.out + ((size_t)(row0 + lr1) * p.hq + head) * D;
+#pragma unroll
+    for (int nb = 0; nb < D / 8; ++nb) {
+        if (lr0 < nrows) *reinterpret_cast<uint32_t*>(out0 + nb * 8 + c) = pack_bf16(o[nb][0] * inv0, o[nb][1] * inv0);
+        if (lr1 < nrows) *reinterpret_cast<uint32_t*>(out1 + nb * 8 + c) = pack_bf16(o[nb][2] * inv1, o[nb][3] * inv1);
+    }
+}
+
+template <typename K>
+int set_smem(K kernel, int bytes, const char* name) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) { ti_set_error("%s: cannot get %d bytes of shared memory: %s", name, bytes, cudaGetErrorString(e)); return (int)e; }
+    return 0;
+}
+
+int check_shape(int hq, int hkv, int d, int page_size, const char* name) {
+    TI_REQUIRE(d == 64 || d == 128, "%s: head_dim %d is not 64 or 128", name, d);
+    TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0 && hq / hkv <= 16, "%s: %d query heads over %d kv heads (at most 16 per kv head)", name, hq, hkv);
+    TI_REQUIRE(page_size >= 16 && ((page_size < TK && TK % page_size == 0) || page_size % TK == 0),
+               "%s: page size %d must be 16, 32 or a multiple of 64", name, page_size);
+    return 0;
+}
+
+}  // namespace
+
+// 1 if the tensor-core attention kernels take these sizes.
+TI_API int ti_attention_bf16_supported(int hq, int hkv, int d, int page_size) {
+    return (d == 64 || d == 128) && hq > 0 && hkv > 0 && hq % hkv == 0 && hq / hkv <= 16 && page_size >= 16 &&
+           ((page_size < TK && TK % page_size == 0) || page_size % TK == 0) ? 1 : 0;
+}
+TI_API int ti_attention_decode_chunk() { return CHUNK; }
+TI_API int ti_attention_prefill_tile() { return TK; }
+
+// Decode: `rows` lists the flat rows of the step whose request brings exactly one token.
+// Scratch: part_o float32 [num_rows * hq * max_splits * d], part_ml float32 [num_rows * hq * max_splits * 2];
+// max_splits >= ceil(longest context / 256). Calls that share the scratch must not overlap.
+TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cache, float* part_o, float* part_ml,
+                                    const int* rows, int num_rows, const int* positions, const int* token_seq,
+                                    const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,
+                                    int num_pages, float scale, int window, int max_splits, int* status,
+                                    cudaStream_t stream) {
+    if (check_shape(hq, hkv, d, page_size, "attention_decode")) return -1;
+    TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && max_splits > 0 && max_splits <= 65535, "attention_decode: bad sizes");
+    if (num_rows == 0) return 0;
+    CUtensorMap map;
+    if (!ti_get_bf16_map(kv_cache, 2ll * num_pages * hkv * page_size, d, page_size < TK ? page_size : TK, &map)) return -1;
+    AttnParams p;
+    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q; p.part_o = part_o; p.part_ml = part_ml;
+    p.rows = rows; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
+    p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
+    p.window = window; p.max_splits = max_splits; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    dim3 grid(max_splits, hkv, num_rows);
+    if (d == 128) {
+        static bool once = false;
+        if (!once) { if (set_smem(decode_attention_kernel<128>, Smem<128>::BYTES, "attention_decode")) return -1; once = true; }
+        decode_attention_kernel<128><<<grid, THREADS, Smem<128>::BYTES, stream>>>(map, p);
+        TI_CHECK_LAUNCH("attention_decode");
+        decode_merge_kernel<128><<<dim3(num_rows, hq), 128, 0, stream>>>(p);
+    } else {
+        static bool once = false;
+        if (!once) { if (set_smem(decode_attention_kernel<64>, Smem<64>::BYTES, "attention_decode")) return -1; once = true; }
+        decode_attention_kernel<64><<<grid, THREADS, Smem<64>::BYTES, stream>>>(map, p);
+        TI_CHECK_LAUNCH("attention_decode");
+        decode_merge_kernel<64><<<dim3(num_rows, hq), 64, 0, stream>>>(p);
+    }
+    TI_CHECK_LAUNCH("attention_decode_merge");
+    return 0;
+}
+
+// Prefill: `tiles` holds num_tiles int4 {request index in the step, first flat row, rows (<= 64),
+// position of the first row}; every tile lies inside one request's portion.
+TI_API int ti_attention_prefill_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
+                                     const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,
+                                     int num_pages, float scale, int window, int* status, cudaStream_t stream) {
+    if (check_shape(hq, hkv, d, page_size, "attention_prefill")) return -1;
+    TI_REQUIRE(num_tiles >= 0 && hq <= 65535, "attention_prefill: bad sizes");
+    if (num_tiles == 0) return 0;
+    CUtensorMap map;
+    if (!ti_get_bf16_map(kv_cache, 2ll * num_pages * hkv * page_size, d, page_size < TK ? page_size : TK, &map)) return -1;
+    AttnParams p;
+    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q; p.part_o = nullptr; p.part_ml = nullptr;
+    p.rows = tiles; p.positions = nullptr; p.token_seq = nullptr; p.block_table = block_table;
+    p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
+    p.window = window; p.max_splits = 0; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    dim3 grid(num_tiles, hq);
+    if (d == 128) {
+        static bool once = false;
+        if (!once) { if (set_smem(prefill_attention_kernel<128>, Smem<128>::BYTES, "attention_prefill")) return -1; once = true; }
+        prefill_attention_kernel<128><<<grid, THREADS, Smem<128>::BYTES, stream>>>(map, p);
+    } else {
+        static bool once = false;
+        if (!once) { if (set_smem(prefill_attention_kernel<64>, Smem<64>::BYTES, "attention_prefill")) return -1; once = true; }
+        prefill_attention_kernel<64><<<grid, THREADS, Smem<64>::BYTES, stream>>>(map, p);
+    }
+    TI_CHECK_LAUNCH("attention_prefill");
+    return 0;
+}

@@ -16,8 +16,8 @@
 //
 // Every wait on an mbarrier is bounded; a wait that runs out sets *status, raises the CTA's abort
 // flag, and all warps fall through to the common exit, where tensor memory is freed.
-#include "common.cuh"
-#include <cuda.h>
+#include "sm100_ptx.cuh"
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -28,7 +28,6 @@ constexpr int BK = 64;           // bf16 elements per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BUDGET = 200 * 1024;
-constexpr unsigned long long WAIT_NS = 2000000000ull;   // a wait gives up after two seconds
 
 struct GemmParams {
     void* out;
@@ -38,52 +37,12 @@ struct GemmParams {
     int rows_total;         // extent of the rows operand that tiles walk over
     int cols_total;         // extent of the cols operand
     int gated, out_f32, swap;
+    int splits;             // swapped only: the k range of a tile is cut into this many work units
+    float* partials;        // [tile][split][col][128] float32 scratch for splits > 1
+    int* counters;          // [tile] arrivals; zero before the launch and again after it
     int* status;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait. Returns false if the CTA is aborting or the wait ran out (then it raises the abort).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    for (uint32_t i = 1;; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 0u) {
-            if (*abort_flag) return false;
-            if (global_ns() - t0 > WAIT_NS) {
-                *abort_flag = 1;
-                if (status) atomicExch(status, code);
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
 // Shared-memory operand descriptor: K-major tile of rows x 64 bf16, 128-byte swizzle; rows are
 // 128 bytes apart, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
@@ -127,7 +86,7 @@ struct Cfg {
     static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
     static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;        // two accumulators; a power of two
-    static constexpr int EXCH_FLOATS = 64 * (BN + 1);                   // swapped gated epilogue only
+    static constexpr int EXCH_FLOATS = BN <= 64 ? 64 * (BN + 1) + 2 : 2;   // swapped gated epilogue (BN <= 64) + one word
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EXCH_FLOATS * 4 + 256;
 };
 
@@ -159,6 +118,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     const int col_tiles = (p.cols_total + cols_per_tile - 1) / cols_per_tile;
     const int num_tiles = row_tiles * col_tiles;
     const int num_kb = (p.K + BK - 1) / BK;
+    const int num_units = num_tiles * p.splits;     // unit = tile * splits + split: a tile's splits run side by side
 
     if (threadIdx.x == 0) {
         abort_sh = 0;
@@ -181,10 +141,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+                const int tile = unit / p.splits, split = unit % p.splits;
                 const int rt = tile % row_tiles, ct = tile / row_tiles;
                 const int r0 = rt * rows_per_tile, c0 = ct * cols_per_tile;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int kb0 = (int)((long long)split * num_kb / p.splits);
+                const int kb1 = (int)((long long)(split + 1) * num_kb / p.splits);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
@@ -205,15 +168,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     }
                 }
             }
-            // On the way out no copy of this CTA may still be in flight: every stage it armed is
-            // either consumed (normal end: the MMA warp waited on it) or awaited here, bounded.
+            // After an abort, give the copies this CTA still has in flight time to land (they take
+            // microseconds) before shared memory is given up: a bounded wait of one millisecond.
             if (!ok) {
-                for (int s = 0; s < C::STAGES; ++s) {
-                    const unsigned long long t0 = global_ns();
-                    const uint32_t armed = it > (uint32_t)s ? ((it - 1 - s) / C::STAGES) & 1u : 2u;
-                    if (armed == 2u) continue;
-                    while (!mbar_try_wait(full_bar((it - 1 - s) % C::STAGES), armed) && global_ns() - t0 < 1000000ull) {}
-                }
+                const unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 1000000ull) {}
             }
         }
     } else if (warp == 1) {
@@ -222,12 +181,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             constexpr uint32_t idesc = make_idesc(BM, BN);
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++tile_i) {
+                const int split = unit % p.splits;
+                const int kb0 = (int)((long long)split * num_kb / p.splits);
+                const int kb1 = (int)((long long)(split + 1) * num_kb / p.splits);
                 const uint32_t as = tile_i & 1u, aph = (tile_i >> 1) & 1u;
                 if (!mbar_wait(acc_empty_bar(as), aph ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
                 tmem_fence_after();
                 const uint32_t d_tmem = tmem_base + as * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1u;
                     if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, 13)) { ok = false; break; }
@@ -238,7 +200,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // 16 bf16 = 32 bytes along K inside the 128-byte swizzled row: +2 in 16-byte units
-                        umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));           // the stage is free once these MMAs have read it
                 }
@@ -251,7 +213,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         const int row_in_tile = lane_group * 32 + lane;
         uint32_t tile_i = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+        for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++tile_i) {
+            const int tile = unit / p.splits, split = unit % p.splits;
             const int rt = tile % row_tiles, ct = tile / row_tiles;
             const int r0 = rt * rows_per_tile, c0 = ct * cols_per_tile;
             const uint32_t as = tile_i & 1u, aph = (tile_i >> 1) & 1u;
@@ -259,6 +222,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             tmem_fence_after();
             const uint32_t t_addr = tmem_base + as * BN + ((uint32_t)(lane_group * 32) << 16);
             float v[16], u[16];
+            bool released = false;
+            // Split k range: every unit leaves its partial accumulator in scratch; the unit that
+            // arrives last sums all partials of the tile in split order (so the result does not
+            // depend on who was last) and runs the epilogue.
+            float* tile_partials = nullptr;
+            if (p.splits > 1) {
+                tile_partials = p.partials + (size_t)tile * p.splits * BN * BM;
+                float* mine = tile_partials + (size_t)split * BN * BM + row_in_tile;
+                for (int c = 0; c < BN; c += 16) {
+                    tmem_ld16(t_addr + c, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) __stcg(mine + (size_t)(c + i) * BM, v[i]);
+                }
+                tmem_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(as));
+                released = true;
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    const int arrived = atomicAdd(p.counters + tile, 1);
+                    if (arrived == p.splits - 1) p.counters[tile] = 0;     // leave the counter ready for the next launch
+                    *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]) = arrived;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int arrived = *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (arrived != p.splits - 1) continue;
+                __threadfence();
+            }
+            auto load_chunk = [&](int c, float* dst) {
+                if (p.splits > 1) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) dst[i] = 0.f;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float* src = tile_partials + (size_t)sp * BN * BM + row_in_tile;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) dst[i] += __ldcg(src + (size_t)(c + i) * BM);
+                    }
+                } else {
+                    tmem_ld16(t_addr + c, dst);
+                }
+            };
             if (!p.swap) {
                 const int m = r0 + row_in_tile;
                 const bool row_ok = m < p.M;
@@ -351,7 +357,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     const bool n_ok = n < p.N;
                     const float b = (p.bias && n_ok) ? p.bias[n] : 0.f;
                     for (int c = 0; c < BN; c += 16) {
-                        tmem_ld16(t_addr + c, v);
+                        load_chunk(c, v);
                         if (!n_ok) continue;
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
@@ -370,7 +376,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     const bool is_up = row_in_tile >= 64;
                     const int jj = row_in_tile & 63;
                     for (int c = 0; c < BN; c += 16) {
-                        tmem_ld16(t_addr + c, v);
+                        load_chunk(c, v);
                         if (is_up) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) exch[jj * (BN + 1) + c + i] = v[i];
@@ -392,9 +398,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     }
                 }
             }
-            tmem_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar(as));   // this half of tensor memory may be overwritten
+            if (!released) {
+                tmem_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(as));   // this half of tensor memory may be overwritten
+            }
         }
     }
 
@@ -408,66 +416,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 }
 
 // ---------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; int rows, k, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 1000003u ^ (size_t)k.k * 10007u ^ (size_t)k.box_rows;
+// How many work units to cut a tile's k range into, so that the units fill the SMs evenly:
+// a decode step is bound by how fast all SMs together can stream the weights, and 32 or 48 tiles
+// leave most of the 148 SMs idle. Needs scratch for the partial sums.
+int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int num_counters) {
+    if (tiles > num_counters) return 1;
+    if (const char* forced = getenv("TINYINFER_B200_GEMM_SPLITS")) {     // experiments only
+        const int s = atoi(forced);
+        if (s >= 1 && num_kb / s >= 1 && (long long)tiles * s * bn * BM <= workspace_floats) return s;
     }
-};
-
-// A tensor map of a row-major [rows, k] bf16 matrix, boxes of box_rows x 64, 128-byte swizzle.
-bool get_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    const MapKey key{ptr, rows, k, box_rows};
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return true; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) { ti_set_error("gemm_tcgen05: cuTensorMapEncodeTiled is not available from this driver"); return false; }
-    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUtensorMap m;
-    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { ti_set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (%d) for [%d, %d] box %d", (int)r, rows, k, box_rows); return false; }
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, m);
-    *out = m;
-    return true;
-}
-
-int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = ti_sm_count();
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= 8; ++s) {
+        if (s > 1 && (num_kb / s < 4 || (long long)tiles * s * bn * BM > workspace_floats)) break;
+        const long long units = (long long)tiles * s;
+        const double eff = (double)units / (double)(((units + sms - 1) / sms) * sms);
+        if (eff > best_eff + 0.04) { best_eff = eff; best = s; }
     }
-    return n;
+    return best;
 }
 
 template <int BN>
@@ -478,7 +445,8 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmP
         if (e != cudaSuccess) { ti_set_error("gemm_tcgen05: cannot get %d bytes of shared memory: %s", Cfg<BN>::SMEM_BYTES, cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
-    const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+    num_tiles *= p.splits;
+    const int grid = num_tiles < ti_sm_count() ? num_tiles : ti_sm_count();
     gemm_tcgen05_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(rows_map, cols_map, p);
     TI_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
@@ -491,8 +459,11 @@ TI_API int ti_gemm_bf16_supported(int M, int N, int K) { return (M > 0 && N > 0 
 
 // y = x . w^T in bfloat16 with float32 accumulation. gated: w is [2N, K] (gate rows, then up rows),
 // out [M, N] = silu(x.gate) * (x.up). out_f32: out is float32. status: device word set if a wait ran out.
+// workspace / counters: float32 scratch and zeroed int32 words for the split-k path of small M (may be
+// null: then no tile is split). Calls that share them must be ordered on one stream.
 TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bias, const void* residual,
-                        int M, int N, int K, int gated, int out_f32, int* status, cudaStream_t stream) {
+                        int M, int N, int K, int gated, int out_f32, float* workspace, long long workspace_floats,
+                        int* counters, int num_counters, int* status, cudaStream_t stream) {
     TI_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_bf16: bad sizes M=%d N=%d K=%d", M, N, K);
     TI_REQUIRE(K % 8 == 0, "gemm_bf16: K=%d is not a multiple of 8 (rows must start on 16-byte boundaries)", K);
     TI_REQUIRE(!(gated && (bias || residual || out_f32)), "gemm_bf16: the gated form takes no bias, residual or float32 output");
@@ -501,6 +472,7 @@ TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bi
     GemmParams p;
     p.out = out; p.bias = bias; p.residual = (const __nv_bfloat16*)residual;
     p.M = M; p.N = N; p.K = K; p.gated = gated; p.out_f32 = out_f32; p.status = status;
+    p.splits = 1; p.partials = workspace; p.counters = counters;
     const int w_rows = gated ? 2 * N : N;
     CUtensorMap rows_map, cols_map;
     if (M <= 64) {
@@ -508,24 +480,26 @@ TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bi
         p.swap = 1;
         p.rows_total = N; p.cols_total = M;
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-        if (!get_map(w, w_rows, K, gated ? BM / 2 : BM, &rows_map)) return -1;
-        if (!get_map(x, M, K, bn, &cols_map)) return -1;
+        if (!ti_get_bf16_map(w, w_rows, K, gated ? BM / 2 : BM, &rows_map)) return -1;
+        if (!ti_get_bf16_map(x, M, K, bn, &cols_map)) return -1;
         const int tiles = (N + (gated ? 64 : 128) - 1) / (gated ? 64 : 128);
+        if (workspace && counters)
+            p.splits = choose_splits(tiles, (K + BK - 1) / BK, bn, workspace_floats, num_counters);
         if (bn == 16) return launch<16>(rows_map, cols_map, p, tiles, stream);
         if (bn == 32) return launch<32>(rows_map, cols_map, p, tiles, stream);
         return launch<64>(rows_map, cols_map, p, tiles, stream);
     }
     p.swap = 0;
     p.rows_total = M; p.cols_total = N;
-    if (!get_map(x, M, K, BM, &rows_map)) return -1;
+    if (!ti_get_bf16_map(x, M, K, BM, &rows_map)) return -1;
     const int row_tiles = (M + BM - 1) / BM;
     const bool wide = (gated ? 2 * N : N) >= 256;
     if (wide) {
-        if (!get_map(w, w_rows, K, gated ? 128 : 256, &cols_map)) return -1;
+        if (!ti_get_bf16_map(w, w_rows, K, gated ? 128 : 256, &cols_map)) return -1;
         const int cpt = gated ? 128 : 256;
         return launch<256>(rows_map, cols_map, p, row_tiles * ((N + cpt - 1) / cpt), stream);
     }
-    if (!get_map(w, w_rows, K, gated ? 64 : 128, &cols_map)) return -1;
+    if (!ti_get_bf16_map(w, w_rows, K, gated ? 64 : 128, &cols_map)) return -1;
     const int cpt = gated ? 64 : 128;
     return launch<128>(rows_map, cols_map, p, row_tiles * ((N + cpt - 1) / cpt), stream);
 }

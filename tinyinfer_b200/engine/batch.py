@@ -53,6 +53,12 @@ class StepContext:
     starts: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_context: int = 0
+    # the attention kernels' split of the batch: rows of single decoded tokens, and tiles
+    # [entry, first row, rows, first position] of prompt portions
+    decode_rows: Optional[torch.Tensor] = None
+    num_decode: int = 0
+    prefill_tiles: Optional[torch.Tensor] = None
+    num_prefill_tiles: int = 0
     # filled by the runner: entry of the run order -> CacheView
     views: Dict[int, CacheView] = field(default_factory=dict)
 
@@ -70,7 +76,8 @@ class BatchBuffers:
         self.device = torch.device(device)
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
         self.max_blocks, self.num_groups = max_blocks, num_groups
-        words = 3 * max_tokens + 4 * max_seqs + 1 + max_tokens + num_groups * max_seqs * max_blocks + 64
+        words = (3 * max_tokens + 4 * max_seqs + 1 + max_tokens + num_groups * max_seqs * max_blocks
+                 + max_seqs + 4 * (max_tokens // 64 + max_seqs) + 128)
         self.host = torch.empty(words, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self.dev = torch.empty(words, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -117,6 +124,9 @@ class BatchBuffers:
 
         put("ids", ids); put("pos", pos); put("seq", seq); put("cu", cu)
         put("starts", list(starts)); put("ctx", ctx_lens); put("slots", list(slots)); put("rows", rows)
+        from ..ops import plan_attention
+        decode_rows, tiles = plan_attention(q_lens, starts)
+        put("dec", decode_rows); put("tiles", tiles)
         for g in range(self.num_groups):
             w = widths[g]
             padded: List[int] = []
@@ -145,4 +155,5 @@ class BatchBuffers:
             state_slots=view("slots"), logit_rows=view("rows"),
             block_tables=[view(f"bt{g}").view(s, widths[g]) for g in range(self.num_groups)],
             status=self.status, q_lens=q_lens, starts=list(starts), max_q_len=max(q_lens, default=0),
-            max_context=max(ctx_lens, default=0))
+            max_context=max(ctx_lens, default=0), decode_rows=view("dec"), num_decode=len(decode_rows),
+            prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4)

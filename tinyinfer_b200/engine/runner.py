@@ -95,6 +95,8 @@ class ModelRunner:
 
     def check_status(self) -> None:
         """Reads the word kernels set when they met an index without a page (synchronises)."""
+        from .. import ops
+        ops.check_kernel_status()
         code = int(self.buffers.status.item())
         if code:
             self.buffers.status.zero_()

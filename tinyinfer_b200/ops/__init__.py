@@ -41,7 +41,61 @@ _SIGNATURES = {
                       c_void_p, c_void_p, c_void_p],
     },
 }
+_SIGNATURES["sm100"] = {
+    "ti_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                     c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p],
+}
+_SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
+    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
+_SIGNATURES["sm100"]["ti_attention_prefill_bf16"] = [
+    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+    c_float, c_int, c_void_p, c_void_p]
+DECODE_CHUNK = 256        # keys per split of the decode attention kernel
+PREFILL_TILE = 64         # query rows per CTA of the prefill attention kernel
 _bound = {}
+_status = {}
+
+
+def kernel_status(device) -> torch.Tensor:
+    """The int32 device word that kernels with bounded waits set when a wait runs out."""
+    key = torch.device(device)
+    t = _status.get(key)
+    if t is None:
+        t = _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return t
+
+
+def check_kernel_status() -> None:
+    """Raises if any kernel reported a wait that ran out (synchronises)."""
+    for t in _status.values():
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise KernelError(f"a kernel gave up waiting on a barrier (status {code})")
+
+
+_WORKSPACE_FLOATS = 8 * 1024 * 1024      # 32 MB of float32 partial sums for split-k small-batch products
+_NUM_COUNTERS = 4096
+_workspace = {}
+
+
+def _gemm_scratch(device):
+    """(partials, counters) shared by all small-batch matrix products on this device; safe because
+    they are ordered on one stream and every launch leaves the counters at zero."""
+    key = torch.device(device)
+    pair = _workspace.get(key)
+    if pair is None:
+        pair = _workspace[key] = (torch.empty(_WORKSPACE_FLOATS, dtype=torch.float32, device=key),
+                                  torch.zeros(_NUM_COUNTERS, dtype=torch.int32, device=key))
+    return pair
+
+
+def _tensor_core_ok(x: torch.Tensor, w: torch.Tensor, *others) -> bool:
+    """The tcgen05 kernels take bfloat16 operands whose rows start on 16-byte boundaries."""
+    if x.dtype != torch.bfloat16 or x.shape[1] % 8:
+        return False
+    return all(t is None or t.data_ptr() % 16 == 0 for t in (x, w) + others)
 
 
 def _fn(lib_name: str, name: str):
@@ -153,6 +207,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         if tuple(residual.shape) != (m, n):
             raise KernelError("linear: residual shape differs from the output's")
     out = torch.empty((m, n), dtype=torch.float32 if out_float32 else x.dtype, device=x.device)
+    if _tensor_core_ok(x, w):
+        ws, counters = _gemm_scratch(x.device)
+        _run("sm100", "ti_gemm_bf16", out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual),
+             m, n, k, 0, int(out_float32), ws.data_ptr(), ws.numel(), counters.data_ptr(), counters.numel(),
+             kernel_status(x.device).data_ptr(), _stream())
+        return out
     _run("core", "ti_gemm_simt", out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual),
          m, n, k, 0, int(out_float32 and x.dtype != torch.float32), _dtype_code(x), _stream())
     return out
@@ -168,6 +228,12 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         raise KernelError("gated_linear: weight must be [2I, K]")
     inter = w_gate_up.shape[0] // 2
     out = torch.empty((m, inter), dtype=x.dtype, device=x.device)
+    if _tensor_core_ok(x, w_gate_up):
+        ws, counters = _gemm_scratch(x.device)
+        _run("sm100", "ti_gemm_bf16", out.data_ptr(), x.data_ptr(), w_gate_up.data_ptr(), None, None,
+             m, inter, k, 1, 0, ws.data_ptr(), ws.numel(), counters.data_ptr(), counters.numel(),
+             kernel_status(x.device).data_ptr(), _stream())
+        return out
     _run("core", "ti_gemm_simt", out.data_ptr(), x.data_ptr(), w_gate_up.data_ptr(), None, None,
          m, inter, k, 1, 0, _dtype_code(x), _stream())
     return out
@@ -214,13 +280,58 @@ def qk_norm_rope_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int,
     return q
 
 
+def plan_attention(q_lens, starts):
+    """Splits a step's entries into single decoded tokens and portions of prompts.
+    Returns (decode_rows, tiles): flat rows of entries that bring one token, and for the others
+    tiles [entry, first flat row, rows, first position] of at most PREFILL_TILE query rows,
+    longest key range first."""
+    decode_rows, tiles = [], []
+    row = 0
+    for i, (n, start) in enumerate(zip(q_lens, starts)):
+        if n == 1:
+            decode_rows.append(row)
+        else:
+            for off in range(0, n, PREFILL_TILE):
+                tiles.append((i, row + off, min(PREFILL_TILE, n - off), start + off))
+        row += n
+    tiles.sort(key=lambda t: -(t[3] + t[2]))
+    return decode_rows, [x for t in tiles for x in t]
+
+
+def attention_tensor_cores_ok(q: torch.Tensor, kv_cache: torch.Tensor) -> bool:
+    """The tensor-core attention kernels take bfloat16, head sizes 64 and 128, up to 16 query heads
+    per kv head, and pages of 16, 32 or a multiple of 64 tokens."""
+    _, hq, d = q.shape
+    hkv, page = kv_cache.shape[2], kv_cache.shape[3]
+    return (q.dtype == torch.bfloat16 and d in (64, 128) and hq % hkv == 0 and hq // hkv <= 16
+            and (page in (16, 32) or page % 64 == 0))
+
+
+_attn_scratch = {}
+
+
+def _decode_scratch(device, floats: int) -> torch.Tensor:
+    key = torch.device(device)
+    t = _attn_scratch.get(key)
+    if t is None or t.numel() < floats:
+        t = _attn_scratch[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=key)
+    return t
+
+
+def reserve_decode_scratch(device, num_rows: int, num_heads: int, head_dim: int, max_context: int) -> None:
+    """Sizes the decode attention scratch up front (before a CUDA graph is captured)."""
+    splits = (max_context + DECODE_CHUNK - 1) // DECODE_CHUNK
+    _decode_scratch(device, num_rows * num_heads * splits * (head_dim + 2))
+
+
 def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch.Tensor,
                     token_seq: torch.Tensor, block_table: torch.Tensor, scale: float,
                     window: Optional[int] = None, step=None,
                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of q [T, Hq, D] over the pages of each token's own request.
     Token t sees keys max(0, pos - window + 1) .. pos of request ``token_seq[t]``.
-    Returns [T, Hq * D]. ``step`` (the batch summary) lets the op pick a faster kernel."""
+    Returns [T, Hq * D]. ``step`` (the StepContext of the batch) carries the split of the batch
+    into decoded tokens and prompt portions; without it the split is derived here (a device read)."""
     _check(q, "q", None, 3)
     _check(kv_cache, "kv_cache", q.dtype, 5)
     _check(positions, "positions", torch.int32, 1)
@@ -231,10 +342,50 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
     if d2 != d or kv_cache.shape[0] != 2:
         raise KernelError("paged_attention: kv_cache does not match q")
     out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
-    _run("core", "ti_attention_generic", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
-         positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1],
-         t, hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), _ptr(status),
-         _dtype_code(q), _stream())
+    if t == 0:
+        return out
+    if not attention_tensor_cores_ok(q, kv_cache):
+        _run("core", "ti_attention_generic", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+             positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+             t, hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), _ptr(status),
+             _dtype_code(q), _stream())
+        return out
+    if step is not None:
+        decode_rows, num_decode = step.decode_rows, step.num_decode
+        tiles, num_tiles, max_context = step.prefill_tiles, step.num_prefill_tiles, step.max_context
+    else:
+        pos_h, seq_h = positions.tolist(), token_seq.tolist()
+        q_lens, starts = [], []
+        for i, (p_, s_) in enumerate(zip(pos_h, seq_h)):
+            if i and seq_h[i - 1] == s_ and pos_h[i - 1] + 1 == p_:
+                q_lens[-1] += 1
+            else:
+                q_lens.append(1)
+                starts.append(p_)
+        # entries here are runs of consecutive positions; their request index comes from token_seq
+        rows_l, tiles_l = plan_attention(q_lens, starts)
+        firsts, r = [], 0
+        for n in q_lens:
+            firsts.append(seq_h[r])
+            r += n
+        for k in range(0, len(tiles_l), 4):
+            tiles_l[k] = firsts[tiles_l[k]]
+        decode_rows = torch.tensor(rows_l or [0], dtype=torch.int32, device=q.device)
+        tiles = torch.tensor(tiles_l or [0, 0, 0, 0], dtype=torch.int32, device=q.device)
+        num_decode, num_tiles, max_context = len(rows_l), len(tiles_l) // 4, max(pos_h) + 1
+    kstatus = kernel_status(q.device).data_ptr()
+    if num_decode:
+        splits = (max_context + DECODE_CHUNK - 1) // DECODE_CHUNK
+        scratch = _decode_scratch(q.device, num_decode * hq * splits * (d + 2))
+        part_ml = scratch.data_ptr() + 4 * num_decode * hq * splits * d
+        _run("sm100", "ti_attention_decode_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+             scratch.data_ptr(), part_ml, decode_rows.data_ptr(), num_decode, positions.data_ptr(),
+             token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
+             num_pages, float(scale), int(window or 0), splits, kstatus, _stream())
+    if num_tiles:
+        _run("sm100", "ti_attention_prefill_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+             tiles.data_ptr(), num_tiles, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
+             num_pages, float(scale), int(window or 0), kstatus, _stream())
     return out
 
 

@@ -35,6 +35,9 @@ LIBRARIES: Dict[str, dict] = {
     "core": dict(sources=["runtime.cu", "elementwise.cu", "rope_append.cu",
                           "attention_generic.cu", "gemm_simt.cu", "sampling.cu"],
                  headers=["common.cuh"], link=[]),
+    # bfloat16 tensor-core kernels (tcgen05 + TMA); only a bfloat16 model loads it
+    "sm100": dict(sources=["runtime.cu", "sm100_host.cu", "gemm_tcgen05.cu", "attention_mma.cu"],
+                  headers=["common.cuh", "sm100_ptx.cuh"], link=[]),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}
