@@ -83,6 +83,29 @@ def test_long_decoding_and_first_tokens(tmp_path, dtype):
         assert err <= TOL[dtype]
 
 
+def test_graph_replay_equals_eager_steps(tmp_path):
+    """Decode steps replayed from a captured CUDA graph give the very logits of eager steps."""
+    from tinyinfer_b200.engine.replay import TraceSession
+    cfg = helpers.TINY["D"]
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=2, dtype="bfloat16")
+    requests = helpers.random_requests(cfg, [300, 280, 290], seed=3)
+    steps = []
+    for i in range(240):           # three requests side by side, one token each a step
+        steps.append({"step": i, "entries": [{"id": r, "tokens": [t[i]], "want": [0]} for r, t in requests.items()],
+                      "end": []})
+    out = {}
+    for graphs in (False, True):
+        session = TraceSession(folder, "bfloat16", 3 * 320, page_size=64, cuda_graphs=graphs, poison_cache=True)
+        out[graphs] = helpers.collect(session, steps)
+        session.runner.check_status()
+        assert (session.runner.graph_replays > 200) == graphs
+    for r in requests:
+        for p in range(240):
+            assert np.array_equal(out[True][r][p], out[False][r][p]), (r, p)
+    want = helpers.plain_logits(folder, {r: t[:240] for r, t in requests.items()})
+    assert helpers.first_bad(out[True], want, TOL["bfloat16"]) is None
+
+
 def run_trace_program(folder, dtype, out, steps, max_tokens, page_size=16):
     cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
            "--out", str(out), "--max-tokens", str(max_tokens), "--page-size", str(page_size)]

@@ -86,9 +86,11 @@ class BatchBuffers:
         self.bytes_copied = 0              # host-to-device bytes of all steps so far
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
-              tables: Sequence[Sequence[Sequence[int]]]) -> StepContext:
+              tables: Sequence[Sequence[Sequence[int]]], fixed_layout: bool = False) -> StepContext:
         """``starts[i]``: tokens entry i's request already holds; ``slots[i]``: its state slot;
-        ``tables[g][i]``: its block table in cache group g."""
+        ``tables[g][i]``: its block table in cache group g. ``fixed_layout`` pads every block
+        table to the widest possible, so that two steps with the same numbers of tokens and
+        requests put every array at the same address (what a captured CUDA graph needs)."""
         q_lens = [len(e.tokens) for e in entries]
         t, s = sum(q_lens), len(entries)
         if t > self.max_tokens or s > self.max_seqs:
@@ -111,7 +113,7 @@ class BatchBuffers:
             cu.append(cu[-1] + n)
         ctx_lens = [starts[i] + q_lens[i] for i in range(s)]
         widths = [max((len(tb) for tb in tables[g]), default=0) for g in range(self.num_groups)]
-        widths = [max(1, w) for w in widths]
+        widths = [self.max_blocks if fixed_layout else max(1, w) for w in widths]
         if max(widths, default=1) > self.max_blocks:
             raise ValueError("a block table is longer than the buffers allow")
         flat: List[int] = []

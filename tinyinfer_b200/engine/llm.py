@@ -58,7 +58,7 @@ class LLM:
             self.model, page_size=page, num_pages=num_pages, max_requests=self.config.live_requests,
             max_seqs_per_step=self.config.max_num_seqs,
             max_tokens_per_step=self.config.max_num_batched_tokens,
-            max_model_len=self.config.max_model_len)
+            max_model_len=self.config.max_model_len, cuda_graphs=self.config.cuda_graphs)
         eos = self.config.eos_token_id
         if eos < 0:
             model_eos = getattr(self.model_config, "eos_token_id", None)

@@ -31,7 +31,8 @@ def pool_pages(max_tokens: int, page_size: int) -> int:
 
 class TraceSession:
     def __init__(self, model_dir, dtype: str, max_tokens: int, *, page_size: int = 16,
-                 device="cuda:0", max_live: int = 8, poison_cache: bool = False, model=None):
+                 device="cuda:0", max_live: int = 8, poison_cache: bool = False, model=None,
+                 cuda_graphs: bool = True):
         if model is None:
             require_cuda(device)
             model, _ = load_model(model_dir, dtype, device)
@@ -40,7 +41,7 @@ class TraceSession:
         self.runner = ModelRunner(
             model, page_size=page_size, num_pages=pool_pages(max_tokens, page_size),
             max_requests=max_live, max_tokens_per_step=max(max_tokens, 1), max_model_len=limit,
-            poison_cache=poison_cache)
+            poison_cache=poison_cache, cuda_graphs=cuda_graphs)
 
     def run_step(self, step: dict) -> Optional[np.ndarray]:
         """Runs one step; returns float32 logits [wanted, vocab] or None if nothing is wanted."""

@@ -20,9 +20,10 @@ from .batch import BatchBuffers, CacheView, StepContext, StepEntry
 class ModelRunner:
     def __init__(self, model, *, page_size: int, num_pages: int, max_requests: int,
                  max_tokens_per_step: int, max_model_len: int, max_seqs_per_step: int = 0,
-                 poison_cache: bool = False):
+                 poison_cache: bool = False, cuda_graphs: bool = False):
         """``max_requests``: requests that may hold cache at a time (state slots);
-        ``max_seqs_per_step``: requests in one step (0: the same)."""
+        ``max_seqs_per_step``: requests in one step (0: the same); ``cuda_graphs``: steps made of
+        single decoded tokens only are captured once per batch size and replayed."""
         self.model = model
         self.device = model.device
         needs = model.cache_needs()
@@ -34,6 +35,11 @@ class ModelRunner:
                                     max_seqs_per_step or max_requests, max_blocks,
                                     max(1, len(self.manager.groups)))
         self.steps_run = 0
+        self.cuda_graphs = (cuda_graphs and self.device.type == "cuda"
+                            and all(b.mixer.graph_safe for b in model.blocks))
+        self._graphs = {}          # (requests, split bucket) -> (graph, static logits)
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: Hashable) -> None:
@@ -77,12 +83,46 @@ class ModelRunner:
         caches = [self.manager.get(rid) for rid in ids]
         num_groups = len(self.manager.groups)
         tables = [[rc.tables[g] for rc in caches] for g in range(num_groups)] or [[[] for _ in caches]]
-        ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables)
+        decode_only = self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables,
+                                 fixed_layout=decode_only)
         self._bind_views(ctx)
-        logits = self.model.forward(ctx)
+        logits = self._graph_forward(ctx) if decode_only else self.model.forward(ctx)
         for e, start in zip(entries, starts):
             self.manager.commit(e.request_id, start + len(e.tokens))
         self.steps_run += 1
+        return logits
+
+    def _graph_forward(self, ctx: StepContext) -> torch.Tensor:
+        """A step of single decoded tokens: replayed from a CUDA graph captured for this number
+        of requests. The graph reads the step's arrays from the fixed device buffer that
+        ``build`` has just filled; the attention grid is sized for the context rounded up to a
+        power of two of 256-key splits, so a handful of graphs cover every context length.
+        The returned logits live in the graph's own memory until the next replay."""
+        from .. import ops
+        from ..ops import library
+        splits = 1
+        while splits * ops.DECODE_CHUNK < ctx.max_context:
+            splits *= 2
+        ctx.max_context = splits * ops.DECODE_CHUNK
+        key = (ctx.num_seqs, splits)
+        hit = self._graphs.get(key)
+        if hit is not None:
+            hit[0].replay()
+            self.graph_replays += 1
+            library.count_replayed_launches(hit[2])
+            return hit[1]
+        logits = self.model.forward(ctx)              # eager once: also sets up every kernel it uses
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        launches_before = library.launch_count()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            static_logits = self.model.forward(ctx)
+        kernels_in_graph = library.launch_count() - launches_before
+        library.count_replayed_launches(-kernels_in_graph)       # captured, not run
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        self._graphs[key] = (graph, static_logits, kernels_in_graph)
         return logits
 
     def _bind_views(self, ctx: StepContext) -> None:

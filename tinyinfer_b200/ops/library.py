@@ -167,9 +167,18 @@ def loaded_libraries() -> Dict[str, ctypes.CDLL]:
     return dict(_loaded)
 
 
+_replayed_launches = 0
+
+
+def count_replayed_launches(n: int) -> None:
+    """Kernels that ran as part of a replayed CUDA graph (they do not pass through the launchers)."""
+    global _replayed_launches
+    _replayed_launches += int(n)
+
+
 def launch_count() -> int:
-    """Kernels launched through the libraries of this process so far."""
-    return sum(int(lib.ti_launch_count()) for lib in _loaded.values())
+    """Kernels of this package launched by this process so far, directly or in a replayed graph."""
+    return sum(int(lib.ti_launch_count()) for lib in _loaded.values()) + _replayed_launches
 
 
 def build_all(verbose: bool = True) -> List[Path]:

@@ -14,6 +14,8 @@ from .base import CacheNeed, Mixer, TensorSpec, build_position, register_mixer
 
 
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
         if spec.num_heads % spec.num_kv_heads:

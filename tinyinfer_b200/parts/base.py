@@ -73,6 +73,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if forward() only launches kernels on the step's device tensors (no host reads, no
+    # Python branching on the step's contents): such a step may be captured in a CUDA graph.
+    graph_safe = False
+
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 
