@@ -574,3 +574,56 @@ TI_API int ti_attention_prefill_bf16(void* out, const void* q, const void* kv_ca
     TI_CHECK_LAUNCH("attention_prefill");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// A decode-attention entry point that allocates nothing (declared in tinyinfer_b200_noalloc.h; the
+// reference has no counterpart). It is ti_attention_decode_bf16 with the split partials kept in a
+// fixed array inside this library instead of a buffer the caller allocates.
+//
+// Who needs it: code that runs where device allocation is off limits. A plugin called from inside
+// another runtime's stream callback or graph-capture region, a serving loop that has handed all free
+// memory to its cache and must not grow, or a host that forbids cudaMalloc after start-up for
+// latency reasons can still call this: it issues kernel launches only.
+//
+// The array is `static __device__`: every GPU that loads this library holds TI_NOALLOC_SCRATCH_FLOATS
+// floats (8 MB) of it until the process exits. In host code the array's name is only a stand-in, not
+// a device address, so the first call on each device looks the address up with
+// cudaGetSymbolAddress while that device is current and keeps it. That first call should be made
+// before any stream capture begins. All calls on a device share the array: two calls that overlap on
+// the GPU (different streams, no ordering) race on it. Nothing in it needs clearing between calls:
+// every word the merge kernel reads was written by the split kernel of the same call.
+constexpr long long TI_NOALLOC_SCRATCH_FLOATS = 2ll * 1024 * 1024;
+static __device__ __align__(256) float g_noalloc_decode_scratch[TI_NOALLOC_SCRATCH_FLOATS];
+
+TI_API long long ti_attention_decode_noalloc_capacity() { return TI_NOALLOC_SCRATCH_FLOATS; }
+
+TI_API int ti_attention_decode_bf16_noalloc(void* out, const void* q, const void* kv_cache, const int* rows,
+                                            int num_rows, const int* positions, const int* token_seq,
+                                            const int* block_table, int max_blocks, int hq, int hkv, int d,
+                                            int page_size, int num_pages, float scale, int window, int max_splits,
+                                            int* status, cudaStream_t stream) {
+    constexpr int MAX_DEVICES = 64;
+    static float* scratch_of_device[MAX_DEVICES] = {};
+    TI_REQUIRE(num_rows >= 0 && max_splits > 0 && hq > 0 && d > 0, "attention_decode_noalloc: bad sizes");
+    const long long need = (long long)num_rows * hq * max_splits * (d + 2);
+    TI_REQUIRE(need <= TI_NOALLOC_SCRATCH_FLOATS,
+               "attention_decode_noalloc: %d rows x %d heads x %d splits x (%d + 2) = %lld floats exceed the built-in "
+               "scratch of %lld floats; use ti_attention_decode_bf16 with a buffer of your own",
+               num_rows, hq, max_splits, d, need, TI_NOALLOC_SCRATCH_FLOATS);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    TI_REQUIRE(e == cudaSuccess && dev >= 0 && dev < MAX_DEVICES, "attention_decode_noalloc: no current device (%s)",
+               cudaGetErrorString(e));
+    if (scratch_of_device[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_decode_scratch);
+        TI_REQUIRE(e == cudaSuccess && ptr != nullptr, "attention_decode_noalloc: cudaGetSymbolAddress failed: %s",
+                   cudaGetErrorString(e));
+        scratch_of_device[dev] = ptr;
+    }
+    float* part_o = scratch_of_device[dev];
+    float* part_ml = part_o + (long long)num_rows * hq * max_splits * d;
+    return ti_attention_decode_bf16(out, q, kv_cache, part_o, part_ml, rows, num_rows, positions, token_seq,
+                                    block_table, max_blocks, hq, hkv, d, page_size, num_pages, scale, window,
+                                    max_splits, status, stream);
+}
