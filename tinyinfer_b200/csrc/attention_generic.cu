@@ -20,6 +20,8 @@ __global__ void __launch_bounds__(AG_THREADS) attention_generic_kernel(
     __shared__ float p[AG_THREADS];
     __shared__ long long row_off[AG_THREADS];
     __shared__ float red[33];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
     const int tid = threadIdx.x;
     const int h = blockIdx.x, t = blockIdx.y;
     const int pos = positions[t];
@@ -89,12 +91,12 @@ TI_API int ti_attention_generic(
     dim3 grid(hq, num_tokens);
     if (dtype == TI_F32) {
         const float* kc = (const float*)kv_cache;
-        attention_generic_kernel<float><<<grid, AG_THREADS, 0, stream>>>(
+        ti_launch(attention_generic_kernel<float>, grid, AG_THREADS, 0, stream,
             (float*)out, (const float*)q, kc, kc + v_off, positions, token_seq, block_table, max_blocks, hq, hkv,
             d, page_size, num_pages, scale, window, status);
     } else if (dtype == TI_BF16) {
         const __nv_bfloat16* kc = (const __nv_bfloat16*)kv_cache;
-        attention_generic_kernel<__nv_bfloat16><<<grid, AG_THREADS, 0, stream>>>(
+        ti_launch(attention_generic_kernel<__nv_bfloat16>, grid, AG_THREADS, 0, stream,
             (__nv_bfloat16*)out, (const __nv_bfloat16*)q, kc, kc + v_off, positions, token_seq, block_table,
             max_blocks, hq, hkv, d, page_size, num_pages, scale, window, status);
     } else TI_REQUIRE(false, "attention: unknown dtype %d", dtype);

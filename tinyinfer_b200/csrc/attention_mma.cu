@@ -129,6 +129,8 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
 
+    ti_grid_launch_dependents();
+    ti_grid_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
     const int row = p.rows[r];
     const int ctx = p.positions[row] + 1;
@@ -298,6 +300,8 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
 // One block per (decode row, query head): merges the splits that hold visible keys.
 template <int D>
 __global__ void decode_merge_kernel(const AttnParams p) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
     const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     const int row = p.rows[r];
     const int ctx = p.positions[row] + 1;
@@ -330,6 +334,8 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_kernel(const __grid
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
 
+    ti_grid_launch_dependents();
+    ti_grid_wait();
     const int4 td = reinterpret_cast<const int4*>(p.rows)[blockIdx.x];
     const int seq = td.x, row0 = td.y, nrows = td.z, pos0 = td.w;
     const int head = blockIdx.y;
@@ -532,15 +538,15 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
     if (d == 128) {
         static bool once = false;
         if (!once) { if (set_smem(decode_attention_kernel<128>, Smem<128>::BYTES, "attention_decode")) return -1; once = true; }
-        decode_attention_kernel<128><<<grid, THREADS, Smem<128>::BYTES, stream>>>(map, p);
+        ti_launch(decode_attention_kernel<128>, grid, THREADS, Smem<128>::BYTES, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
-        decode_merge_kernel<128><<<dim3(num_rows, hq), 128, 0, stream>>>(p);
+        ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
     } else {
         static bool once = false;
         if (!once) { if (set_smem(decode_attention_kernel<64>, Smem<64>::BYTES, "attention_decode")) return -1; once = true; }
-        decode_attention_kernel<64><<<grid, THREADS, Smem<64>::BYTES, stream>>>(map, p);
+        ti_launch(decode_attention_kernel<64>, grid, THREADS, Smem<64>::BYTES, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
-        decode_merge_kernel<64><<<dim3(num_rows, hq), 64, 0, stream>>>(p);
+        ti_launch(decode_merge_kernel<64>, dim3(num_rows, hq), 64, 0, stream, p);
     }
     TI_CHECK_LAUNCH("attention_decode_merge");
     return 0;
@@ -565,11 +571,11 @@ TI_API int ti_attention_prefill_bf16(void* out, const void* q, const void* kv_ca
     if (d == 128) {
         static bool once = false;
         if (!once) { if (set_smem(prefill_attention_kernel<128>, Smem<128>::BYTES, "attention_prefill")) return -1; once = true; }
-        prefill_attention_kernel<128><<<grid, THREADS, Smem<128>::BYTES, stream>>>(map, p);
+        ti_launch(prefill_attention_kernel<128>, grid, THREADS, Smem<128>::BYTES, stream, map, p);
     } else {
         static bool once = false;
         if (!once) { if (set_smem(prefill_attention_kernel<64>, Smem<64>::BYTES, "attention_prefill")) return -1; once = true; }
-        prefill_attention_kernel<64><<<grid, THREADS, Smem<64>::BYTES, stream>>>(map, p);
+        ti_launch(prefill_attention_kernel<64>, grid, THREADS, Smem<64>::BYTES, stream, map, p);
     }
     TI_CHECK_LAUNCH("attention_prefill");
     return 0;

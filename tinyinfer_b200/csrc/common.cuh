@@ -33,6 +33,31 @@ void ti_count_launch(int n = 1);
         ti_count_launch();                                                      \
     } while (0)
 
+// Programmatic dependent launch: every kernel of this package waits for the kernels before it in
+// the stream with ti_grid_wait() before it touches anything they wrote (and before it writes
+// anything), and lets the kernel after it start its own prologue early with
+// ti_grid_launch_dependents(). Launched without the attribute, both are no-ops.
+__device__ __forceinline__ void ti_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ti_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool ti_pdl_enabled();
+
+// Launches `kernel` with the programmatic-stream-serialization attribute (unless switched off by
+// TINYINFER_B200_PDL=0): it may begin while the previous kernel of the stream drains.
+template <typename... KArgs, typename... Args>
+cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ti_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(
     __shared__ float As[GS_BK][GS_BM + 4];
     __shared__ float Bs[GS_BK][GS_BN + 4];
     __shared__ float Cs[GATED ? GS_BK : 1][GS_BN + 4];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;          // 16 x 16 threads, 4 x 4 outputs each
     const int m0 = blockIdx.y * GS_BM, n0 = blockIdx.x * GS_BN;
@@ -84,17 +86,17 @@ TI_API int ti_gemm_simt(void* out, const void* x, const void* w, const float* bi
     TI_REQUIRE(grid.y <= 65535, "gemm: too many rows");
     if (dtype == TI_F32) {
         if (gated)
-            gemm_simt_kernel<float, float, true><<<grid, GS_THREADS, 0, stream>>>((float*)out, (const float*)x, (const float*)w, nullptr, nullptr, M, N, K, N);
+            ti_launch(gemm_simt_kernel<float, float, true>, grid, GS_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, nullptr, nullptr, M, N, K, N);
         else
-            gemm_simt_kernel<float, float, false><<<grid, GS_THREADS, 0, stream>>>((float*)out, (const float*)x, (const float*)w, bias, (const float*)residual, M, N, K, 0);
+            ti_launch(gemm_simt_kernel<float, float, false>, grid, GS_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, bias, (const float*)residual, M, N, K, 0);
     } else if (dtype == TI_BF16) {
         typedef __nv_bfloat16 B;
         if (gated)
-            gemm_simt_kernel<B, B, true><<<grid, GS_THREADS, 0, stream>>>((B*)out, (const B*)x, (const B*)w, nullptr, nullptr, M, N, K, N);
+            ti_launch(gemm_simt_kernel<B, B, true>, grid, GS_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, nullptr, nullptr, M, N, K, N);
         else if (out_f32)
-            gemm_simt_kernel<B, float, false><<<grid, GS_THREADS, 0, stream>>>((float*)out, (const B*)x, (const B*)w, bias, (const B*)residual, M, N, K, 0);
+            ti_launch(gemm_simt_kernel<B, float, false>, grid, GS_THREADS, 0, stream, (float*)out, (const B*)x, (const B*)w, bias, (const B*)residual, M, N, K, 0);
         else
-            gemm_simt_kernel<B, B, false><<<grid, GS_THREADS, 0, stream>>>((B*)out, (const B*)x, (const B*)w, bias, (const B*)residual, M, N, K, 0);
+            ti_launch(gemm_simt_kernel<B, B, false>, grid, GS_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, bias, (const B*)residual, M, N, K, 0);
     } else TI_REQUIRE(false, "gemm: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("gemm_simt");
     return 0;

@@ -110,6 +110,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
 
+    ti_grid_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // tiles: gated normal tiles hold BN/2 gate and BN/2 up columns; gated swapped tiles 64 + 64 rows
     const int rows_per_tile = (p.gated && p.swap) ? BM / 2 : BM;
@@ -139,33 +140,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
-                const int tile = unit / p.splits, split = unit % p.splits;
+            // The copies of one k block: `rows_side` / `cols_side` pick the operand(s) to load.
+            auto issue = [&](int unit, int kb, int s, bool rows_side, bool cols_side) {
+                const int tile = unit / p.splits;
                 const int rt = tile % row_tiles, ct = tile / row_tiles;
                 const int r0 = rt * rows_per_tile, c0 = ct * cols_per_tile;
-                const int kb0 = (int)((long long)split * num_kb / p.splits);
-                const int kb1 = (int)((long long)(split + 1) * num_kb / p.splits);
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % C::STAGES;
-                    const uint32_t ph = (it / C::STAGES) & 1u;
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
-                    const uint32_t a_dst = smem_u32(stages + s * C::STAGE_BYTES);
-                    const uint32_t b_dst = a_dst + BM * BK * 2;
-                    mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                const uint32_t a_dst = smem_u32(stages + s * C::STAGE_BYTES);
+                const uint32_t b_dst = a_dst + BM * BK * 2;
+                if (rows_side) {
                     if (p.gated && p.swap) {          // 64 gate rows, then 64 up rows
                         tma_load_2d(a_dst, &map_rows, full_bar(s), kb * BK, r0);
                         tma_load_2d(a_dst + (BM / 2) * BK * 2, &map_rows, full_bar(s), kb * BK, p.N + r0);
                     } else {
                         tma_load_2d(a_dst, &map_rows, full_bar(s), kb * BK, r0);
                     }
+                }
+                if (cols_side) {
                     if (p.gated && !p.swap) {         // BN/2 gate rows, then BN/2 up rows
                         tma_load_2d(b_dst, &map_cols, full_bar(s), kb * BK, c0);
                         tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_cols, full_bar(s), kb * BK, p.N + c0);
                     } else {
                         tma_load_2d(b_dst, &map_cols, full_bar(s), kb * BK, c0);
                     }
+                }
+            };
+            auto kb_range = [&](int unit, int& kb0, int& kb1) {
+                const int split = unit % p.splits;
+                kb0 = (int)((long long)split * num_kb / p.splits);
+                kb1 = (int)((long long)(split + 1) * num_kb / p.splits);
+            };
+            // Before waiting for the kernels ahead of this one in the stream: the weights do not
+            // depend on them, so their copies for the first ring of stages start right away and
+            // HBM stays busy while the previous kernel drains. The activations follow after the wait.
+            const bool weights_are_rows = p.swap != 0;
+            uint32_t pre = 0;
+            for (int unit = blockIdx.x; unit < num_units && pre < (uint32_t)C::STAGES; unit += gridDim.x) {
+                int kb0, kb1;
+                kb_range(unit, kb0, kb1);
+                for (int kb = kb0; kb < kb1 && pre < (uint32_t)C::STAGES; ++kb, ++pre) {
+                    mbar_expect_tx(full_bar(pre), C::STAGE_BYTES);
+                    issue(unit, kb, pre, weights_are_rows, !weights_are_rows);
+                }
+            }
+            ti_grid_wait();
+            uint32_t it = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+                int kb0, kb1;
+                kb_range(unit, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % C::STAGES;
+                    if (it < pre) {                   // its weights are already on their way
+                        issue(unit, kb, s, !weights_are_rows, weights_are_rows);
+                        continue;
+                    }
+                    const uint32_t ph = (it / C::STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                    issue(unit, kb, s, true, true);
                 }
             }
             // After an abort, give the copies this CTA still has in flight time to land (they take
@@ -209,6 +241,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
+        ti_grid_wait();                                  // residual, scratch and out belong to earlier kernels until now
         const int lane_group = warp & 3;                 // the 32 accumulator lanes this warp may read
         const int row_in_tile = lane_group * 32 + lane;
         uint32_t tile_i = 0;
@@ -430,6 +463,7 @@ int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int
     double best_eff = 0.0;
     for (int s = 1; s <= 8; ++s) {
         if (s > 1 && (num_kb / s < 4 || (long long)tiles * s * bn * BM > workspace_floats)) break;
+        if (s > 1 && s * bn * 40 > num_kb * BK) break;     // partial sums must stay small beside the weights
         const long long units = (long long)tiles * s;
         const double eff = (double)units / (double)(((units + sms - 1) / sms) * sms);
         if (eff > best_eff + 0.04) { best_eff = eff; best = s; }
@@ -447,7 +481,7 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmP
     }
     num_tiles *= p.splits;
     const int grid = num_tiles < ti_sm_count() ? num_tiles : ti_sm_count();
-    gemm_tcgen05_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(rows_map, cols_map, p);
+    ti_launch(gemm_tcgen05_kernel<BN>, grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream, rows_map, cols_map, p);
     TI_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }

@@ -18,6 +18,8 @@ __global__ void qk_norm_rope_append_kernel(
     const int* __restrict__ block_table, int max_blocks,
     int hq, int hkv, int d, int page_size, int num_pages, int* __restrict__ status) {
     __shared__ float buf[RA_WARPS][RA_MAX_D];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.x * RA_WARPS + warp;
     const int t = blockIdx.y;
@@ -78,6 +80,99 @@ __global__ void qk_norm_rope_append_kernel(
     }
 }
 
+// Head sizes 64 and 128 with the rotation over the whole head (or none): a lane owns D / 32
+// neighbouring features, loads and stores them as one vector, and gets its rotation partner
+// (the feature D / 2 away) from the lane 16 further on.
+template <typename T, int D>
+__global__ void __launch_bounds__(RA_WARPS * 32) qk_norm_rope_append_vec_kernel(
+    T* __restrict__ q_out, const T* __restrict__ qkv, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const float* __restrict__ inv_freq,
+    const int* __restrict__ positions, const int* __restrict__ token_seq,
+    const int* __restrict__ block_table, int max_blocks,
+    int hq, int hkv, int page_size, int num_pages, int* __restrict__ status) {
+    constexpr int VEC = D / 32;
+    struct alignas(sizeof(T) * VEC) Pack { T e[VEC]; };
+    ti_grid_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.x * RA_WARPS + warp;
+    const int t = blockIdx.y;
+    const int heads_total = hq + 2 * hkv;
+    if (head >= heads_total) return;
+    const bool is_q = head < hq;
+    const bool is_k = !is_q && head < hq + hkv;
+    if (!is_q && k_cache == nullptr) return;
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    float wv[VEC], fr[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {                 // constants: read before the wait
+        wv[i] = w ? w[lane * VEC + i] : 1.f;
+        fr[i] = inv_freq ? inv_freq[(lane & 15) * VEC + i] : 0.f;
+    }
+    ti_grid_wait();
+    const Pack in = *reinterpret_cast<const Pack*>(qkv + ((size_t)t * heads_total + head) * D + lane * VEC);
+    float x[VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        x[i] = to_f32(in.e[i]);
+        ss += x[i] * x[i];
+    }
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) x[i] = wv[i] * x[i] * inv;
+    }
+    const int pos = positions[t];
+    if ((is_q || is_k) && inv_freq != nullptr) {
+        const float pos_f = (float)pos;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+            float s, c;
+            sincosf(pos_f * fr[i], &s, &c);
+            x[i] = lane < 16 ? x[i] * c - other * s : x[i] * c + other * s;
+        }
+    }
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * hq + head) * D;
+    } else {
+        const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0 && status) atomicExch(status, 1);
+            return;
+        }
+        const int kvh = is_k ? head - hq : head - hq - hkv;
+        dst = (is_k ? k_cache : v_cache) + (((size_t)page * hkv + kvh) * page_size + pos % page_size) * D;
+    }
+    Pack o;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o.e[i] = from_f32<T>(x[i]);
+    *reinterpret_cast<Pack*>(dst + lane * VEC) = o;
+}
+
+template <typename T>
+static void launch_rope(T* q_out, const T* qkv, T* kc, size_t v_off, const float* q_norm_w, const float* k_norm_w,
+                        float eps, const float* inv_freq, int rotary_dim, const int* positions, const int* token_seq,
+                        const int* block_table, int max_blocks, int num_tokens, int hq, int hkv, int d, int page_size,
+                        int num_pages, int* status, cudaStream_t stream) {
+    dim3 grid((hq + 2 * hkv + RA_WARPS - 1) / RA_WARPS, num_tokens);
+    T* vc = kc ? kc + v_off : nullptr;
+    const bool whole = inv_freq == nullptr || rotary_dim == d;
+    if (whole && d == 128)
+        ti_launch(qk_norm_rope_append_vec_kernel<T, 128>, grid, RA_WARPS * 32, 0, stream, q_out, qkv, kc, vc, q_norm_w,
+                  k_norm_w, eps, inv_freq, positions, token_seq, block_table, max_blocks, hq, hkv, page_size, num_pages, status);
+    else if (whole && d == 64)
+        ti_launch(qk_norm_rope_append_vec_kernel<T, 64>, grid, RA_WARPS * 32, 0, stream, q_out, qkv, kc, vc, q_norm_w,
+                  k_norm_w, eps, inv_freq, positions, token_seq, block_table, max_blocks, hq, hkv, page_size, num_pages, status);
+    else
+        ti_launch(qk_norm_rope_append_kernel<T>, grid, RA_WARPS * 32, 0, stream, q_out, qkv, kc, vc, q_norm_w, k_norm_w,
+                  eps, inv_freq, rotary_dim, positions, token_seq, block_table, max_blocks, hq, hkv, d, page_size,
+                  num_pages, status);
+}
+
 TI_API int ti_qk_norm_rope_append(
     void* q_out, const void* qkv, void* kv_cache, const float* q_norm_w, const float* k_norm_w, float eps,
     const float* inv_freq, int rotary_dim, const int* positions, const int* token_seq,
@@ -90,19 +185,15 @@ TI_API int ti_qk_norm_rope_append(
     TI_REQUIRE(num_tokens <= 65535, "qk_norm_rope_append: more than 65535 tokens in one step");
     if (num_tokens == 0) return 0;
     const size_t v_off = (size_t)num_pages * hkv * page_size * d;
-    dim3 grid((hq + 2 * hkv + RA_WARPS - 1) / RA_WARPS, num_tokens);
-    if (dtype == TI_F32) {
-        float* kc = (float*)kv_cache;
-        qk_norm_rope_append_kernel<float><<<grid, RA_WARPS * 32, 0, stream>>>(
-            (float*)q_out, (const float*)qkv, kc, kc ? kc + v_off : nullptr, q_norm_w, k_norm_w, eps, inv_freq,
-            rotary_dim, positions, token_seq, block_table, max_blocks, hq, hkv, d, page_size, num_pages, status);
-    } else if (dtype == TI_BF16) {
-        __nv_bfloat16* kc = (__nv_bfloat16*)kv_cache;
-        qk_norm_rope_append_kernel<__nv_bfloat16><<<grid, RA_WARPS * 32, 0, stream>>>(
-            (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, kc, kc ? kc + v_off : nullptr, q_norm_w, k_norm_w,
-            eps, inv_freq, rotary_dim, positions, token_seq, block_table, max_blocks, hq, hkv, d, page_size,
-            num_pages, status);
-    } else TI_REQUIRE(false, "qk_norm_rope_append: unknown dtype %d", dtype);
+    if (dtype == TI_F32)
+        launch_rope<float>((float*)q_out, (const float*)qkv, (float*)kv_cache, v_off, q_norm_w, k_norm_w, eps, inv_freq,
+                           rotary_dim, positions, token_seq, block_table, max_blocks, num_tokens, hq, hkv, d, page_size,
+                           num_pages, status, stream);
+    else if (dtype == TI_BF16)
+        launch_rope<__nv_bfloat16>((__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)kv_cache, v_off,
+                                   q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, positions, token_seq, block_table,
+                                   max_blocks, num_tokens, hq, hkv, d, page_size, num_pages, status, stream);
+    else TI_REQUIRE(false, "qk_norm_rope_append: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("qk_norm_rope_append");
     return 0;
 }

@@ -68,6 +68,8 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(
     __shared__ Best sh_best[SP_THREADS / 32];
     __shared__ unsigned hist[256];
     __shared__ unsigned sel_prefix, sel_remaining;
+    ti_grid_launch_dependents();
+    ti_grid_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* x = logits + (size_t)row * vocab;
 
@@ -144,7 +146,71 @@ TI_API int ti_sample(int* out, const float* logits, int num_rows, int vocab, con
                      const int* step, cudaStream_t stream) {
     TI_REQUIRE(num_rows >= 0 && vocab > 0, "sample: bad sizes");
     if (num_rows == 0) return 0;
-    sample_kernel<<<num_rows, SP_THREADS, 0, stream>>>(out, logits, vocab, temperature, topk, greedy, seed, stream_id, step);
+    ti_launch(sample_kernel, num_rows, SP_THREADS, 0, stream, out, logits, vocab, temperature, topk, greedy, seed, stream_id, step);
     TI_CHECK_LAUNCH("sample");
+    return 0;
+}
+
+// ------------------------------------------------------------------ argmax over many blocks
+// A row of 150 thousand logits is too long for one block: AM_PARTS blocks each scan a slice and
+// leave their best in scratch; the block that arrives last (a counter per row, left at zero again)
+// picks among the parts. Ties go to the lowest index at both levels.
+constexpr int AM_PARTS = 32;
+
+__global__ void __launch_bounds__(SP_THREADS) argmax_parts_kernel(
+    int* __restrict__ out, const float* __restrict__ logits, int vocab, float* __restrict__ part_val,
+    int* __restrict__ part_idx, int* __restrict__ counters) {
+    __shared__ Best sh_best[SP_THREADS / 32];
+    __shared__ int last_sh;
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int part = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+    const float* x = logits + (size_t)row * vocab;
+    const int chunk = ((vocab + AM_PARTS - 1) / AM_PARTS + 3) & ~3;
+    const int begin = part * chunk, end = min(vocab, begin + chunk);
+    Best b{0.f, -1};
+    if ((((uintptr_t)x) & 15) == 0 && (vocab & 3) == 0) {
+        for (int i = begin + tid * 4; i < end; i += SP_THREADS * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(x + i);
+            if (v.x == v.x) b = better(b, Best{v.x, i});
+            if (v.y == v.y) b = better(b, Best{v.y, i + 1});
+            if (v.z == v.z) b = better(b, Best{v.z, i + 2});
+            if (v.w == v.w) b = better(b, Best{v.w, i + 3});
+        }
+    } else {
+        for (int i = begin + tid; i < end; i += SP_THREADS) {
+            const float v = x[i];
+            if (v == v) b = better(b, Best{v, i});
+        }
+    }
+    b = block_best(b, sh_best);
+    if (tid == 0) {
+        part_val[row * AM_PARTS + part] = b.v;
+        part_idx[row * AM_PARTS + part] = b.i;
+        __threadfence();
+        const int arrived = atomicAdd(counters + row, 1);
+        last_sh = arrived == AM_PARTS - 1;
+        if (last_sh) counters[row] = 0;
+    }
+    __syncthreads();
+    if (!last_sh) return;
+    __threadfence();
+    Best m{0.f, -1};
+    if (tid < AM_PARTS) m = Best{__ldcg(part_val + row * AM_PARTS + tid), __ldcg(part_idx + row * AM_PARTS + tid)};
+    m = block_best(m, sh_best);
+    if (tid == 0) out[row] = m.i < 0 ? 0 : m.i;
+}
+
+TI_API int ti_argmax_parts() { return AM_PARTS; }
+
+// part_val / part_idx: scratch of num_rows * ti_argmax_parts() entries; counters: num_rows zeroed ints
+// (left zeroed). Calls that share them must be ordered on one stream.
+TI_API int ti_argmax(int* out, const float* logits, int num_rows, int vocab, float* part_val, int* part_idx,
+                     int* counters, cudaStream_t stream) {
+    TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && vocab > 0, "argmax: bad sizes");
+    if (num_rows == 0) return 0;
+    ti_launch(argmax_parts_kernel, dim3(AM_PARTS, num_rows), SP_THREADS, 0, stream, out, logits, vocab, part_val,
+              part_idx, counters);
+    TI_CHECK_LAUNCH("argmax");
     return 0;
 }

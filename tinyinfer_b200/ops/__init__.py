@@ -39,6 +39,7 @@ _SIGNATURES = {
                          c_int, c_int, c_int, c_void_p],
         "ti_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p],
+        "ti_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     },
 }
 _SIGNATURES["sm100"] = {
@@ -75,13 +76,13 @@ def check_kernel_status() -> None:
             raise KernelError(f"a kernel gave up waiting on a barrier (status {code})")
 
 
-_WORKSPACE_FLOATS = 8 * 1024 * 1024      # 32 MB of float32 partial sums for split-k small-batch products
-_NUM_COUNTERS = 4096
+_WORKSPACE_FLOATS = 12 * 1024 * 1024     # 48 MB of float32 partial tiles for the stream-k cuts of matrix products
+_NUM_COUNTERS = 16384
 _workspace = {}
 
 
 def _gemm_scratch(device):
-    """(partials, counters) shared by all small-batch matrix products on this device; safe because
+    """(partials, counters) shared by all tensor-core matrix products on this device; safe because
     they are ordered on one stream and every launch leaves the counters at zero."""
     key = torch.device(device)
     pair = _workspace.get(key)
@@ -390,12 +391,25 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
 
 
 # ---------------------------------------------------------------------- sampling
+_ARGMAX_PARTS = 32
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     """Index of the largest logit of every row (first index on ties), int32 [N]."""
     _check(logits, "logits", torch.float32, 2)
-    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    _run("core", "ti_sample", out.data_ptr(), logits.data_ptr(), logits.shape[0], logits.shape[1],
-         None, None, None, None, None, None, _stream())
+    n = logits.shape[0]
+    out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    key = torch.device(logits.device)
+    scratch = _argmax_scratch.get(key)
+    if scratch is None or scratch[2].numel() < n:
+        rows = max(256, n)
+        scratch = _argmax_scratch[key] = (
+            torch.empty(rows * _ARGMAX_PARTS, dtype=torch.float32, device=key),
+            torch.empty(rows * _ARGMAX_PARTS, dtype=torch.int32, device=key),
+            torch.zeros(rows, dtype=torch.int32, device=key))
+    _run("core", "ti_argmax", out.data_ptr(), logits.data_ptr(), n, logits.shape[1], scratch[0].data_ptr(),
+         scratch[1].data_ptr(), scratch[2].data_ptr(), _stream())
     return out
 
 
