@@ -34,7 +34,7 @@ struct AttnParams {
     const int* positions;
     const int* token_seq;
     const int* block_table;
-    int max_blocks, hq, hkv, page_size, num_pages, window, max_splits;
+    int max_blocks, hq, hkv, page_size, num_pages, window, max_splits, num_rows;
     float scale_log2;              // softmax scale times log2(e)
     int* status;
 };
@@ -67,6 +67,8 @@ struct Smem {
     static constexpr int TILE_BYTES = HALVES * TK * 128;      // keys OR values of one tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int BYTES = 1024 + STAGES * STAGE_BYTES + 128;
+    // decode adds its merge buffer: [4 warps][query heads of a kv head <= 16][D + 2] floats
+    static int decode_bytes(int group) { return BYTES + 4 * group * (D + 2) * 4; }
 };
 
 // Issues the copies of tile `t` (keys t*TK .. t*TK+63 of the request) into a stage. Pieces whose
@@ -118,182 +120,204 @@ __device__ __forceinline__ void zero_value_rows(uint8_t* v_tile, int keep_lo, in
 }
 
 // ------------------------------------------------------------------------------------ decode
+// Persistent: a CTA walks over work items (decode row, kv head, split of 256 keys), item = cta,
+// cta + grid, ...; the loading warp runs ahead into the next item while the consumers merge and
+// write the current one, so HBM does not idle at item boundaries.
 template <int D>
 __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                    const AttnParams p) {
     using S = Smem<D>;
+    constexpr int LD = D + 2;                              // merge buffer row: D outputs, maximum, sum
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+    float* mbuf = reinterpret_cast<float*>(smem + STAGES * S::STAGE_BYTES + 128);   // [4 warps][group][LD]
     const uint32_t bar0 = smem_u32(bars);
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
 
     ti_grid_launch_dependents();
-    ti_grid_wait();
-    const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
-    const int row = p.rows[r];
-    const int ctx = p.positions[row] + 1;
-    const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
-    const int k_begin = max(split * CHUNK, lo), k_end = min(ctx, (split + 1) * CHUNK);
-    if (k_begin >= k_end) return;                       // this split holds no visible key
-    const int* table = p.block_table + (size_t)p.token_seq[row] * p.max_blocks;
-    const int tile0 = k_begin / TK, tile1 = (k_end + TK - 1) / TK;
     const int group = p.hq / p.hkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
+    const int num_items = p.num_rows * p.hkv * p.max_splits;
     if (threadIdx.x == 0) {
         abort_sh = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(bar0 + 8u * s, 1); mbar_init(bar0 + 8u * (STAGES + s), 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    ti_grid_wait();
+
+    // item -> its row, kv head and key range; false if the split holds no visible key
+    struct Item { int r, row, kvh, split, k_begin, k_end; };
+    auto get_item = [&](int w, Item& it) {
+        it.split = w % p.max_splits;
+        const int rest = w / p.max_splits;
+        it.kvh = rest % p.hkv;
+        it.r = rest / p.hkv;
+        it.row = p.rows[it.r];
+        const int ctx = p.positions[it.row] + 1;
+        const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
+        it.k_begin = max(it.split * CHUNK, lo);
+        it.k_end = min(ctx, (it.split + 1) * CHUNK);
+        return it.k_begin < it.k_end;
+    };
 
     if (warp == 4) {
         if (lane == 0) {
-            uint32_t it = 0;
-            for (int t = tile0; t < tile1; ++t, ++it) {
-                const int s = it % STAGES;
-                if (!mbar_wait(bar0 + 8u * (STAGES + s), ((it / STAGES) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
-                load_tile<D>(&kv_map, p, table, kvh, t, smem_u32(smem + s * S::STAGE_BYTES), bar0 + 8u * s);
+            uint32_t n = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+                Item it;
+                if (!get_item(w, it)) continue;
+                const int* table = p.block_table + (size_t)p.token_seq[it.row] * p.max_blocks;
+                for (int t = it.k_begin / TK; t < (it.k_end + TK - 1) / TK; ++t, ++n) {
+                    const int s = n % STAGES;
+                    if (!mbar_wait(bar0 + 8u * (STAGES + s), ((n / STAGES) & 1u) ^ 1u, abort_flag, p.status, 21)) { ok = false; break; }
+                    load_tile<D>(&kv_map, p, table, it.kvh, t, smem_u32(smem + s * S::STAGE_BYTES), bar0 + 8u * s);
+                }
             }
         }
         return;
     }
 
-    // ---- consumers: the 16 rows of the MMA are the query heads of this kv head (rows >= group are zero)
+    // ---- consumers: the 16 rows of the MMA are the query heads of one kv head (rows >= group are zero)
     const int g = lane >> 2, c = (lane & 3) * 2;
-    uint32_t qa[D / 16][4];
-    {
-        const __nv_bfloat16* q0 = p.q + ((size_t)row * p.hq + (size_t)kvh * group) * D;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            qa[ks][0] = g < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + ks * 16 + c) : 0u;
-            qa[ks][1] = g + 8 < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + ks * 16 + c) : 0u;
-            qa[ks][2] = g < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + ks * 16 + c + 8) : 0u;
-            qa[ks][3] = g + 8 < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + ks * 16 + c + 8) : 0u;
-        }
-    }
-    float o[D / 8][4];
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int id = lane >> 3, rr = lane & 7;
-    bool ok = true;
-
-    uint32_t it = 0;
-    for (int t = tile0; t < tile1; ++t, ++it) {
-        const int s = it % STAGES;
-        if (!mbar_wait(bar0 + 8u * s, (it / STAGES) & 1u, abort_flag, p.status, 22)) { ok = false; break; }
-        uint8_t* k_tile = smem + s * S::STAGE_BYTES;
-        uint8_t* v_tile = k_tile + S::TILE_BYTES;
-        const int w0 = warp * 16;                         // this warp's 16 keys of the tile
-        const int tok0 = t * TK + w0;
-        if (tok0 < k_end && tok0 + 16 > k_begin) {
-            float sc[2][4] = {};
+    uint32_t n = 0;
+    for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
+        Item item;
+        if (!get_item(w, item)) continue;
+        uint32_t qa[D / 16][4];
+        {
+            const __nv_bfloat16* q0 = p.q + ((size_t)item.row * p.hq + (size_t)item.kvh * group) * D;
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-                uint32_t b[4];
-                const int krow = w0 + (id >> 1) * 8 + rr;
-                ldmatrix_x4(b, smem_u32(k_tile) + tile_off(krow, ks * 2 + (id & 1)));
-                mma_bf16(sc[0], qa[ks], b[0], b[1]);
-                mma_bf16(sc[1], qa[ks], b[2], b[3]);
-            }
-            float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-            for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int tok = tok0 + nb * 8 + c + (j & 1);
-                    const float v = (tok >= k_begin && tok < k_end) ? sc[nb][j] * p.scale_log2 : -INFINITY;
-                    sc[nb][j] = v;
-                    mx[j >> 1] = fmaxf(mx[j >> 1], v);
-                }
-            float corr[2], m_use[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-                const float m_new = fmaxf(m_run[h], mx[h]);
-                m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-                corr[h] = exp2f(m_run[h] - m_use[h]);
-                m_run[h] = m_new;
-                l_run[h] *= corr[h];
-            }
-#pragma unroll
-            for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float pv = exp2f(sc[nb][j] - m_use[j >> 1]);
-                    sc[nb][j] = pv;
-                    l_run[j >> 1] += pv;
-                }
-            uint32_t pa[4] = {pack_bf16(sc[0][0], sc[0][1]), pack_bf16(sc[0][2], sc[0][3]),
-                              pack_bf16(sc[1][0], sc[1][1]), pack_bf16(sc[1][2], sc[1][3])};
-            if (tok0 < k_begin || tok0 + 16 > k_end) {    // warp-local: only this warp reads these rows
-                zero_value_rows<D>(v_tile, k_begin - t * TK, k_end - t * TK, lane, 32, w0, w0 + 16);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // a later TMA copy overwrites these rows
-                __syncwarp();
-            }
-#pragma unroll
-            for (int nb = 0; nb < D / 8; nb += 2) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    o[nb][j] *= corr[j >> 1];
-                    o[nb + 1][j] *= corr[j >> 1];
-                }
-                uint32_t b[4];
-                const int vrow = w0 + (id & 1) * 8 + rr;
-                ldmatrix_x4_trans(b, smem_u32(v_tile) + tile_off(vrow, nb + (id >> 1)));
-                mma_bf16(o[nb], pa, b[0], b[1]);
-                mma_bf16(o[nb + 1], pa, b[2], b[3]);
+                qa[ks][0] = g < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + ks * 16 + c) : 0u;
+                qa[ks][1] = g + 8 < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + ks * 16 + c) : 0u;
+                qa[ks][2] = g < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + ks * 16 + c + 8) : 0u;
+                qa[ks][3] = g + 8 < group ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + ks * 16 + c + 8) : 0u;
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar0 + 8u * (STAGES + s));
-    }
+        float o[D / 8][4];
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+        const int k_begin = item.k_begin, k_end = item.k_end;
 
-    // ---- merge the four warps (each saw a quarter of the keys) and write the split's partial
+        for (int t = k_begin / TK; t < (k_end + TK - 1) / TK; ++t, ++n) {
+            const int s = n % STAGES;
+            if (!mbar_wait(bar0 + 8u * s, (n / STAGES) & 1u, abort_flag, p.status, 22)) return;
+            uint8_t* k_tile = smem + s * S::STAGE_BYTES;
+            uint8_t* v_tile = k_tile + S::TILE_BYTES;
+            const int w0 = warp * 16;                         // this warp's 16 keys of the tile
+            const int tok0 = t * TK + w0;
+            if (tok0 < k_end && tok0 + 16 > k_begin) {
+                float sc[2][4] = {};
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");       // every consumer is done with the stages
-    if (!ok) return;
-    float* mbuf = reinterpret_cast<float*>(smem);         // [4 warps][16 rows][D + 2]
-    constexpr int LD = D + 2;
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    uint32_t b[4];
+                    const int krow = w0 + (id >> 1) * 8 + rr;
+                    ldmatrix_x4(b, smem_u32(k_tile) + tile_off(krow, ks * 2 + (id & 1)));
+                    mma_bf16(sc[0], qa[ks], b[0], b[1]);
+                    mma_bf16(sc[1], qa[ks], b[2], b[3]);
+                }
+                float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int nb = 0; nb < D / 8; ++nb) {
-        float* base = mbuf + ((size_t)warp * 16) * LD + nb * 8 + c;
-        base[(size_t)g * LD] = o[nb][0];
-        base[(size_t)g * LD + 1] = o[nb][1];
-        base[(size_t)(g + 8) * LD] = o[nb][2];
-        base[(size_t)(g + 8) * LD + 1] = o[nb][3];
-    }
-    if ((lane & 3) == 0) {
-        mbuf[((size_t)warp * 16 + g) * LD + D] = m_run[0];
-        mbuf[((size_t)warp * 16 + g) * LD + D + 1] = l_run[0];
-        mbuf[((size_t)warp * 16 + g + 8) * LD + D] = m_run[1];
-        mbuf[((size_t)warp * 16 + g + 8) * LD + D + 1] = l_run[1];
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    for (int idx = threadIdx.x; idx < group * D; idx += CONSUMER_THREADS) {
-        const int hrow = idx / D, d = idx % D;
-        float mw[4], m_all = -INFINITY;
+                for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-        for (int w = 0; w < 4; ++w) { mw[w] = mbuf[((size_t)w * 16 + hrow) * LD + D]; m_all = fmaxf(m_all, mw[w]); }
-        const float m_use = m_all == -INFINITY ? 0.f : m_all;
-        float acc = 0.f, l_all = 0.f;
+                    for (int j = 0; j < 4; ++j) {
+                        const int tok = tok0 + nb * 8 + c + (j & 1);
+                        const float v = (tok >= k_begin && tok < k_end) ? sc[nb][j] * p.scale_log2 : -INFINITY;
+                        sc[nb][j] = v;
+                        mx[j >> 1] = fmaxf(mx[j >> 1], v);
+                    }
+                float corr[2], m_use[2];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float f = exp2f(mw[w] - m_use);
-            acc += f * mbuf[((size_t)w * 16 + hrow) * LD + d];
-            l_all += f * mbuf[((size_t)w * 16 + hrow) * LD + D + 1];
+                for (int h = 0; h < 2; ++h) {
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                    const float m_new = fmaxf(m_run[h], mx[h]);
+                    m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+                    corr[h] = exp2f(m_run[h] - m_use[h]);
+                    m_run[h] = m_new;
+                    l_run[h] *= corr[h];
+                }
+#pragma unroll
+                for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float pv = exp2f(sc[nb][j] - m_use[j >> 1]);
+                        sc[nb][j] = pv;
+                        l_run[j >> 1] += pv;
+                    }
+                uint32_t pa[4] = {pack_bf16(sc[0][0], sc[0][1]), pack_bf16(sc[0][2], sc[0][3]),
+                                  pack_bf16(sc[1][0], sc[1][1]), pack_bf16(sc[1][2], sc[1][3])};
+                if (tok0 < k_begin || tok0 + 16 > k_end) {    // warp-local: only this warp reads these rows
+                    zero_value_rows<D>(v_tile, k_begin - t * TK, k_end - t * TK, lane, 32, w0, w0 + 16);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // a later TMA copy overwrites these rows
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int nb = 0; nb < D / 8; nb += 2) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        o[nb][j] *= corr[j >> 1];
+                        o[nb + 1][j] *= corr[j >> 1];
+                    }
+                    uint32_t b[4];
+                    const int vrow = w0 + (id & 1) * 8 + rr;
+                    ldmatrix_x4_trans(b, smem_u32(v_tile) + tile_off(vrow, nb + (id >> 1)));
+                    mma_bf16(o[nb], pa, b[0], b[1]);
+                    mma_bf16(o[nb + 1], pa, b[2], b[3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar0 + 8u * (STAGES + s));
         }
-        const size_t slot = ((size_t)r * p.hq + (size_t)kvh * group + hrow) * p.max_splits + split;
-        p.part_o[slot * D + d] = acc;
-        if (d == 0) { p.part_ml[slot * 2] = m_all; p.part_ml[slot * 2 + 1] = l_all; }
+
+        // ---- merge the four warps (each saw a quarter of the keys) and write the split's partial.
+        // Only the rows that are real query heads travel through shared memory.
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");       // the previous item's merge buffer has been read
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb) {
+            float* base = mbuf + ((size_t)warp * group) * LD + nb * 8 + c;
+            if (g < group) { base[(size_t)g * LD] = o[nb][0]; base[(size_t)g * LD + 1] = o[nb][1]; }
+            if (g + 8 < group) { base[(size_t)(g + 8) * LD] = o[nb][2]; base[(size_t)(g + 8) * LD + 1] = o[nb][3]; }
+        }
+        if ((lane & 3) == 0) {
+            if (g < group) {
+                mbuf[((size_t)warp * group + g) * LD + D] = m_run[0];
+                mbuf[((size_t)warp * group + g) * LD + D + 1] = l_run[0];
+            }
+            if (g + 8 < group) {
+                mbuf[((size_t)warp * group + g + 8) * LD + D] = m_run[1];
+                mbuf[((size_t)warp * group + g + 8) * LD + D + 1] = l_run[1];
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int idx = threadIdx.x; idx < group * D; idx += CONSUMER_THREADS) {
+            const int hrow = idx / D, d = idx % D;
+            float mw[4], m_all = -INFINITY;
+#pragma unroll
+            for (int w4 = 0; w4 < 4; ++w4) { mw[w4] = mbuf[((size_t)w4 * group + hrow) * LD + D]; m_all = fmaxf(m_all, mw[w4]); }
+            const float m_use = m_all == -INFINITY ? 0.f : m_all;
+            float acc = 0.f, l_all = 0.f;
+#pragma unroll
+            for (int w4 = 0; w4 < 4; ++w4) {
+                const float f = exp2f(mw[w4] - m_use);
+                acc += f * mbuf[((size_t)w4 * group + hrow) * LD + d];
+                l_all += f * mbuf[((size_t)w4 * group + hrow) * LD + D + 1];
+            }
+            const size_t slot = ((size_t)item.r * p.hq + (size_t)item.kvh * group + hrow) * p.max_splits + item.split;
+            p.part_o[slot * D + d] = acc;
+            if (d == 0) { p.part_ml[slot * 2] = m_all; p.part_ml[slot * 2 + 1] = l_all; }
+        }
     }
 }
 
@@ -534,17 +558,24 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
     p.rows = rows; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
     p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window; p.max_splits = max_splits; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    dim3 grid(max_splits, hkv, num_rows);
+    p.num_rows = num_rows;
+    const int group = hq / hkv;
+    const long long items = (long long)num_rows * hkv * max_splits;
+    TI_REQUIRE(items < (1ll << 31), "attention_decode: too many work items");
     if (d == 128) {
-        static bool once = false;
-        if (!once) { if (set_smem(decode_attention_kernel<128>, Smem<128>::BYTES, "attention_decode")) return -1; once = true; }
-        ti_launch(decode_attention_kernel<128>, grid, THREADS, Smem<128>::BYTES, stream, map, p);
+        const int bytes = Smem<128>::decode_bytes(group);
+        static int configured = 0;
+        if (configured < bytes) { if (set_smem(decode_attention_kernel<128>, bytes, "attention_decode")) return -1; configured = bytes; }
+        const int slots = ti_sm_count() * (bytes <= 113 * 1024 ? 2 : 1);
+        ti_launch(decode_attention_kernel<128>, (int)(items < slots ? items : slots), THREADS, bytes, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
         ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
     } else {
-        static bool once = false;
-        if (!once) { if (set_smem(decode_attention_kernel<64>, Smem<64>::BYTES, "attention_decode")) return -1; once = true; }
-        ti_launch(decode_attention_kernel<64>, grid, THREADS, Smem<64>::BYTES, stream, map, p);
+        const int bytes = Smem<64>::decode_bytes(group);
+        static int configured = 0;
+        if (configured < bytes) { if (set_smem(decode_attention_kernel<64>, bytes, "attention_decode")) return -1; configured = bytes; }
+        const int slots = ti_sm_count() * (bytes <= 56 * 1024 ? 4 : (bytes <= 75 * 1024 ? 3 : 2));
+        ti_launch(decode_attention_kernel<64>, (int)(items < slots ? items : slots), THREADS, bytes, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
         ti_launch(decode_merge_kernel<64>, dim3(num_rows, hq), 64, 0, stream, p);
     }
