@@ -84,14 +84,20 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.f +
 template <int BN>
 struct Cfg {
     static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
-    static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;        // two accumulators; a power of two
     static constexpr int EXCH_FLOATS = BN <= 64 ? 64 * (BN + 1) + 2 : 2;   // swapped gated epilogue (BN <= 64) + one word
+    // small-batch tiles (BN <= 64) take half an SM's shared memory, so that two CTAs share an SM: one
+    // streams weights while the other reduces and stores, and the next kernel's CTAs can move in early
+    static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
+    static constexpr int BUDGET = SMEM_BUDGET / CTAS_PER_SM - EXCH_FLOATS * 4;
+    static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 12 ? 12 : (BUDGET / STAGE_BYTES);
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EXCH_FLOATS * 4 + 256;
+    static_assert(STAGES >= 2, "too little shared memory for a pipeline");
+    static_assert(CTAS_PER_SM * (SMEM_BYTES + 1024) <= 227 * 1024, "the CTAs of an SM do not fit its shared memory");
 };
 
 template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, Cfg<BN>::CTAS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     const GemmParams p) {
     using C = Cfg<BN>;
@@ -458,12 +464,13 @@ int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int
         const int s = atoi(forced);
         if (s >= 1 && num_kb / s >= 1 && (long long)tiles * s * bn * BM <= workspace_floats) return s;
     }
-    const int sms = ti_sm_count();
+    const int sms = ti_sm_count() * 2;                    // two small-batch CTAs share an SM
     int best = 1;
     double best_eff = 0.0;
     for (int s = 1; s <= 8; ++s) {
         if (s > 1 && (num_kb / s < 4 || (long long)tiles * s * bn * BM > workspace_floats)) break;
-        if (s > 1 && s * bn * 40 > num_kb * BK) break;     // partial sums must stay small beside the weights
+        // partial sums must stay small beside the weights, unless the tiles alone leave most SMs idle
+        if (s > 1 && s * bn * 40 > num_kb * BK && (tiles * 2 >= sms || s > 4)) break;
         const long long units = (long long)tiles * s;
         const double eff = (double)units / (double)(((units + sms - 1) / sms) * sms);
         if (eff > best_eff + 0.04) { best_eff = eff; best = s; }
@@ -480,7 +487,8 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmP
         configured = true;
     }
     num_tiles *= p.splits;
-    const int grid = num_tiles < ti_sm_count() ? num_tiles : ti_sm_count();
+    const int slots = ti_sm_count() * Cfg<BN>::CTAS_PER_SM;
+    const int grid = num_tiles < slots ? num_tiles : slots;
     ti_launch(gemm_tcgen05_kernel<BN>, grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream, rows_map, cols_map, p);
     TI_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
