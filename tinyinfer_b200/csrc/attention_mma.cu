@@ -348,7 +348,7 @@ __global__ void decode_merge_kernel(const AttnParams p) {
 // One CTA per (tile of up to 64 consecutive query tokens of one request, query head); warp w owns
 // query rows 16w .. 16w+15 of the tile.
 template <int D>
-__global__ void __launch_bounds__(THREADS) prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
+__global__ void __launch_bounds__(THREADS, 2) prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                     const AttnParams p) {
     using S = Smem<D>;
     extern __shared__ uint8_t smem_raw[];
