@@ -106,6 +106,31 @@ def test_graph_replay_equals_eager_steps(tmp_path):
     assert helpers.first_bad(out[True], want, TOL["bfloat16"]) is None
 
 
+BIG = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=4099, hidden_size=4096,
+    num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    intermediate_size=12288, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_bias=False,
+    tie_word_embeddings=False, max_position_embeddings=4096)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_sizes_of_the_benchmark_model(tmp_path, dtype):
+    """One layer with the sizes of the benchmark model (hidden 4096, 32/8 heads of 128, feed-forward
+    12288; a small odd vocabulary): the shapes the tensor-core kernels are tuned for, checked through
+    the engine in every kind of step, in both dtypes."""
+    from tinyinfer_b200.engine.replay import TraceSession
+    folder = helpers.make_model_folder(tmp_path / "m", BIG, seed=6, dtype=dtype, std=0.02)
+    requests = helpers.random_requests(BIG, [130, 70, 33, 200], seed=2)
+    want = helpers.plain_logits(folder, requests)
+    for tag, steps in (("tail", helpers.trace_decode_tail(requests, tail=20)),
+                       ("mixed", helpers.trace_mixed(requests, seed=4, max_live=3))):
+        session = TraceSession(folder, dtype, helpers.peak_tokens(steps), page_size=64, poison_cache=True)
+        got = helpers.collect(session, steps)
+        session.runner.check_status()
+        bad = helpers.first_bad(got, want, TOL[dtype])
+        assert bad is None, (tag, bad)
+
+
 def run_trace_program(folder, dtype, out, steps, max_tokens, page_size=16):
     cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
            "--out", str(out), "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
