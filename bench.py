@@ -121,9 +121,9 @@ def main() -> int:
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference does not install offline: its extension needs CUTLASS headers "
-                          "it does not ship (setup.py third_party/cutlass) and its engine needs a real "
-                          "checkpoint with a tokenizer"}))
+                          "the reference does not install offline: pip finds no torch>=2.4 in the wheelhouse, and with "
+                          "--no-deps its extension fails to build (linear.cu: cutlass/cutlass.h not found; "
+                          "third_party/cutlass is not shipped); its engine also needs a real checkpoint with a tokenizer"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this engine is single-GPU by design (got --gpus {args.gpus})")
