@@ -465,6 +465,7 @@ int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int
         if (s >= 1 && num_kb / s >= 1 && (long long)tiles * s * bn * BM <= workspace_floats) return s;
     }
     const int sms = ti_sm_count() * 2;                    // two small-batch CTAs share an SM
+    if (tiles * 2 >= sms) return 1;                       // every SM has a tile: cutting them only adds the merge
     int best = 1;
     double best_eff = 0.0;
     for (int s = 1; s <= 8; ++s) {
