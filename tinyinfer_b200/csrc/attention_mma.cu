@@ -1,20 +1,19 @@
-// bfloat16 paged attention on tensor cores for head sizes 64 and 128: a split-KV kernel for single
-// decoded tokens (FlashDecoding: tinyinfer/csrc/flash_decoding.cu:17-336 of the reference, here
-// batched over requests in ONE launch, with the query heads of a kv head sharing one read of its
-// keys and values) and a causal kernel for portions of prompts that reads the cached prefix
-// through the block table (tinyinfer/csrc/flash_attention.cu:5-234 plus the gather the reference
-// does on the host, tinyinfer/layers/attention.py:60-81).
+// bfloat16 paged attention for single decoded tokens, head sizes 64 and 128: a split-KV kernel
+// (FlashDecoding: tinyinfer/csrc/flash_decoding.cu:17-336 of the reference, here batched over requests
+// in ONE launch, with the query heads of a kv head sharing one read of its keys and values).
 //
 // Keys and values come straight from the pages: a warp of its own issues TMA tile copies
 // (64 keys x 64 features, 128-byte swizzle) into a 3-stage ring guarded by mbarriers; four warps
-// consume them with ldmatrix + mma.sync.m16n8k16 (bf16 in, float32 out). Scores, running maximum
-// (from -inf), sums and outputs are float32; probabilities are rounded to bfloat16 for the second
-// product. Masked scores are assigned -inf (never added), and value rows that no query of the CTA
-// may see are zeroed in shared memory, so stale or unwritten pages cannot leak NaNs.
+// consume them with ldmatrix + mma.sync.m16n8k16 (bf16 in, float32 out): a decoded token has at most
+// 16 query rows per kv head, far too few for a 128-row tcgen05 tile, and the kernel is bound by HBM,
+// not by the tensor pipe. Scores, running maximum (from -inf), sums and outputs are float32;
+// probabilities are rounded to bfloat16 for the second product. Masked scores are assigned -inf
+// (never added), and value rows that no query of the CTA may see are zeroed in shared memory, so
+// stale or unwritten pages cannot leak NaNs.
 //
-// The decode split is by position only (256 keys per split), so a request's result does not depend
-// on what else is in the batch. Partial results (unnormalised output, maximum, sum per split) go
-// to float32 scratch and a second kernel merges them.
+// The split is by position only (256 keys per split), so a request's result does not depend on what
+// else is in the batch. Partial results (unnormalised output, maximum, sum per split) go to float32
+// scratch and a second kernel merges them. (Prompt portions: attention_prefill_tcgen05.cu.)
 #include "sm100_ptx.cuh"
 
 namespace {
@@ -344,177 +343,6 @@ __global__ void decode_merge_kernel(const AttnParams p) {
     p.out[((size_t)row * p.hq + h) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
 }
 
-// ------------------------------------------------------------------------------------ prefill
-// One CTA per (tile of up to 64 consecutive query tokens of one request, query head); warp w owns
-// query rows 16w .. 16w+15 of the tile.
-template <int D>
-__global__ void __launch_bounds__(THREADS, 2) prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
-                                                                    const AttnParams p) {
-    using S = Smem<D>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
-    const uint32_t bar0 = smem_u32(bars);
-    __shared__ int abort_sh;
-    volatile int* abort_flag = &abort_sh;
-
-    ti_grid_launch_dependents();
-    ti_grid_wait();
-    const int4 td = reinterpret_cast<const int4*>(p.rows)[blockIdx.x];
-    const int seq = td.x, row0 = td.y, nrows = td.z, pos0 = td.w;
-    const int head = blockIdx.y;
-    const int kvh = head / (p.hq / p.hkv);
-    const int hi = pos0 + nrows;                                   // one past the last key any query sees
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0; // first key the first query sees
-    const int* table = p.block_table + (size_t)seq * p.max_blocks;
-    const int tile0 = lo / TK, tile1 = (hi + TK - 1) / TK;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        abort_sh = 0;
-        for (int s = 0; s < STAGES; ++s) { mbar_init(bar0 + 8u * s, 1); mbar_init(bar0 + 8u * (STAGES + s), 4); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    if (warp == 4) {
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int t = tile0; t < tile1; ++t, ++it) {
-                const int s = it % STAGES;
-                if (!mbar_wait(bar0 + 8u * (STAGES + s), ((it / STAGES) & 1u) ^ 1u, abort_flag, p.status, 23)) break;
-                load_tile<D>(&kv_map, p, table, kvh, t, smem_u32(smem + s * S::STAGE_BYTES), bar0 + 8u * s);
-            }
-        }
-        return;
-    }
-
-    const int g = lane >> 2, c = (lane & 3) * 2;
-    const int lr0 = warp * 16 + g, lr1 = lr0 + 8;                  // this thread's two query rows (tile-local)
-    const int qpos0 = pos0 + lr0, qpos1 = pos0 + lr1;
-    const int warp_qmin = pos0 + warp * 16, warp_qmax = min(pos0 + warp * 16 + 15, hi - 1);
-    const bool warp_active = warp * 16 < nrows;
-    uint32_t qa[D / 16][4];
-    {
-        const __nv_bfloat16* q0 = p.q + ((size_t)(row0 + lr0) * p.hq + head) * D;
-        const __nv_bfloat16* q1 = p.q + ((size_t)(row0 + lr1) * p.hq + head) * D;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            qa[ks][0] = lr0 < nrows ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c) : 0u;
-            qa[ks][1] = lr1 < nrows ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c) : 0u;
-            qa[ks][2] = lr0 < nrows ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c + 8) : 0u;
-            qa[ks][3] = lr1 < nrows ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c + 8) : 0u;
-        }
-    }
-    float o[D / 8][4];
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    const int id = lane >> 3, rr = lane & 7;
-    bool ok = true;
-
-    uint32_t it = 0;
-    for (int t = tile0; t < tile1; ++t, ++it) {
-        const int s = it % STAGES;
-        if (!mbar_wait(bar0 + 8u * s, (it / STAGES) & 1u, abort_flag, p.status, 24)) { ok = false; break; }
-        uint8_t* k_tile = smem + s * S::STAGE_BYTES;
-        uint8_t* v_tile = k_tile + S::TILE_BYTES;
-        const int tk0 = t * TK;
-        if (tk0 < lo || tk0 + TK > hi) {                  // CTA-uniform: the first or the last tile
-            zero_value_rows<D>(v_tile, lo - tk0, hi - tk0, threadIdx.x, CONSUMER_THREADS, 0, TK);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // a later TMA copy overwrites these rows
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
-        // a warp whose queries all lie before the tile, or whose windows all ended before it, skips it
-        const bool sees = warp_active && tk0 <= warp_qmax && (p.window == 0 || tk0 + TK - 1 > warp_qmin - p.window);
-        if (sees) {
-            float sc[TK / 8][4];
-#pragma unroll
-            for (int nb = 0; nb < TK / 8; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-#pragma unroll
-                for (int np = 0; np < TK / 16; ++np) {
-                    uint32_t b[4];
-                    const int krow = np * 16 + (id >> 1) * 8 + rr;
-                    ldmatrix_x4(b, smem_u32(k_tile) + tile_off(krow, ks * 2 + (id & 1)));
-                    mma_bf16(sc[2 * np], qa[ks], b[0], b[1]);
-                    mma_bf16(sc[2 * np + 1], qa[ks], b[2], b[3]);
-                }
-            }
-            const bool need_mask = tk0 + TK - 1 > warp_qmin || (p.window > 0 && tk0 <= warp_qmax - p.window);
-            float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-            for (int nb = 0; nb < TK / 8; ++nb)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float v = sc[nb][j] * p.scale_log2;
-                    if (need_mask) {
-                        const int tok = tk0 + nb * 8 + c + (j & 1);
-                        const int qp = (j >> 1) ? qpos1 : qpos0;
-                        const bool keep = tok <= qp && (p.window == 0 || tok > qp - p.window);
-                        v = keep ? v : -INFINITY;
-                    }
-                    sc[nb][j] = v;
-                    mx[j >> 1] = fmaxf(mx[j >> 1], v);
-                }
-            float corr[2], m_use[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-                const float m_new = fmaxf(m_run[h], mx[h]);
-                m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-                corr[h] = exp2f(m_run[h] - m_use[h]);
-                m_run[h] = m_new;
-                l_run[h] *= corr[h];
-            }
-#pragma unroll
-            for (int nb = 0; nb < TK / 8; ++nb)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float pv = exp2f(sc[nb][j] - m_use[j >> 1]);
-                    sc[nb][j] = pv;
-                    l_run[j >> 1] += pv;
-                }
-#pragma unroll
-            for (int nb = 0; nb < D / 8; ++nb)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) o[nb][j] *= corr[j >> 1];
-#pragma unroll
-            for (int kk = 0; kk < TK / 16; ++kk) {
-                const uint32_t pa[4] = {pack_bf16(sc[2 * kk][0], sc[2 * kk][1]), pack_bf16(sc[2 * kk][2], sc[2 * kk][3]),
-                                        pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]),
-                                        pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3])};
-#pragma unroll
-                for (int nb = 0; nb < D / 8; nb += 2) {
-                    uint32_t b[4];
-                    const int vrow = kk * 16 + (id & 1) * 8 + rr;
-                    ldmatrix_x4_trans(b, smem_u32(v_tile) + tile_off(vrow, nb + (id >> 1)));
-                    mma_bf16(o[nb], pa, b[0], b[1]);
-                    mma_bf16(o[nb + 1], pa, b[2], b[3]);
-                }
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar0 + 8u * (STAGES + s));
-    }
-    if (!ok) return;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-    }
-    const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
-    __nv_bfloat16* out0 = p.out + ((size_t)(row0 + lr0) * p.hq + head) * D;
-    __nv_bfloat16* out1 = p.out + ((size_t)(row0 + lr1) * p.hq + head) * D;
-#pragma unroll
-    for (int nb = 0; nb < D / 8; ++nb) {
-        if (lr0 < nrows) *reinterpret_cast<uint32_t*>(out0 + nb * 8 + c) = pack_bf16(o[nb][0] * inv0, o[nb][1] * inv0);
-        if (lr1 < nrows) *reinterpret_cast<uint32_t*>(out1 + nb * 8 + c) = pack_bf16(o[nb][2] * inv1, o[nb][3] * inv1);
-    }
-}
-
 template <typename K>
 int set_smem(K kernel, int bytes, const char* name) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -538,7 +366,6 @@ TI_API int ti_attention_bf16_supported(int hq, int hkv, int d, int page_size) {
            ((page_size < TK && TK % page_size == 0) || page_size % TK == 0) ? 1 : 0;
 }
 TI_API int ti_attention_decode_chunk() { return CHUNK; }
-TI_API int ti_attention_prefill_tile() { return TK; }
 
 // Decode: `rows` lists the flat rows of the step whose request brings exactly one token.
 // Scratch: part_o float32 [num_rows * hq * max_splits * d], part_ml float32 [num_rows * hq * max_splits * 2];
@@ -580,35 +407,6 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
         ti_launch(decode_merge_kernel<64>, dim3(num_rows, hq), 64, 0, stream, p);
     }
     TI_CHECK_LAUNCH("attention_decode_merge");
-    return 0;
-}
-
-// Prefill: `tiles` holds num_tiles int4 {request index in the step, first flat row, rows (<= 64),
-// position of the first row}; every tile lies inside one request's portion.
-TI_API int ti_attention_prefill_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
-                                     const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,
-                                     int num_pages, float scale, int window, int* status, cudaStream_t stream) {
-    if (check_shape(hq, hkv, d, page_size, "attention_prefill")) return -1;
-    TI_REQUIRE(num_tiles >= 0 && hq <= 65535, "attention_prefill: bad sizes");
-    if (num_tiles == 0) return 0;
-    CUtensorMap map;
-    if (!ti_get_bf16_map(kv_cache, 2ll * num_pages * hkv * page_size, d, page_size < TK ? page_size : TK, &map)) return -1;
-    AttnParams p;
-    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q; p.part_o = nullptr; p.part_ml = nullptr;
-    p.rows = tiles; p.positions = nullptr; p.token_seq = nullptr; p.block_table = block_table;
-    p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
-    p.window = window; p.max_splits = 0; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    dim3 grid(num_tiles, hq);
-    if (d == 128) {
-        static bool once = false;
-        if (!once) { if (set_smem(prefill_attention_kernel<128>, Smem<128>::BYTES, "attention_prefill")) return -1; once = true; }
-        ti_launch(prefill_attention_kernel<128>, grid, THREADS, Smem<128>::BYTES, stream, map, p);
-    } else {
-        static bool once = false;
-        if (!once) { if (set_smem(prefill_attention_kernel<64>, Smem<64>::BYTES, "attention_prefill")) return -1; once = true; }
-        ti_launch(prefill_attention_kernel<64>, grid, THREADS, Smem<64>::BYTES, stream, map, p);
-    }
-    TI_CHECK_LAUNCH("attention_prefill");
     return 0;
 }
 

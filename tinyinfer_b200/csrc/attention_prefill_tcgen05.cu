@@ -1,0 +1,379 @@
+// Causal paged attention for portions of prompts on the tcgen05 tensor cores (bfloat16, head sizes
+// 64 and 128). One CTA owns 128 consecutive query tokens of one request and one query head:
+//
+//   warp 0      TMA: the query tile once, then key/value tiles of 128 keys from the pages (the cached
+//               prefix and the portion itself, through the block table) into a 2-stage ring;
+//   warp 1      one thread issues the MMAs: S = Q K^T (128 x 128, fp32 in tensor memory, two buffers so
+//               that the scores of tile j+1 are computed while tile j is in the softmax), then
+//               O_j = P V (P from shared memory, V straight from the page layout as an MN-major operand);
+//   warps 2..5  softmax: a thread owns a query row (its tensor-memory lane), reads the scores with
+//               tcgen05.ld, masks by assignment, keeps the running maximum (from -inf) and sum in
+//               float32, writes P as bfloat16 into the swizzled operand tile, and folds every O_j into
+//               its float32 output row in registers with the usual rescaling.
+//
+// It replaces what the reference does with a gather on the host and a scalar FlashAttention kernel
+// (tinyinfer/layers/attention.py:60-81, tinyinfer/csrc/flash_attention.cu:5-234). Every mbarrier wait
+// is bounded (status word, abort flag, tensor memory freed on the common exit). Value rows that no
+// query of the CTA may see are zeroed in shared memory before the second product, so pages that
+// were never written or were given back cannot leak NaNs through 0 * NaN.
+#include "sm100_ptx.cuh"
+
+namespace {
+
+constexpr int QM = 128;              // query rows per CTA = accumulator lanes
+constexpr int KT = 128;              // keys per tile
+constexpr int KV_STAGES = 2;
+constexpr int PF_THREADS = 192;
+
+struct PrefillParams {
+    __nv_bfloat16* out;              // [T, Hq * D]
+    const int* tiles;                // int4 {request index, first flat row, rows (<= 128), first position}
+    const int* block_table;
+    int max_blocks, hq, hkv, page_size, num_pages, window;
+    float scale_log2;
+    int* status;
+};
+
+template <int D>
+struct PfSmem {
+    static constexpr int HALVES = D / 64;
+    static constexpr int Q_BYTES = HALVES * QM * 128;
+    static constexpr int KV_TILE = HALVES * KT * 128;         // keys OR values of a tile
+    static constexpr int STAGE = 2 * KV_TILE;
+    static constexpr int P_BYTES = (KT / 64) * QM * 128;
+    static constexpr int BYTES = 1024 + Q_BYTES + KV_STAGES * STAGE + P_BYTES + 256;
+    static constexpr int TMEM_COLS = 512;                     // S0 at 0, S1 at 128, O_j at 256
+};
+
+__device__ __forceinline__ float ex2(float x) {          // 2^x, flushing; inputs are <= 0 or -inf
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                            const PrefillParams p) {
+    using S = PfSmem<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_tile = smem;
+    uint8_t* kv_ring = smem + S::Q_BYTES;
+    uint8_t* p_tile = kv_ring + KV_STAGES * S::STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + S::P_BYTES);
+    const uint32_t bar0 = smem_u32(bars);
+    // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, o_full
+    const uint32_t q_full = bar0;
+    auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto kv_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+    auto s_full = [&](int b) { return bar0 + 8u * (5 + b); };
+    auto s_empty = [&](int b) { return bar0 + 8u * (7 + b); };
+    const uint32_t p_full = bar0 + 8u * 9, o_full = bar0 + 8u * 10;
+    __shared__ uint32_t tmem_base_sh;
+    __shared__ int abort_sh;
+    volatile int* abort_flag = &abort_sh;
+
+    ti_grid_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        abort_sh = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+            mbar_init(s_full(s), 1);
+            mbar_init(s_empty(s), 4);
+        }
+        mbar_init(p_full, 4);
+        mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&tmem_base_sh, S::TMEM_COLS);
+    tmem_fence_before();
+    __syncthreads();
+    tmem_fence_after();
+    const uint32_t tmem_base = tmem_base_sh;
+    ti_grid_wait();                                     // q, the pages and the tables come from earlier kernels
+
+    const int4 td = reinterpret_cast<const int4*>(p.tiles)[blockIdx.x];
+    const int seq = td.x, row0 = td.y, nrows = td.z, pos0 = td.w;
+    const int head = blockIdx.y;
+    const int kvh = head / (p.hq / p.hkv);
+    const int hi = pos0 + nrows;                                   // one past the last key any query sees
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0; // first key the first query sees
+    const int tile0 = lo / KT, tile1 = (hi + KT - 1) / KT;
+    const int num_tiles = tile1 - tile0;
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(q_full, S::Q_BYTES);
+#pragma unroll
+            for (int hh = 0; hh < S::HALVES; ++hh)
+                tma_load_2d(smem_u32(q_tile) + hh * (QM * 128), &q_map, q_full, head * D + hh * 64, row0);
+            const int piece_rows = p.page_size < 64 ? p.page_size : 64;
+            const int pieces = KT / piece_rows;
+            for (int j = 0; j < num_tiles; ++j) {
+                const int s = j % KV_STAGES;
+                if (!mbar_wait(kv_empty(s), ((j / KV_STAGES) & 1u) ^ 1u, abort_flag, p.status, 31)) break;
+                const int t = tile0 + j;
+                uint32_t bytes = 0;
+                for (int i = 0; i < pieces; ++i) {
+                    const int logical = (t * KT + i * piece_rows) / p.page_size;
+                    const int page = logical < p.max_blocks ? table[logical] : -1;
+                    if (page >= 0 && page < p.num_pages) bytes += (uint32_t)piece_rows * 128u * S::HALVES * 2u;
+                }
+                mbar_expect_tx(kv_full(s), bytes);
+                const uint32_t stage = smem_u32(kv_ring + s * S::STAGE);
+                for (int i = 0; i < pieces; ++i) {
+                    const int tok = t * KT + i * piece_rows;
+                    const int logical = tok / p.page_size;
+                    const int page = logical < p.max_blocks ? table[logical] : -1;
+                    if (page < 0 || page >= p.num_pages) continue;      // never written, or given back by a window
+                    const int off = tok % p.page_size;
+                    const int krow = (page * p.hkv + kvh) * p.page_size + off;
+                    const int vrow = ((p.num_pages + page) * p.hkv + kvh) * p.page_size + off;
+#pragma unroll
+                    for (int hh = 0; hh < S::HALVES; ++hh) {
+                        const uint32_t dst = stage + hh * (KT * 128) + i * piece_rows * 128;
+                        tma_load_2d(dst, &kv_map, kv_full(s), hh * 64, krow);
+                        tma_load_2d(dst + S::KV_TILE, &kv_map, kv_full(s), hh * 64, vrow);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc(QM, KT);               // S = Q K^T: both operands K-major
+            constexpr uint32_t idesc_o = make_idesc(QM, D, true);          // O = P V: V is MN-major (features contiguous)
+            const uint32_t q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
+            bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 32);
+            auto issue_s = [&](int j) {                                    // scores of tile j into buffer j % 2
+                const int s = j % KV_STAGES, b = j & 1;
+                if (!mbar_wait(kv_full(s), (j / KV_STAGES) & 1u, abort_flag, p.status, 33)) return false;
+                if (!mbar_wait(s_empty(b), ((j >> 1) & 1u) ^ 1u, abort_flag, p.status, 34)) return false;
+                tmem_fence_after();
+                const uint32_t k_addr = smem_u32(kv_ring + s * S::STAGE);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * (QM * 128) + (ks & 3) * 32;     // half, then 32 bytes a step
+                    umma_bf16(tmem_base + b * KT, make_sw128_desc(q_addr + off), make_sw128_desc(k_addr + off),
+                              idesc_s, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full(b));
+                return true;
+            };
+            if (ok && num_tiles > 0) ok = issue_s(0);
+            for (int j = 0; j < num_tiles && ok; ++j) {
+                if (j + 1 < num_tiles) ok = issue_s(j + 1);
+                if (!ok) break;
+                if (!mbar_wait(p_full, j & 1u, abort_flag, p.status, 35)) { ok = false; break; }
+                tmem_fence_after();
+                const int s = j % KV_STAGES;
+                const uint32_t v_addr = smem_u32(kv_ring + s * S::STAGE) + S::KV_TILE;
+#pragma unroll
+                for (int ks = 0; ks < KT / 16; ++ks) {
+                    // A: 16 keys = 32 bytes along the swizzled row of P; B: 16 key rows of V = 2048 bytes
+                    const uint64_t adesc = make_sw128_desc(p_addr + (ks >> 2) * (QM * 128) + (ks & 3) * 32);
+                    const uint64_t bdesc = make_sw128_desc_mn(v_addr + ks * 16 * 128, KT * 128, 1024);
+                    umma_bf16(tmem_base + 2 * KT, adesc, bdesc, idesc_o, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(o_full);             // O_j is complete (and P and this stage have been read)
+                umma_commit(kv_empty(s));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax and output (warps 2..5)
+        const int lane_group = warp & 3;
+        const int r = lane_group * 32 + lane;                          // query row of the tile = tensor-memory lane
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
+        const int qpos = pos0 + r;
+        const int etid = threadIdx.x - 64;
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < num_tiles && ok; ++j) {
+            const int b = j & 1, s = j % KV_STAGES;
+            const int tk0 = (tile0 + j) * KT;
+            if (!mbar_wait(s_full(b), (j >> 1) & 1u, abort_flag, p.status, 36)) { ok = false; break; }
+            tmem_fence_after();
+            // Columns of this tile the row may see: kmin < column <= kmax (tile-local). A chunk of 32
+            // columns inside that range needs no per-element test, one outside it no arithmetic at all.
+            const int kmax = qpos - tk0;
+            const int kmin = p.window > 0 ? qpos - p.window - tk0 : -1;
+            // the same bounds for the warp's first and last row: the choice per chunk must be the
+            // same for the whole warp, because tcgen05.ld is a warp-wide instruction
+            const int wmax0 = pos0 + lane_group * 32 - tk0, wmax1 = wmax0 + 31;
+            const int wmin0 = p.window > 0 ? wmax0 - p.window : -1, wmin1 = p.window > 0 ? wmax1 - p.window : -1;
+            float v[32];
+            // pass 1: the row maximum of the visible scores (raw; the scale is positive)
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < KT; c += 32) {
+                if (c > wmax1 || c + 31 <= wmin0) continue;
+                tmem_ld32(lane_addr + b * KT + c, v);
+                if (c + 31 <= wmax0 && c > wmin1) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c + i <= kmax && c + i > kmin) ? v[i] : -INFINITY);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = ex2(m_run - m_use);
+            m_run = m_new;
+            // fold the previous tile's product into the output row, rescaled for the new maximum;
+            // this also means P and the O buffer of tensor memory are free again
+            if (j > 0) {
+                if (!mbar_wait(o_full, (j - 1) & 1u, abort_flag, p.status, 37)) { ok = false; break; }
+                tmem_fence_after();
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    tmem_ld32(lane_addr + 2 * KT + c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c + i] = (o[c + i] + v[i]) * corr;
+                }
+            }
+            l_run *= corr;
+            // value rows no query may see: zero them once the tile has landed (first and last tiles only)
+            if (tk0 < lo || tk0 + KT > hi) {
+                if (!mbar_wait(kv_full(s), (j / KV_STAGES) & 1u, abort_flag, p.status, 38)) { ok = false; break; }
+                uint8_t* v_tile = kv_ring + s * S::STAGE + S::KV_TILE;
+                for (int idx = etid; idx < KT * (D / 8); idx += 128) {
+                    const int row = idx / (D / 8), chunk = idx % (D / 8);
+                    if (row >= lo - tk0 && row < hi - tk0) continue;
+                    *reinterpret_cast<uint4*>(v_tile + (chunk >> 3) * (KT * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) =
+                        make_uint4(0, 0, 0, 0);
+                }
+            }
+            // pass 2: probabilities, their sum, and P as the bfloat16 operand tile (row r, 128-byte swizzle)
+#pragma unroll
+            for (int c = 0; c < KT; c += 32) {
+                const bool none = c > wmax1 || c + 31 <= wmin0;
+                if (none) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                } else {
+                    tmem_ld32(lane_addr + b * KT + c, v);
+                    if (c + 31 <= wmax0 && c > wmin1) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            v[i] = ex2(fmaf(v[i], p.scale_log2, -m_use));
+                            l_run += v[i];
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            v[i] = (c + i <= kmax && c + i > kmin) ? ex2(fmaf(v[i], p.scale_log2, -m_use)) : 0.f;
+                            l_run += v[i];
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) {                     // 8 keys = one 16-byte chunk
+                    const int chunk = ((c & 63) >> 3) + q8;
+                    uint4 w;
+                    w.x = pack2(v[q8 * 8], v[q8 * 8 + 1]);
+                    w.y = pack2(v[q8 * 8 + 2], v[q8 * 8 + 3]);
+                    w.z = pack2(v[q8 * 8 + 4], v[q8 * 8 + 5]);
+                    w.w = pack2(v[q8 * 8 + 6], v[q8 * 8 + 7]);
+                    *reinterpret_cast<uint4*>(p_tile + (c >> 6) * (QM * 128) + r * 128 + ((chunk ^ (r & 7)) << 4)) = w;
+                }
+            }
+            tmem_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P and the zeroed rows are read by the MMA
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_empty(b));
+                mbar_arrive(p_full);
+            }
+        }
+        if (ok && num_tiles > 0) {
+            if (mbar_wait(o_full, (num_tiles - 1) & 1u, abort_flag, p.status, 39)) {
+                tmem_fence_after();
+                float v[32];
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+                __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.hq + head) * D;
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    tmem_ld32(lane_addr + 2 * KT + c, v);
+                    if (r < nrows) {
+#pragma unroll
+                        for (int q8 = 0; q8 < 4; ++q8) {
+                            uint4 w;
+                            w.x = pack2((o[c + q8 * 8] + v[q8 * 8]) * inv, (o[c + q8 * 8 + 1] + v[q8 * 8 + 1]) * inv);
+                            w.y = pack2((o[c + q8 * 8 + 2] + v[q8 * 8 + 2]) * inv, (o[c + q8 * 8 + 3] + v[q8 * 8 + 3]) * inv);
+                            w.z = pack2((o[c + q8 * 8 + 4] + v[q8 * 8 + 4]) * inv, (o[c + q8 * 8 + 5] + v[q8 * 8 + 5]) * inv);
+                            w.w = pack2((o[c + q8 * 8 + 6] + v[q8 * 8 + 6]) * inv, (o[c + q8 * 8 + 7] + v[q8 * 8 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(dst + c + q8 * 8) = w;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- common exit
+    tmem_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tmem_fence_after();
+        tmem_dealloc(tmem_base, S::TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+TI_API int ti_attention_prefill_tile_rows() { return QM; }
+
+// Prefill attention on tcgen05. `tiles`: num_tiles int4 {request index in the step, first flat row,
+// rows (<= 128), position of the first row}, every tile inside one request's portion. q [T, Hq, D],
+// out [T, Hq * D], kv_cache [2, num_pages, Hkv, page_size, D]; page_size 16, 32 or a multiple of 64.
+TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
+                                        int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
+                                        int page_size, int num_pages, float scale, int window, int* status,
+                                        cudaStream_t stream) {
+    TI_REQUIRE(d == 64 || d == 128, "attention_prefill_tc: head_dim %d is not 64 or 128", d);
+    TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0 && hq <= 65535, "attention_prefill_tc: bad head counts");
+    TI_REQUIRE(page_size == 16 || page_size == 32 || page_size % 64 == 0, "attention_prefill_tc: page size %d", page_size);
+    TI_REQUIRE(num_tiles >= 0 && num_tokens > 0, "attention_prefill_tc: bad sizes");
+    if (num_tiles == 0) return 0;
+    CUtensorMap q_map, kv_map;
+    if (!ti_get_bf16_map(q, num_tokens, hq * d, QM, &q_map)) return -1;
+    if (!ti_get_bf16_map(kv_cache, 2ll * num_pages * hkv * page_size, d, page_size < 64 ? page_size : 64, &kv_map)) return -1;
+    PrefillParams p;
+    p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    dim3 grid(num_tiles, hq);
+    if (d == 128) {
+        static bool once = false;
+        if (!once) {
+            cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<128>::BYTES);
+            TI_REQUIRE(e == cudaSuccess, "attention_prefill_tc: shared memory: %s", cudaGetErrorString(e));
+            once = true;
+        }
+        ti_launch(prefill_attention_tc_kernel<128>, grid, PF_THREADS, PfSmem<128>::BYTES, stream, q_map, kv_map, p);
+    } else {
+        static bool once = false;
+        if (!once) {
+            cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<64>::BYTES);
+            TI_REQUIRE(e == cudaSuccess, "attention_prefill_tc: shared memory: %s", cudaGetErrorString(e));
+            once = true;
+        }
+        ti_launch(prefill_attention_tc_kernel<64>, grid, PF_THREADS, PfSmem<64>::BYTES, stream, q_map, kv_map, p);
+    }
+    TI_CHECK_LAUNCH("attention_prefill_tc");
+    return 0;
+}

@@ -77,7 +77,7 @@ class BatchBuffers:
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
         self.max_blocks, self.num_groups = max_blocks, num_groups
         words = (3 * max_tokens + 4 * max_seqs + 1 + max_tokens + num_groups * max_seqs * max_blocks
-                 + max_seqs + 4 * (max_tokens // 64 + max_seqs) + 128)
+                 + max_seqs + 4 * (max_tokens // 64 + max_seqs) + 128)   # tiles: at most one per 64 tokens plus one per request
         self.host = torch.empty(words, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self.dev = torch.empty(words, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)

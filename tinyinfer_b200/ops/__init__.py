@@ -49,11 +49,11 @@ _SIGNATURES["sm100"] = {
 _SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
-_SIGNATURES["sm100"]["ti_attention_prefill_bf16"] = [
-    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+_SIGNATURES["sm100"]["ti_attention_prefill_tc_bf16"] = [
+    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
     c_float, c_int, c_void_p, c_void_p]
 DECODE_CHUNK = 256        # keys per split of the decode attention kernel
-PREFILL_TILE = 64         # query rows per CTA of the prefill attention kernel
+PREFILL_TILE = 128        # query rows per CTA of the prefill attention kernel
 _bound = {}
 _status = {}
 
@@ -384,8 +384,8 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
              token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), splits, kstatus, _stream())
     if num_tiles:
-        _run("sm100", "ti_attention_prefill_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
-             tiles.data_ptr(), num_tiles, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
+        _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+             tiles.data_ptr(), num_tiles, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), kstatus, _stream())
     return out
 
