@@ -6,10 +6,11 @@
 //   warp 1      one thread issues the MMAs: S = Q K^T (128 x 128, fp32 in tensor memory, two buffers so
 //               that the scores of tile j+1 are computed while tile j is in the softmax), then
 //               O_j = P V (P from shared memory, V straight from the page layout as an MN-major operand);
-//   warps 2..5  softmax: a thread owns a query row (its tensor-memory lane), reads the scores with
-//               tcgen05.ld, masks by assignment, keeps the running maximum (from -inf) and sum in
-//               float32, writes P as bfloat16 into the swizzled operand tile, and folds every O_j into
-//               its float32 output row in registers with the usual rescaling.
+//   warps 2..9  softmax: two threads share a query row (its tensor-memory lane), each half of the keys
+//               and of the output features; they read the scores with tcgen05.ld, mask by assignment,
+//               keep the running maximum (from -inf) and sum in float32, write P as bfloat16 into the
+//               swizzled operand tile, and fold every O_j into their float32 output row in registers
+//               with the usual rescaling.
 //
 // It replaces what the reference does with a gather on the host and a scalar FlashAttention kernel
 // (tinyinfer/layers/attention.py:60-81, tinyinfer/csrc/flash_attention.cu:5-234). Every mbarrier wait
@@ -23,7 +24,7 @@ namespace {
 constexpr int QM = 128;              // query rows per CTA = accumulator lanes
 constexpr int KT = 128;              // keys per tile
 constexpr int KV_STAGES = 2;
-constexpr int PF_THREADS = 192;
+constexpr int PF_THREADS = 320;      // TMA warp, MMA warp, eight softmax warps
 
 struct PrefillParams {
     __nv_bfloat16* out;              // [T, Hq * D]
@@ -75,6 +76,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     auto s_empty = [&](int b) { return bar0 + 8u * (7 + b); };
     const uint32_t p_full = bar0 + 8u * 9, o_full = bar0 + 8u * 10;
     __shared__ uint32_t tmem_base_sh;
+    __shared__ float max_xch[2][2][QM];      // [tile parity][column half][row]: row maxima of the halves
+    __shared__ float sum_xch[2][QM];
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
 
@@ -87,9 +90,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
             mbar_init(s_full(s), 1);
-            mbar_init(s_empty(s), 4);
+            mbar_init(s_empty(s), 8);
         }
-        mbar_init(p_full, 4);
+        mbar_init(p_full, 8);
         mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -190,15 +193,20 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             }
         }
     } else {
-        // ------------------------------------------------------------ softmax and output (warps 2..5)
+        // ------------------------------------------------------------ softmax and output (warps 2..9)
+        // Two warps share a quarter of the rows (their tensor-memory lanes) and split the columns:
+        // `half` 0 owns keys 0..63 of every tile and output features 0..D/2-1, half 1 the rest.
+        // The row maximum goes through shared memory once per tile; the row sums meet at the end.
         const int lane_group = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = lane_group * 32 + lane;                          // query row of the tile = tensor-memory lane
         const uint32_t lane_addr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
         const int qpos = pos0 + r;
-        const int etid = threadIdx.x - 64;
-        float o[D];
+        const int etid = threadIdx.x - 64;                             // 0..255 among the softmax threads
+        constexpr int KH = KT / 2, DH = D / 2;                         // this thread's share of keys and features
+        float o[DH];
 #pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        for (int i = 0; i < DH; ++i) o[i] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < num_tiles && ok; ++j) {
@@ -218,7 +226,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             // pass 1: the row maximum of the visible scores (raw; the scale is positive)
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < KT; c += 32) {
+            for (int cc = 0; cc < KH; cc += 32) {
+                const int c = half * KH + cc;
                 if (c > wmax1 || c + 31 <= wmin0) continue;
                 tmem_ld32(lane_addr + b * KT + c, v);
                 if (c + 31 <= wmax0 && c > wmin1) {
@@ -229,6 +238,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c + i <= kmax && c + i > kmin) ? v[i] : -INFINITY);
                 }
             }
+            max_xch[b][half][r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + lane_group) : "memory");     // the two warps of this row quarter
+            mx = fmaxf(mx, max_xch[b][half ^ 1][r]);
             const float m_new = fmaxf(m_run, mx * p.scale_log2);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float corr = ex2(m_run - m_use);
@@ -239,8 +251,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 if (!mbar_wait(o_full, (j - 1) & 1u, abort_flag, p.status, 37)) { ok = false; break; }
                 tmem_fence_after();
 #pragma unroll
-                for (int c = 0; c < D; c += 32) {
-                    tmem_ld32(lane_addr + 2 * KT + c, v);
+                for (int c = 0; c < DH; c += 32) {
+                    tmem_ld32(lane_addr + 2 * KT + half * DH + c, v);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[c + i] = (o[c + i] + v[i]) * corr;
                 }
@@ -250,7 +262,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             if (tk0 < lo || tk0 + KT > hi) {
                 if (!mbar_wait(kv_full(s), (j / KV_STAGES) & 1u, abort_flag, p.status, 38)) { ok = false; break; }
                 uint8_t* v_tile = kv_ring + s * S::STAGE + S::KV_TILE;
-                for (int idx = etid; idx < KT * (D / 8); idx += 128) {
+                for (int idx = etid; idx < KT * (D / 8); idx += 256) {
                     const int row = idx / (D / 8), chunk = idx % (D / 8);
                     if (row >= lo - tk0 && row < hi - tk0) continue;
                     *reinterpret_cast<uint4*>(v_tile + (chunk >> 3) * (KT * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) =
@@ -259,7 +271,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             }
             // pass 2: probabilities, their sum, and P as the bfloat16 operand tile (row r, 128-byte swizzle)
 #pragma unroll
-            for (int c = 0; c < KT; c += 32) {
+            for (int cc = 0; cc < KH; cc += 32) {
+                const int c = half * KH + cc;
                 const bool none = c > wmax1 || c + 31 <= wmin0;
                 if (none) {
 #pragma unroll
@@ -303,11 +316,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             if (mbar_wait(o_full, (num_tiles - 1) & 1u, abort_flag, p.status, 39)) {
                 tmem_fence_after();
                 float v[32];
-                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-                __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.hq + head) * D;
+                sum_xch[half][r] = l_run;
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + lane_group) : "memory");
+                const float l_all = l_run + sum_xch[half ^ 1][r];
+                const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+                __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.hq + head) * D + half * DH;
 #pragma unroll
-                for (int c = 0; c < D; c += 32) {
-                    tmem_ld32(lane_addr + 2 * KT + c, v);
+                for (int c = 0; c < DH; c += 32) {
+                    tmem_ld32(lane_addr + 2 * KT + half * DH + c, v);
                     if (r < nrows) {
 #pragma unroll
                         for (int q8 = 0; q8 < 4; ++q8) {
