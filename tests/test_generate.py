@@ -133,3 +133,33 @@ def test_command_line(tmp_path):
     check_greedy(folder, [5, 17, 3, 200], rows[0]["token_ids"], 5e-5)
     bad = subprocess.run(cmd + ["--speculative"], capture_output=True, text=True, timeout=600)
     assert bad.returncode != 0 and "does not build" in bad.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 3e-2)])
+def test_page_pressure_waits_and_preempts_but_gives_the_same_tokens(tmp_path, dtype, tol):
+    """With so few pages that prompts wait and a running request is preempted and recomputed, every
+    request still gets the tokens it gets with plenty of pages (greedy, checked by teacher forcing)."""
+    from tinyinfer_b200 import LLM
+    cfg = helpers.TINY["C"]
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=5, dtype=dtype)
+    requests = helpers.random_requests(cfg, [60, 45, 70, 30, 55, 20], seed=9)
+    prompts = list(requests.values())
+    params = SamplingParams(greedy=True, max_tokens=40)
+    roomy = LLM(folder, dtype=dtype, max_num_batched_tokens=64, max_num_seqs=4, kvcache_block_size=16,
+                num_kvcache_blocks=64, prefill_chunk=32, max_model_len=160)
+    want = roomy.generate(prompts, params)
+    assert roomy.scheduler.num_preemptions == 0
+    tight = LLM(folder, dtype=dtype, max_num_batched_tokens=64, max_num_seqs=4, kvcache_block_size=16,
+                num_kvcache_blocks=14, prefill_chunk=32, max_model_len=160)
+    got = tight.generate(prompts, params)
+    assert tight.scheduler.num_preemptions > 0, "the pool was not tight enough to preempt"
+    assert all(o["finish_reason"] == "max_tokens" and len(o["token_ids"]) == 40 for o in got)
+    assert sum(o["statistics"]["preemptions"] for o in got) == tight.scheduler.num_preemptions
+    for p, o in zip(prompts, got):
+        check_greedy(folder, p, o["token_ids"], tol)
+    same = sum(a["token_ids"] == b["token_ids"] for a, b in zip(want, got))
+    assert same >= len(prompts) - 1          # a near-tie may flip under another batching
+    tight.runner.check_status()
+    tight.runner.manager.check_consistency()
+    assert not tight.runner.manager.live_requests
