@@ -56,8 +56,13 @@ def test_generate_with_plain_ops_on_cpu(tmp_path, monkeypatch):
     cfg = helpers.TINY_A
     folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=3)
     llm = llm_mod.LLM(folder, dtype="float32", device="cpu", max_num_batched_tokens=24, max_num_seqs=3,
-                      kvcache_block_size=4, num_kvcache_blocks=30, prefill_chunk=8, max_model_len=128)
-    generate_and_check(llm, folder, cfg, 1e-5)
+                      kvcache_block_size=4, num_kvcache_blocks=30, prefill_chunk=8, max_model_len=128, track_nll=True)
+    prompts, outs = generate_and_check(llm, folder, cfg, 1e-5)
+    # the perplexity statistic: exp of the mean NLL of the generated tokens under the plain model
+    pcfg, w = plain.read_model_folder(folder, torch.float64)
+    logp = torch.log_softmax(plain.forward(pcfg, w, prompts[2] + outs[2]["token_ids"]), dim=-1)
+    nll = -sum(float(logp[len(prompts[2]) - 1 + i, t]) for i, t in enumerate(outs[2]["token_ids"]))
+    assert abs(outs[2]["statistics"]["perplexity"] - np.exp(nll / 8)) < 1e-3 * np.exp(nll / 8)
     assert llm.runner.manager.stats()["groups"][0]["pages_taken"] > 30
 
 

@@ -307,3 +307,9 @@ def test_sampling_distribution_and_topk(ops):
     draws = ops.sample(logits, temp, topk, zeros, seed, zeros, step).cpu().numpy()
     allowed = set(torch.topk(row[0], k).indices.tolist())
     assert set(draws.tolist()) <= allowed and len(set(draws.tolist())) == k
+
+
+def test_token_nll(ops):
+    logits = rnd(7, 1003, dtype=torch.float32, std=3.0)
+    tokens = torch.tensor([0, 1002, 5, 500, 77, 3, 999], dtype=torch.int32, device=dev())
+    torch.testing.assert_close(ops.token_nll(logits, tokens), ref.token_nll(logits, tokens), rtol=1e-5, atol=1e-5)

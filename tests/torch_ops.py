@@ -120,9 +120,14 @@ def sample(logits, temperature, topk, greedy, seed, stream_id, step):
     return torch.tensor(out, dtype=torch.int32, device=logits.device)
 
 
+def token_nll(logits, tokens):
+    x = logits.double()
+    return (torch.logsumexp(x, dim=-1) - x.gather(1, tokens.long()[:, None])[:, 0]).float()
+
+
 def launch_count():
     return 0
 
 
 ALL = ["embedding", "rmsnorm", "add", "linear", "gated_linear", "qk_norm_rope_append",
-       "paged_attention", "argmax", "sample", "launch_count"]
+       "paged_attention", "argmax", "sample", "token_nll", "launch_count"]

@@ -20,6 +20,7 @@ class EngineConfig:
     seed: int = 0                           # base of the sampling streams
     eos_token_id: int = -1                  # -1: taken from the model's configuration, if any
     cuda_graphs: bool = True                # replay captured decode steps
+    track_nll: bool = False                 # sum each request's token NLL (the perplexity statistic)
     device: str = "cuda:0"
 
     def validate(self) -> None:

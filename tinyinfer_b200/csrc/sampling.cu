@@ -214,3 +214,33 @@ TI_API int ti_argmax(int* out, const float* logits, int num_rows, int vocab, flo
     TI_CHECK_LAUNCH("argmax");
     return 0;
 }
+
+// ------------------------------------------------------------------ negative log-likelihood
+// nll[row] = logsumexp(logits[row]) - logits[row][token[row]] in float32
+// (tinyinfer/layers/sampler.py:82-86 of the reference): what the perplexity statistic sums.
+__global__ void __launch_bounds__(SP_THREADS) nll_kernel(float* __restrict__ out, const float* __restrict__ logits,
+                                                         const int* __restrict__ tokens, int vocab) {
+    __shared__ float red[33];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int row = blockIdx.x;
+    const float* x = logits + (size_t)row * vocab;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < vocab; i += SP_THREADS) mx = fmaxf(mx, x[i]);
+    mx = block_max(mx, red);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += SP_THREADS) sum += expf(x[i] - mx);
+    sum = block_sum(sum, red);
+    if (threadIdx.x == 0) {
+        const int t = tokens[row];
+        out[row] = (t >= 0 && t < vocab) ? mx + logf(sum) - x[t] : 0.f;
+    }
+}
+
+TI_API int ti_token_nll(float* out, const float* logits, const int* tokens, int num_rows, int vocab, cudaStream_t stream) {
+    TI_REQUIRE(num_rows >= 0 && vocab > 0, "token_nll: bad sizes");
+    if (num_rows == 0) return 0;
+    ti_launch(nll_kernel, num_rows, SP_THREADS, 0, stream, out, logits, tokens, vocab);
+    TI_CHECK_LAUNCH("token_nll");
+    return 0;
+}

@@ -97,7 +97,12 @@ class LLM:
         sampling = [it for it in items if it.sample_after]
         tokens = self.sampler.sample(
             logits, [it.seq.sampling_params for it in sampling],
-            [it.seq.seq_id for it in sampling], [it.seq.num_completion_tokens for it in sampling])
+            [it.seq.seq_id for it in sampling], [it.seq.num_completion_tokens for it in sampling],
+            with_nll=self.config.track_nll)
+        if self.config.track_nll:
+            tokens, nlls = tokens
+            for it, nll in zip(sampling, nlls):
+                it.seq.sum_nll += nll
         self.scheduler.postprocess(items, {it.seq.seq_id: tok for it, tok in zip(sampling, tokens)})
         return items
 

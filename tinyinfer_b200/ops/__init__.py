@@ -40,6 +40,7 @@ _SIGNATURES = {
         "ti_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p],
         "ti_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "ti_token_nll": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
 }
 _SIGNATURES["sm100"] = {
@@ -430,6 +431,18 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, topk: torch.Tensor, 
     _run("core", "ti_sample", out.data_ptr(), logits.data_ptr(), n, logits.shape[1],
          temperature.data_ptr(), topk.data_ptr(), greedy.data_ptr(), seed.data_ptr(),
          stream_id.data_ptr(), step.data_ptr(), _stream())
+    return out
+
+
+def token_nll(logits: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """logsumexp(logits[row]) - logits[row, tokens[row]] in float32, [N]."""
+    _check(logits, "logits", torch.float32, 2)
+    _check(tokens, "tokens", torch.int32, 1)
+    if tokens.shape[0] != logits.shape[0]:
+        raise KernelError("token_nll: one token per row")
+    out = torch.empty((logits.shape[0],), dtype=torch.float32, device=logits.device)
+    _run("core", "ti_token_nll", out.data_ptr(), logits.data_ptr(), tokens.data_ptr(), logits.shape[0],
+         logits.shape[1], _stream())
     return out
 
 
