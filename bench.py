@@ -252,7 +252,8 @@ def main() -> int:
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": args.batch * 4, "ms_per_step": max(e2e_ms, wall_ms) / args.steps}
 
     out = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, random weights)", "value": head["tok_s"],
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.model_size.upper()} shape, random weights)",
+        "value": head["tok_s"],
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
@@ -261,7 +262,8 @@ def main() -> int:
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.resolved_head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "seq_len": ctx_len, "prefill_tokens": len(prompt),
-                   "page_size": page, "parallelism": "single-gpu", "l2": "inputs>L2 (weights 15 GB)",
+                   "page_size": page, "parallelism": "single-gpu",
+                   "l2": f"inputs>L2 (weights {numbers['weight_bytes'] / 1e9:.1f} GB read per step)",
                    "cache_fill": "random for device-timed decode, real prefill for e2e"},
         "clocks": head["clocks"], "e2e": e2e, "gpu_launches": head["launches"],
         "prefill": prefill, "roofline": roofline, "points": points,

@@ -4,7 +4,9 @@ printed figures of the reference's benchmarks/benchmark_throughput.py:12-20,50-7
 (output_tokens_per_s, computed_plus_output_tokens_per_s, requests_per_s, TTFT and TPOT per
 request). The reference's workloads are text prompts (benchmarks/workloads.py); here seeded
 random token ids of the same length classes stand in: short (32-64 tokens), long_prefill
-(2-4 K tokens), shared_prefix (a common 512-token head and short tails)."""
+(2-4 K tokens), shared_prefix (a common 512-token head and short tails). A fourth workload,
+mixed, is a continuous-batching mix: prompts of 16-1024 tokens, 16-512 generated tokens each, half
+of the requests greedy and half at temperature 0.7."""
 import argparse
 import json
 import os
@@ -31,14 +33,20 @@ def workload(name, vocab, rng, n):
 def main():
     ap = argparse.ArgumentParser()
     add_engine_options(ap)
-    ap.add_argument("--workload", choices=["short", "long_prefill", "shared_prefix"], default="short")
+    ap.add_argument("--workload", choices=["short", "long_prefill", "shared_prefix", "mixed"], default="short")
     ap.add_argument("--num-requests", type=int, default=16)
     ap.add_argument("--max-tokens", type=int, default=128)
     args = ap.parse_args()
     llm = build_llm(args)
     rng = random.Random(args.seed)
-    prompts = workload(args.workload, llm.model.spec.vocab_size, rng, args.num_requests)
-    params = SamplingParams(greedy=True, max_tokens=args.max_tokens, ignore_eos=True)
+    vocab = llm.model.spec.vocab_size
+    if args.workload == "mixed":
+        prompts = [[rng.randrange(vocab) for _ in range(rng.randint(16, 1024))] for _ in range(args.num_requests)]
+        params = [SamplingParams(greedy=i % 2 == 0, temperature=0.7, topk=100, max_tokens=rng.randint(16, 512),
+                                 ignore_eos=True, seed=i) for i in range(args.num_requests)]
+    else:
+        prompts = workload(args.workload, vocab, rng, args.num_requests)
+        params = SamplingParams(greedy=True, max_tokens=args.max_tokens, ignore_eos=True)
     llm.generate(prompts[:1], SamplingParams(greedy=True, max_tokens=2, ignore_eos=True))   # warm-up
     t0 = time.perf_counter()
     outs = llm.generate(prompts, params)
@@ -46,7 +54,8 @@ def main():
     out_tokens = sum(len(o["token_ids"]) for o in outs)
     prompt_tokens = sum(len(p) for p in prompts)
     print(json.dumps({
-        "workload": args.workload, "requests": len(prompts), "wall_s": wall,
+        "workload": args.workload, "requests": len(prompts), "wall_s": wall, "steps": llm.runner.steps_run,
+        "graph_replays": llm.runner.graph_replays, "preemptions": llm.scheduler.num_preemptions,
         "output_tokens_per_s": out_tokens / wall,
         "computed_plus_output_tokens_per_s": (prompt_tokens + out_tokens) / wall,
         "requests_per_s": len(prompts) / wall,

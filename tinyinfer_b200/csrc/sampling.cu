@@ -7,7 +7,8 @@
 // depends only on (seed, stream, step) and its logits, whatever else is in the batch.
 #include "common.cuh"
 
-constexpr int SP_THREADS = 256;
+constexpr int SP_THREADS = 256;      // argmax parts, nll
+constexpr int SK_THREADS = 1024;     // the one-block-per-row sampling kernel: a row is 150 thousand logits
 
 __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
 #pragma unroll
@@ -61,11 +62,52 @@ __device__ __forceinline__ Best block_best(Best x, Best* sh) {
     return sh[0];
 }
 
-__global__ void __launch_bounds__(SP_THREADS) sample_kernel(
+// Block-wide best for blocks of NT threads.
+template <int NT>
+__device__ __forceinline__ Best block_best_n(Best x, Best* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best y;
+        y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+        y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+        x = better(x, y);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) sh[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        Best y = lane < NT / 32 ? sh[lane] : Best{0.f, -1};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best z;
+            z.v = __shfl_xor_sync(0xffffffffu, y.v, o);
+            z.i = __shfl_xor_sync(0xffffffffu, y.i, o);
+            y = better(y, z);
+        }
+        if (lane == 0) sh[0] = y;
+    }
+    __syncthreads();
+    return sh[0];
+}
+
+// Calls f(value, index) for every logit of the row, four at a time where the row allows it.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* x, int vocab, F f) {
+    if ((((uintptr_t)x) & 15) == 0 && (vocab & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < vocab; i += SK_THREADS * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(x + i);
+            f(v.x, i); f(v.y, i + 1); f(v.z, i + 2); f(v.w, i + 3);
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += SK_THREADS) f(x[i], i);
+    }
+}
+
+__global__ void __launch_bounds__(SK_THREADS) sample_kernel(
     int* __restrict__ out, const float* __restrict__ logits, int vocab,
     const float* __restrict__ temperature, const int* __restrict__ topk, const int* __restrict__ greedy,
     const long long* __restrict__ seed, const int* __restrict__ stream_id, const int* __restrict__ step) {
-    __shared__ Best sh_best[SP_THREADS / 32];
+    __shared__ Best sh_best[SK_THREADS / 32];
     __shared__ unsigned hist[256];
     __shared__ unsigned sel_prefix, sel_remaining;
     ti_grid_launch_dependents();
@@ -75,11 +117,8 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(
 
     if (greedy == nullptr || greedy[row]) {
         Best b{0.f, -1};
-        for (int i = tid; i < vocab; i += SP_THREADS) {
-            const float v = x[i];
-            if (v == v) b = better(b, Best{v, i});
-        }
-        b = block_best(b, sh_best);
+        for_each_logit(x, vocab, [&](float v, int i) { if (v == v) b = better(b, Best{v, i}); });
+        b = block_best_n<SK_THREADS>(b, sh_best);
         if (tid == 0) out[row] = b.i < 0 ? 0 : b.i;
         return;
     }
@@ -92,16 +131,17 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(
         if (tid == 0) { sel_prefix = 0u; sel_remaining = (unsigned)k; }
         for (int pass = 0; pass < 4; ++pass) {
             const int shift = 24 - 8 * pass;
-            hist[tid] = 0u;
+            if (tid < 256) hist[tid] = 0u;
             __syncthreads();
             const unsigned prefix = sel_prefix;
             const unsigned mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-            for (int i = tid; i < vocab; i += SP_THREADS) {
-                const float v = x[i] / temp;
-                if (!(v == v)) continue;
-                const unsigned key = order_key(v);
-                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u);
-            }
+            for_each_logit(x, vocab, [&](float raw, int) {
+                const float v = raw / temp;
+                if (v == v) {
+                    const unsigned key = order_key(v);
+                    if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u);
+                }
+            });
             __syncthreads();
             if (tid == 0) {
                 unsigned remaining = sel_remaining;
@@ -121,22 +161,36 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(
     const uint2 key2 = make_uint2((unsigned)(seed[row] & 0xFFFFFFFFll), (unsigned)((unsigned long long)seed[row] >> 32));
     const unsigned c1 = (unsigned)step[row], c2 = (unsigned)stream_id[row];
     Best b{0.f, -1};
-    for (int blk = tid; blk * 4 < vocab; blk += SP_THREADS) {
+    const bool vec = (((uintptr_t)x) & 15) == 0 && (vocab & 3) == 0;
+    for (int blk = tid; blk * 4 < vocab; blk += SK_THREADS) {
+        float vals[4];
+        if (vec) {
+            const float4 q = *reinterpret_cast<const float4*>(x + blk * 4);
+            vals[0] = q.x; vals[1] = q.y; vals[2] = q.z; vals[3] = q.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) vals[j] = blk * 4 + j < vocab ? x[blk * 4 + j] : -INFINITY;
+        }
+        bool any = false;
+        float sc[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            sc[j] = vals[j] / temp;
+            const bool keep = blk * 4 + j < vocab && sc[j] == sc[j] && sc[j] != -INFINITY && order_key(sc[j]) >= threshold;
+            if (!keep) sc[j] = -INFINITY;
+            any |= keep;
+        }
+        if (!any) continue;                               // the random block is only drawn where something survives
         const uint4 r = philox4x32_10(make_uint4((unsigned)blk, c1, c2, 0u), key2);
         const unsigned words[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int i = blk * 4 + j;
-            if (i >= vocab) break;
-            const float v = x[i] / temp;
-            if (!(v == v) || v == -INFINITY) continue;
-            if (order_key(v) < threshold) continue;
-            const float u = philox_uniform(words[j]);
-            const float g = -logf(-logf(u));
-            b = better(b, Best{v + g, i});
+            if (sc[j] == -INFINITY) continue;
+            const float g = -logf(-logf(philox_uniform(words[j])));
+            b = better(b, Best{sc[j] + g, blk * 4 + j});
         }
     }
-    b = block_best(b, sh_best);
+    b = block_best_n<SK_THREADS>(b, sh_best);
     if (tid == 0) out[row] = b.i < 0 ? 0 : b.i;
 }
 
@@ -146,7 +200,7 @@ TI_API int ti_sample(int* out, const float* logits, int num_rows, int vocab, con
                      const int* step, cudaStream_t stream) {
     TI_REQUIRE(num_rows >= 0 && vocab > 0, "sample: bad sizes");
     if (num_rows == 0) return 0;
-    ti_launch(sample_kernel, num_rows, SP_THREADS, 0, stream, out, logits, vocab, temperature, topk, greedy, seed, stream_id, step);
+    ti_launch(sample_kernel, num_rows, SK_THREADS, 0, stream, out, logits, vocab, temperature, topk, greedy, seed, stream_id, step);
     TI_CHECK_LAUNCH("sample");
     return 0;
 }
