@@ -34,7 +34,9 @@ class CacheStorage:
             if need is None:
                 self.kv.append(None)
             else:
-                pages = manager.groups[manager.group_of_entry[entry]].pool.num_pages
+                # one page more than the pool hands out: the last one takes the keys of the padding rows
+                # that fill a decode batch up to the size of its captured graph (see dump_page)
+                pages = manager.groups[manager.group_of_entry[entry]].pool.num_pages + 1
                 shape = (2, pages, need.num_kv_heads, manager.page_size, need.head_dim)
                 t = torch.empty(shape, dtype=dtype, device=self.device)
                 # tests poison the pool: a read outside a request's own keys then shows as NaN
@@ -45,6 +47,11 @@ class CacheStorage:
             else:
                 self.state.append(torch.zeros((manager.max_requests, *state.shape),
                                               dtype=state.dtype, device=self.device))
+
+    @staticmethod
+    def dump_page(manager: CacheManager, group: int) -> int:
+        """The page id no request ever holds: padding rows write their keys and values there."""
+        return manager.groups[group].pool.num_pages
 
     def reset_state_slot(self, slot: int) -> None:
         for t in self.state:

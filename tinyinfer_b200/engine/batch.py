@@ -53,6 +53,7 @@ class StepContext:
     starts: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_context: int = 0
+    num_real_seqs: int = 0         # entries before the padding rows of a graph-sized batch
     # the attention kernels' split of the batch: rows of single decoded tokens, and tiles
     # [entry, first row, rows, first position] of prompt portions
     decode_rows: Optional[torch.Tensor] = None
@@ -86,11 +87,23 @@ class BatchBuffers:
         self.bytes_copied = 0              # host-to-device bytes of all steps so far
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
-              tables: Sequence[Sequence[Sequence[int]]], fixed_layout: bool = False) -> StepContext:
+              tables: Sequence[Sequence[Sequence[int]]], fixed_layout: bool = False,
+              pad_to: int = 0, pad_pages: Sequence[int] = ()) -> StepContext:
         """``starts[i]``: tokens entry i's request already holds; ``slots[i]``: its state slot;
         ``tables[g][i]``: its block table in cache group g. ``fixed_layout`` pads every block
         table to the widest possible, so that two steps with the same numbers of tokens and
-        requests put every array at the same address (what a captured CUDA graph needs)."""
+        requests put every array at the same address (what a captured CUDA graph needs).
+        ``pad_to`` fills the step up to that many requests with padding rows (token 0 at position 0
+        of a request whose only page is ``pad_pages[g]``, a page no real request holds), so that one
+        captured graph serves a range of batch sizes; their logits come last and are dropped."""
+        num_real = len(entries)
+        if pad_to > num_real:
+            extra = pad_to - num_real
+            entries = list(entries) + [StepEntry(("pad", i), [0], [0]) for i in range(extra)]
+            starts = list(starts) + [0] * extra
+            slots = list(slots) + [0] * extra
+            tables = [list(tables[g]) + [[pad_pages[g]] if g < len(pad_pages) else []] * extra
+                      for g in range(self.num_groups)]
         q_lens = [len(e.tokens) for e in entries]
         t, s = sum(q_lens), len(entries)
         if t > self.max_tokens or s > self.max_seqs:
@@ -158,4 +171,4 @@ class BatchBuffers:
             block_tables=[view(f"bt{g}").view(s, widths[g]) for g in range(self.num_groups)],
             status=self.status, q_lens=q_lens, starts=list(starts), max_q_len=max(q_lens, default=0),
             max_context=max(ctx_lens, default=0), decode_rows=view("dec"), num_decode=len(decode_rows),
-            prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4)
+            prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4, num_real_seqs=num_real)

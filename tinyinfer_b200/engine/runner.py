@@ -84,8 +84,12 @@ class ModelRunner:
         num_groups = len(self.manager.groups)
         tables = [[rc.tables[g] for rc in caches] for g in range(num_groups)] or [[[] for _ in caches]]
         decode_only = self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        pad_to = 0
+        if decode_only:
+            pad_to = min(graph_batch_size(len(entries)), self.buffers.max_seqs)
         ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables,
-                                 fixed_layout=decode_only)
+                                 fixed_layout=decode_only, pad_to=pad_to,
+                                 pad_pages=[CacheStorage.dump_page(self.manager, g) for g in range(num_groups)])
         self._bind_views(ctx)
         logits = self._graph_forward(ctx) if decode_only else self.model.forward(ctx)
         for e, start in zip(entries, starts):
@@ -95,7 +99,8 @@ class ModelRunner:
 
     def _graph_forward(self, ctx: StepContext) -> torch.Tensor:
         """A step of single decoded tokens: replayed from a CUDA graph captured for this number
-        of requests. The graph reads the step's arrays from the fixed device buffer that
+        of requests (batches are padded up to a few sizes, so a handful of graphs serve every batch
+        size). The graph reads the step's arrays from the fixed device buffer that
         ``build`` has just filled; the attention grid is sized for the context rounded up to a
         power of two of 256-key splits, so a handful of graphs cover every context length.
         The returned logits live in the graph's own memory until the next replay."""
@@ -107,11 +112,12 @@ class ModelRunner:
         ctx.max_context = splits * ops.DECODE_CHUNK
         key = (ctx.num_seqs, splits)
         hit = self._graphs.get(key)
+        real = ctx.num_real_seqs
         if hit is not None:
             hit[0].replay()
             self.graph_replays += 1
             library.count_replayed_launches(hit[2])
-            return hit[1]
+            return hit[1][:real]
         logits = self.model.forward(ctx)              # eager once: also sets up every kernel it uses
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
@@ -123,7 +129,7 @@ class ModelRunner:
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
         self._graphs[key] = (graph, static_logits, kernels_in_graph)
-        return logits
+        return logits[:real]
 
     def _bind_views(self, ctx: StepContext) -> None:
         for entry in range(self.model.spec.num_cache_entries):
@@ -141,6 +147,17 @@ class ModelRunner:
         if code:
             self.buffers.status.zero_()
             raise RuntimeError(f"a kernel met a token or key without a page (status {code})")
+
+
+_GRAPH_BATCH_SIZES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024)
+
+
+def graph_batch_size(n: int) -> int:
+    """The batch size of the captured graph that serves a decode step of ``n`` requests."""
+    for size in _GRAPH_BATCH_SIZES:
+        if size >= n:
+            return size
+    return n
 
 
 def pages_that_fit(model, page_size: int, free_bytes: int, utilization: float,
