@@ -47,7 +47,8 @@ def main():
     else:
         prompts = workload(args.workload, vocab, rng, args.num_requests)
         params = SamplingParams(greedy=True, max_tokens=args.max_tokens, ignore_eos=True)
-    llm.generate(prompts[:1], SamplingParams(greedy=True, max_tokens=2, ignore_eos=True))   # warm-up
+    warm = [rng.randrange(vocab) for _ in range(len(prompts[0]))]      # not a timed prompt: nothing of it is shared
+    llm.generate([warm], SamplingParams(greedy=True, max_tokens=2, ignore_eos=True))
     t0 = time.perf_counter()
     outs = llm.generate(prompts, params)
     wall = time.perf_counter() - t0
@@ -56,6 +57,8 @@ def main():
     print(json.dumps({
         "workload": args.workload, "requests": len(prompts), "wall_s": wall, "steps": llm.runner.steps_run,
         "graph_replays": llm.runner.graph_replays, "preemptions": llm.scheduler.num_preemptions,
+        "prefix_caching": bool(llm.config.enable_prefix_caching),
+        "cached_prompt_tokens": sum(o["num_cached_tokens"] for o in outs),
         "output_tokens_per_s": out_tokens / wall,
         "computed_plus_output_tokens_per_s": (prompt_tokens + out_tokens) / wall,
         "requests_per_s": len(prompts) / wall,

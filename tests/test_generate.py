@@ -168,3 +168,62 @@ def test_page_pressure_waits_and_preempts_but_gives_the_same_tokens(tmp_path, dt
     tight.runner.check_status()
     tight.runner.manager.check_consistency()
     assert not tight.runner.manager.live_requests
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 3e-2)])
+def test_shared_prompt_heads_are_taken_from_the_prefix_cache(tmp_path, dtype, tol):
+    """Prompts with a common head: later ones take its pages over instead of computing them, while
+    the first still runs and after it has ended, and a small pool hands kept pages out again.
+    The tokens are those of an engine without the prefix cache and of the plain implementation."""
+    from tinyinfer_b200 import LLM
+    cfg = helpers.TINY["A"]
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=6, dtype=dtype)
+    head = helpers.random_requests(cfg, [53], seed=21)["r0"]
+    tails = list(helpers.random_requests(cfg, [7, 19, 2, 30, 11, 16], seed=22).values())
+    prompts = [head + t for t in tails] + [head[:40]]
+    params = SamplingParams(greedy=True, max_tokens=12)
+    common = dict(dtype=dtype, max_num_batched_tokens=48, max_num_seqs=3, kvcache_block_size=8,
+                  prefill_chunk=24, max_model_len=128)
+    cold = LLM(folder, num_kvcache_blocks=64, enable_prefix_caching=False, **common)
+    want = cold.generate(prompts, params)
+    assert all(o["num_cached_tokens"] == 0 for o in want)
+    for pages in (64, 30):
+        llm = LLM(folder, num_kvcache_blocks=pages, **common)
+        assert llm.config.enable_prefix_caching
+        got = llm.generate(prompts, params)
+        cached = [o["num_cached_tokens"] for o in got]
+        assert cached[0] == 0 and all(c % 8 == 0 for c in cached)
+        # requests admitted beside the first find nothing or a first portion; those admitted after
+        # the head has been stored take over its six full pages
+        assert sum(cached) >= 96, cached
+        if pages == 64:
+            assert cached[4:6] == [48, 48], cached
+            assert cached[6] == 32                                  # 40 tokens: 4 pages, one token left to run
+        for p, o in zip(prompts, got):
+            check_greedy(folder, p, o["token_ids"], tol)
+        same = sum(a["token_ids"] == b["token_ids"] for a, b in zip(want, got))
+        assert same >= len(prompts) - 1          # a near-tie may flip when the head is not run again
+        # the same prompts once more: everything but the last page of each comes from the cache
+        again = llm.generate(prompts, params)
+        assert sum(o["num_cached_tokens"] for o in again) > sum(cached)
+        for p, o in zip(prompts, again):
+            check_greedy(folder, p, o["token_ids"], tol)
+        llm.runner.check_status()
+        llm.runner.manager.check_consistency()
+        assert not llm.runner.manager.live_requests
+        served = sum(cached) + sum(o["num_cached_tokens"] for o in again)
+        hits = llm.runner.manager.stats()["prefix_hit_tokens"]     # counts a prompt that had to wait each time it asked
+        assert hits == served if pages == 64 else hits >= served
+
+
+@pytest.mark.gpu
+def test_prefix_cache_is_off_where_a_window_gives_pages_back(tmp_path):
+    from tinyinfer_b200 import LLM
+    cfg = helpers.TINY["B"]                     # has sliding-window layers
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=2, dtype="float32")
+    kw = dict(dtype="float32", max_num_batched_tokens=32, max_num_seqs=2, kvcache_block_size=8,
+              num_kvcache_blocks=32, max_model_len=96)
+    assert LLM(folder, **kw).config.enable_prefix_caching is False
+    with pytest.raises(ValueError, match="enable_prefix_caching"):
+        LLM(folder, enable_prefix_caching=True, **kw)

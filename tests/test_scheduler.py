@@ -142,3 +142,57 @@ def test_random_traffic_always_finishes(seed):
     assert s.is_finished() and not pending
     assert all(q.is_finished for q in seqs)
     assert m.groups[0].pool.num_free == 12 and not m.live_requests
+
+
+# ---------------------------------------------------------------------------- prefix cache
+def make_prefix(num_pages=16, page=4, **kw):
+    cfg = EngineConfig(**{**dict(max_num_batched_tokens=16, max_num_seqs=4, max_model_len=64,
+                                 kvcache_block_size=page, num_kvcache_blocks=num_pages), **kw})
+    manager = CacheManager([(CacheNeed(2, 16, None), None)], page, num_pages, cfg.live_requests,
+                           prefix_caching=True)
+    return Scheduler(cfg, manager, eos_token_id=9), manager
+
+
+def run_step_stored(s, token=1):
+    """As run_step, and records the keys as stored, which the step function does in the engine."""
+    items = s.schedule()
+    for it in items:
+        s.manager.commit(it.seq.seq_id, it.start_pos + it.num_tokens)
+    s.postprocess(items, {it.seq.seq_id: token for it in items if it.sample_after})
+    s.manager.check_consistency()
+    return [(it.seq.seq_id, it.start_pos, it.num_tokens, it.is_prefill, it.sample_after) for it in items]
+
+
+def test_a_later_prompt_starts_after_the_pages_it_shares():
+    s, m = make_prefix()
+    a = seq(0, 14, max_tokens=3)
+    s.add(a)
+    assert run_step_stored(s) == [(0, 0, 14, True, True)]
+    b = seq(1, 14, max_tokens=2)                          # the same 14 tokens while a still decodes
+    s.add(b)
+    assert run_step_stored(s) == [(0, 14, 1, False, True), (1, 12, 2, True, True)]
+    assert (a.num_cached_tokens, b.num_cached_tokens) == (0, 12)
+    assert m.get(0).tables[0][:3] == m.get(1).tables[0][:3]
+    while not s.is_finished():
+        run_step_stored(s)
+    assert m.groups[0].pool.num_free == 16
+    # after both are gone their pages still serve a prompt that is one page longer
+    c = Sequence(2, list(range(100, 114)) + [1, 1, 5, 6], SamplingParams(greedy=True, max_tokens=1))
+    s.add(c)
+    assert run_step_stored(s) == [(2, 16, 2, True, True)]  # a's decoded tokens 1, 1 filled page 3
+    assert c.num_cached_tokens == 16
+
+
+def test_a_preempted_request_finds_its_own_pages_again():
+    s, m = make_prefix(num_pages=6, max_num_seqs=2)
+    a, b = seq(0, 9, max_tokens=12), seq(1, 9, max_tokens=12)
+    a.token_ids[0] = 55                                    # nothing in common
+    s.add(a), s.add(b)
+    for _ in range(40):
+        if s.is_finished():
+            break
+        run_step_stored(s)
+    assert s.is_finished() and s.num_preemptions >= 1
+    assert b.num_preemptions >= 1 and b.num_cached_tokens >= 4   # the head of its pages outlived a's growth
+    assert a.num_completion_tokens == 12 and b.num_completion_tokens == 12
+    assert m.groups[0].pool.num_free == 6

@@ -50,6 +50,8 @@ def add_engine_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.90)
     ap.add_argument("--num-kvcache-blocks", type=int, default=0, help="0: sized from free memory")
     ap.add_argument("--prefill-chunk", type=int, default=0, help="most prompt tokens of a request per step")
+    ap.add_argument("--no-prefix-caching", action="store_true",
+                    help="compute every prompt from its first token, even if an earlier one began alike")
     ap.add_argument("--device", default="cuda:0")
     for flag in ("--attention-backend", "--quantization", "--speculative", "--draft-model",
                  "--max-draft-tokens", "--host", "--port"):
@@ -67,7 +69,8 @@ def engine_config_from(args) -> EngineConfig:
         max_num_batched_tokens=args.max_num_batched_tokens, max_num_seqs=args.max_num_seqs,
         max_model_len=args.max_model_len, gpu_memory_utilization=args.gpu_memory_utilization,
         kvcache_block_size=args.block_size, num_kvcache_blocks=args.num_kvcache_blocks,
-        prefill_chunk=args.prefill_chunk, dtype=parse_dtype(args.dtype), device=args.device)
+        prefill_chunk=args.prefill_chunk, dtype=parse_dtype(args.dtype), device=args.device,
+        enable_prefix_caching=False if args.no_prefix_caching else None)
 
 
 def build_llm(args):

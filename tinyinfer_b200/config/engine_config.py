@@ -21,6 +21,8 @@ class EngineConfig:
     eos_token_id: int = -1                  # -1: taken from the model's configuration, if any
     cuda_graphs: bool = True                # replay captured decode steps
     track_nll: bool = False                 # sum each request's token NLL (the perplexity statistic)
+    enable_prefix_caching: Optional[bool] = None   # keep full pages for later prompts with the same
+                                                   # start; None: on where the model allows it
     device: str = "cuda:0"
 
     def validate(self) -> None:

@@ -11,6 +11,7 @@ from typing import Dict, List, Optional, Sequence as Seq, Union
 
 import torch
 
+from ..cache import prefix_caching_possible
 from ..config import EngineConfig
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
@@ -54,8 +55,15 @@ class LLM:
             if num_pages <= 0:
                 raise RuntimeError("no device memory left for the cache")
             self.config.num_kvcache_blocks = num_pages
+        possible = prefix_caching_possible(self.model.cache_needs())
+        if self.config.enable_prefix_caching and not possible:
+            raise ValueError("enable_prefix_caching: this model has windows or mixer state, whose "
+                             "pages cannot stand for a prompt's first tokens")
+        if self.config.enable_prefix_caching is None:
+            self.config.enable_prefix_caching = possible
         self.runner = ModelRunner(
             self.model, page_size=page, num_pages=num_pages, max_requests=self.config.live_requests,
+            prefix_caching=self.config.enable_prefix_caching,
             max_seqs_per_step=self.config.max_num_seqs,
             max_tokens_per_step=self.config.max_num_batched_tokens,
             max_model_len=self.config.max_model_len, cuda_graphs=self.config.cuda_graphs)

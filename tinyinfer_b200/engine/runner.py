@@ -20,14 +20,18 @@ from .batch import BatchBuffers, CacheView, StepContext, StepEntry
 class ModelRunner:
     def __init__(self, model, *, page_size: int, num_pages: int, max_requests: int,
                  max_tokens_per_step: int, max_model_len: int, max_seqs_per_step: int = 0,
-                 poison_cache: bool = False, cuda_graphs: bool = False):
+                 poison_cache: bool = False, cuda_graphs: bool = False,
+                 prefix_caching: bool = False):
         """``max_requests``: requests that may hold cache at a time (state slots);
         ``max_seqs_per_step``: requests in one step (0: the same); ``cuda_graphs``: steps made of
-        single decoded tokens only are captured once per batch size and replayed."""
+        single decoded tokens only are captured once per batch size and replayed;
+        ``prefix_caching``: full pages are kept under a hash of their tokens after their request
+        ends (the caller admits requests with their tokens and reports them after each step)."""
         self.model = model
         self.device = model.device
         needs = model.cache_needs()
-        self.manager = CacheManager(needs, page_size, num_pages, max_requests)
+        self.manager = CacheManager(needs, page_size, num_pages, max_requests,
+                                    prefix_caching=prefix_caching)
         self.storage = CacheStorage(needs, self.manager, model.dtype, self.device, poison=poison_cache)
         self.max_model_len = max_model_len
         max_blocks = (max_model_len + page_size - 1) // page_size
@@ -43,8 +47,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: Hashable) -> None:
-        rc = self.manager.admit(request_id)
-        self.storage.reset_state_slot(rc.state_slot)
+        self.manager.admit(request_id)
 
     def release(self, request_id: Hashable) -> None:
         self.manager.release(request_id)
@@ -67,6 +70,8 @@ class ModelRunner:
         for rid in ids:
             if rid not in self.manager:
                 self.admit(rid)
+        for slot in self.manager.take_fresh_slots():      # whoever admitted them: their state starts clean
+            self.storage.reset_state_slot(slot)
         vocab = self.model.spec.vocab_size
         starts: List[int] = []
         for e in entries:

@@ -98,13 +98,17 @@ class Scheduler:
             if not seq.admitted:
                 if not self.manager.can_admit():
                     break
-                self.manager.admit(seq.seq_id)
+                # with a prefix cache the request takes over kept pages that its tokens begin
+                # with (tinyinfer/engine/scheduler.py:132-137); what they cover is not run again
+                rc = self.manager.admit(seq.seq_id, seq.token_ids[:seq.num_prefill_tokens])
                 if not self.manager.can_extend(seq.seq_id, seq.num_prefill_tokens):
                     self.manager.release(seq.seq_id)       # its pages are not there yet: it waits
                     self.waiting.rotate(-1)
                     continue
                 self.manager.extend(seq.seq_id, seq.num_prefill_tokens)
                 seq.admitted = True
+                seq.num_computed_tokens = rc.length
+                seq.num_cached_tokens = rc.length
             remaining = seq.num_prefill_tokens - seq.num_computed_tokens
             chunk = min(remaining, token_budget)
             if self.prefill_chunk > 0:
@@ -165,6 +169,8 @@ class Scheduler:
         for item in items:
             seq = item.seq
             seq.num_computed_tokens = item.start_pos + item.num_tokens
+            if seq.seq_id in self.manager:
+                self.manager.note_tokens(seq.seq_id, seq.token_ids)   # full pages join the prefix cache
             if not item.sample_after:
                 continue                                    # a portion inside the prompt: no token
             seq.append_token(sampled[seq.seq_id])
