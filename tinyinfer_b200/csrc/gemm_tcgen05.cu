@@ -242,27 +242,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty_bar(as));
                 released = true;
-                __threadfence();
+                // Publish, then count: the barrier orders every thread's stores before thread 64's fence,
+                // the fence (cumulative, GPU scope) orders them before its count; on the other side the
+                // count that shows this unit to be the last one is followed by a fence and the barrier,
+                // after which every thread may read the other units' partials (from L2, never from L1).
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 64) {
+                    __threadfence();
                     const int arrived = atomicAdd(p.counters + tile, 1);
                     if (arrived == p.splits - 1) p.counters[tile] = 0;     // leave the counter ready for the next launch
+                    __threadfence();
                     *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]) = arrived;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 const int arrived = *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (arrived != p.splits - 1) continue;
-                __threadfence();
             }
+            // The last arriver's sum: for four columns at a time, the partials of up to sixteen splits are
+            // requested together (64 independent loads), then added in split order. One trip to L2 per
+            // group instead of one per split; the order of the additions, and so the result, is the same.
+            // Swapped tiles skip the columns beyond the last token: nothing of them is stored.
             auto load_chunk = [&](int c, float* dst) {
                 if (p.splits > 1) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) dst[i] = 0.f;
-                    for (int sp = 0; sp < p.splits; ++sp) {
-                        const float* src = tile_partials + (size_t)sp * BN * BM + row_in_tile;
+                    for (int i0 = 0; i0 < 16; i0 += 4) {
+                        float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (!p.swap || c0 + c + i0 < p.M) {
+                            for (int sp0 = 0; sp0 < p.splits; sp0 += 16) {
+                                float part[16][4];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) dst[i] += __ldcg(src + (size_t)(c + i) * BM);
+                                for (int sp = 0; sp < 16; ++sp) {
+                                    const bool in = sp0 + sp < p.splits;
+                                    const float* src = tile_partials + (size_t)(in ? sp0 + sp : 0) * BN * BM + row_in_tile;
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) part[sp][i] = in ? __ldcg(src + (size_t)(c + i0 + i) * BM) : 0.f;
+                                }
+#pragma unroll
+                                for (int sp = 0; sp < 16; ++sp) {
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) acc4[i] += part[sp][i];
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i0 + i] = acc4[i];
                     }
                 } else {
                     tmem_ld16(t_addr + c, dst);
@@ -360,17 +384,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     const bool n_ok = n < p.N;
                     const float b = (p.bias && n_ok) ? p.bias[n] : 0.f;
                     for (int c = 0; c < BN; c += 16) {
+                        // the residual may be the output itself: all of it is read before anything is stored,
+                        // and the reads are in flight together with those of the partials
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int m = c0 + c + i;
+                            u[i] = (p.residual && n_ok && m < p.M) ? __bfloat162float(p.residual[(size_t)m * p.N + n]) : 0.f;
+                        }
                         load_chunk(c, v);
                         if (!n_ok) continue;
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const int m = c0 + c + i;
-                            if (m >= p.M) break;
-                            float val = v[i] + b;
-                            const size_t idx = (size_t)m * p.N + n;
-                            if (p.residual) val += __bfloat162float(p.residual[idx]);
-                            if (p.out_f32) reinterpret_cast<float*>(p.out)[idx] = val;
-                            else reinterpret_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(val);
+                            if (m < p.M) {
+                                const float val = v[i] + b + u[i];
+                                const size_t idx = (size_t)m * p.N + n;
+                                if (p.out_f32) reinterpret_cast<float*>(p.out)[idx] = val;
+                                else reinterpret_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(val);
+                            }
                         }
                     }
                 } else {

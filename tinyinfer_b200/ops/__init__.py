@@ -317,12 +317,15 @@ def attention_tensor_cores_ok(q: torch.Tensor, kv_cache: torch.Tensor) -> bool:
 
 
 _attn_scratch = {}
+_attn_scratch_outgrown = []     # kept alive: captured graphs may still write their partials there
 
 
 def _decode_scratch(device, floats: int) -> torch.Tensor:
     key = torch.device(device)
     t = _attn_scratch.get(key)
     if t is None or t.numel() < floats:
+        if t is not None:
+            _attn_scratch_outgrown.append(t)
         t = _attn_scratch[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=key)
     return t
 
