@@ -320,7 +320,9 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
     }
 }
 
-// One block per (decode row, query head): merges the splits that hold visible keys.
+// One block per (decode row, query head), one thread per feature: merges the splits that hold visible
+// keys. The partials of sixteen splits are requested together (one trip to L2 for a context of 4096)
+// and folded into a running maximum, sum and output, in split order.
 template <int D>
 __global__ void decode_merge_kernel(const AttnParams p) {
     ti_grid_launch_dependents();
@@ -331,14 +333,31 @@ __global__ void decode_merge_kernel(const AttnParams p) {
     const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
     const int s0 = lo / CHUNK, s1 = (ctx - 1) / CHUNK;
     const size_t base = ((size_t)r * p.hq + h) * p.max_splits;
-    float m_all = -INFINITY;
-    for (int s = s0; s <= s1; ++s) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
-    const float m_use = m_all == -INFINITY ? 0.f : m_all;
-    float acc = 0.f, l_all = 0.f;
-    for (int s = s0; s <= s1; ++s) {
-        const float f = exp2f(p.part_ml[(base + s) * 2] - m_use);
-        acc += f * p.part_o[(base + s) * D + d];
-        l_all += f * p.part_ml[(base + s) * 2 + 1];
+    float m_run = -INFINITY, acc = 0.f, l_all = 0.f;
+    for (int sb = s0; sb <= s1; sb += 16) {
+        float ms[16], ls[16], os[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const bool in = sb + j <= s1;
+            const float2 ml = in ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + (base + sb + j) * 2)) : make_float2(-INFINITY, 0.f);
+            ms[j] = ml.x;
+            ls[j] = ml.y;
+            os[j] = in ? __ldcg(p.part_o + (base + sb + j) * D + d) : 0.f;
+        }
+        float m_new = m_run;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) m_new = fmaxf(m_new, ms[j]);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float keep = exp2f(m_run - m_use);          // 0 while nothing has been merged yet
+        acc *= keep;
+        l_all *= keep;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float f = exp2f(ms[j] - m_use);          // 0 for a split that is not there
+            acc += f * os[j];
+            l_all += f * ls[j];
+        }
+        m_run = m_new;
     }
     p.out[((size_t)row * p.hq + h) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
 }
