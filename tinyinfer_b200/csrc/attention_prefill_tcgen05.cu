@@ -115,40 +115,35 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
+        // A tile is KT / piece_rows pieces (a piece lies in one page) x head halves x (keys, values): up to
+        // 32 copies. Each lane issues one of them, so that a tile is on its way in one round instead of
+        // one copy after the other; lane 0 waits for the stage and arms its barrier.
         if (lane == 0) {
             mbar_expect_tx(q_full, S::Q_BYTES);
 #pragma unroll
             for (int hh = 0; hh < S::HALVES; ++hh)
                 tma_load_2d(smem_u32(q_tile) + hh * (QM * 128), &q_map, q_full, head * D + hh * 64, row0);
-            const int piece_rows = p.page_size < 64 ? p.page_size : 64;
-            const int pieces = KT / piece_rows;
-            for (int j = 0; j < num_tiles; ++j) {
-                const int s = j % KV_STAGES;
-                if (!mbar_wait(kv_empty(s), ((j / KV_STAGES) & 1u) ^ 1u, abort_flag, p.status, 31)) break;
-                const int t = tile0 + j;
-                uint32_t bytes = 0;
-                for (int i = 0; i < pieces; ++i) {
-                    const int logical = (t * KT + i * piece_rows) / p.page_size;
-                    const int page = logical < p.max_blocks ? table[logical] : -1;
-                    if (page >= 0 && page < p.num_pages) bytes += (uint32_t)piece_rows * 128u * S::HALVES * 2u;
-                }
-                mbar_expect_tx(kv_full(s), bytes);
-                const uint32_t stage = smem_u32(kv_ring + s * S::STAGE);
-                for (int i = 0; i < pieces; ++i) {
-                    const int tok = t * KT + i * piece_rows;
-                    const int logical = tok / p.page_size;
-                    const int page = logical < p.max_blocks ? table[logical] : -1;
-                    if (page < 0 || page >= p.num_pages) continue;      // never written, or given back by a window
-                    const int off = tok % p.page_size;
-                    const int krow = (page * p.hkv + kvh) * p.page_size + off;
-                    const int vrow = ((p.num_pages + page) * p.hkv + kvh) * p.page_size + off;
-#pragma unroll
-                    for (int hh = 0; hh < S::HALVES; ++hh) {
-                        const uint32_t dst = stage + hh * (KT * 128) + i * piece_rows * 128;
-                        tma_load_2d(dst, &kv_map, kv_full(s), hh * 64, krow);
-                        tma_load_2d(dst + S::KV_TILE, &kv_map, kv_full(s), hh * 64, vrow);
-                    }
-                }
+        }
+        const int piece_rows = p.page_size < 64 ? p.page_size : 64;
+        const int num_copies = (KT / piece_rows) * S::HALVES * 2;
+        const int my_piece = lane / (S::HALVES * 2), my_half = (lane >> 1) % S::HALVES, my_kv = lane & 1;
+        for (int j = 0; j < num_tiles; ++j) {
+            const int s = j % KV_STAGES;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(kv_empty(s), ((j / KV_STAGES) & 1u) ^ 1u, abort_flag, p.status, 31) ? 1 : 0;
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            const int tok = (tile0 + j) * KT + my_piece * piece_rows;
+            const int logical = tok / p.page_size;
+            int page = (lane < num_copies && logical < p.max_blocks) ? table[logical] : -1;
+            if (page >= p.num_pages) page = -1;                     // never written, or given back by a window
+            const uint32_t copies = __popc(__ballot_sync(0xffffffffu, page >= 0));
+            if (lane == 0) mbar_expect_tx(kv_full(s), copies * (uint32_t)piece_rows * 128u);
+            __syncwarp();
+            if (page >= 0) {
+                const int row = ((my_kv * p.num_pages + page) * p.hkv + kvh) * p.page_size + tok % p.page_size;
+                const uint32_t dst = smem_u32(kv_ring + s * S::STAGE) + my_kv * S::KV_TILE + my_half * (KT * 128) +
+                                     my_piece * piece_rows * 128;
+                tma_load_2d(dst, &kv_map, kv_full(s), my_half * 64, row);
             }
         }
     } else if (warp == 1) {
