@@ -127,15 +127,20 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         const int piece_rows = p.page_size < 64 ? p.page_size : 64;
         const int num_copies = (KT / piece_rows) * S::HALVES * 2;
         const int my_piece = lane / (S::HALVES * 2), my_half = (lane >> 1) % S::HALVES, my_kv = lane & 1;
+        auto page_of_tile = [&](int j) {                            // this lane's page of tile j, read ahead of its use
+            const int logical = ((tile0 + j) * KT + my_piece * piece_rows) / p.page_size;
+            const int page = (j < num_tiles && lane < num_copies && logical < p.max_blocks) ? table[logical] : -1;
+            return page >= p.num_pages ? -1 : page;                 // never written, or given back by a window
+        };
+        int page_next = page_of_tile(0);
         for (int j = 0; j < num_tiles; ++j) {
             const int s = j % KV_STAGES;
+            const int page = page_next;
+            page_next = page_of_tile(j + 1);
             int ok = 1;
             if (lane == 0) ok = mbar_wait(kv_empty(s), ((j / KV_STAGES) & 1u) ^ 1u, abort_flag, p.status, 31) ? 1 : 0;
             if (!__shfl_sync(0xffffffffu, ok, 0)) break;
             const int tok = (tile0 + j) * KT + my_piece * piece_rows;
-            const int logical = tok / p.page_size;
-            int page = (lane < num_copies && logical < p.max_blocks) ? table[logical] : -1;
-            if (page >= p.num_pages) page = -1;                     // never written, or given back by a window
             const uint32_t copies = __popc(__ballot_sync(0xffffffffu, page >= 0));
             if (lane == 0) mbar_expect_tx(kv_full(s), copies * (uint32_t)piece_rows * 128u);
             __syncwarp();
