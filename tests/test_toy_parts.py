@@ -1,6 +1,7 @@
-"""A mixer with state of its own, a run order that names a layer twice, and an entry that reads
-another entry's cache: all defined HERE, registered, built and stepped through the framework's
-own model, cache and step function without touching its files. The toy is no one's model."""
+"""A mixer with state of its own, a feed-forward that routes every token to one of three experts, a
+position encoding with stretched positions, a run order that names a layer twice, and an entry that
+reads another entry's cache: all defined HERE, registered, built and stepped through the
+framework's own model, cache and step function without touching its files. The toy is no one's model."""
 import json
 from dataclasses import dataclass
 
@@ -14,7 +15,8 @@ import torch_ops
 from tinyinfer_b200.config import (AttentionSpec, ExecStep, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec,
                                    PositionSpec, TensorNames, register_architecture)
 from tinyinfer_b200.models import DecoderModel
-from tinyinfer_b200.parts import Mixer, StateNeed, TensorSpec, register_mixer
+from tinyinfer_b200.parts import (FeedForward, Mixer, PositionEncoding, StateNeed, TensorSpec,
+                                  register_feed_forward, register_mixer, register_position)
 
 
 # ------------------------------------------------------------------ the toy, as a user would write it
@@ -54,8 +56,72 @@ class RunningMeanMixer(Mixer):
 
 register_mixer("toy_running_mean", RunningMeanMixer)
 
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    kind: str = "toy_top1_experts"
+
+
+class RoutedFeedForward(FeedForward):
+    """Every token goes to the one expert its router logit (float32) is largest for; the expert is a
+    gated MLP whose output is scaled by the softmax weight of that logit. Built from the package's
+    own products; the routing itself is plain tensor code, which is all a toy needs."""
+
+    def tensors(self):
+        h, i, e = self.spec.hidden_size, self.spec.intermediate_size, self.spec.num_experts
+        t = {"router.weight": TensorSpec((e, h), role="vector32")}
+        for k in range(e):
+            t[f"experts.{k}.gate_up.weight"] = TensorSpec((2 * i, h))
+            t[f"experts.{k}.down.weight"] = TensorSpec((h, i))
+        return t
+
+    def load(self, tensors):
+        self.w = tensors
+
+    def forward(self, x, step):
+        from tinyinfer_b200 import ops
+        logits = x.float() @ self.w["router.weight"].T
+        weight, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+        out = torch.zeros_like(x)
+        for k in range(self.spec.num_experts):
+            rows = (choice == k).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            hidden = ops.gated_linear(x.index_select(0, rows).contiguous(), self.w[f"experts.{k}.gate_up.weight"])
+            y = ops.linear(hidden, self.w[f"experts.{k}.down.weight"])
+            out.index_copy_(0, rows, (y.float() * weight[rows, None]).to(x.dtype))
+        return out
+
+
+register_feed_forward("toy_top1_experts", RoutedFeedForward)
+
+
+@dataclass(frozen=True)
+class StretchedRopeSpec:
+    theta: float
+    rotary_dim: int
+    stretch: float                     # position p turns as position p / stretch would
+    kind: str = "toy_stretched_rope"
+
+
+class StretchedRope(PositionEncoding):
+    """Rotary encoding with every position divided by a constant: the same rotation kernel, other
+    frequencies. The attention mixer asks its position part only for inv_freq and rotary_dim."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim
+        self.inv_freq = (1.0 / (spec.theta ** exponent) / spec.stretch).to(device)
+        self.rotary_dim = spec.rotary_dim
+
+
+register_position("toy_stretched_rope", StretchedRope)
+
 TOY = dict(architectures=["ToyForCausalLM"], vocab_size=97, hidden_size=48, heads=3, kv_heads=1, head_dim=16,
-           intermediate_size=80, eps=1e-5, theta=10000.0, max_positions=256)
+           intermediate_size=80, eps=1e-5, theta=10000.0, max_positions=256, experts=3, expert_size=24, stretch=4.0)
 
 
 class ToyConfig:
@@ -74,10 +140,12 @@ class ToyConfig:
         d = self.d
         h, eps = d["hidden_size"], d["eps"]
         attn = AttentionSpec(h, d["heads"], d["kv_heads"], d["head_dim"], d["head_dim"] ** -0.5,
-                             PositionSpec("rope", d["theta"], d["head_dim"]), qk_norm=NormSpec(d["head_dim"], eps))
+                             StretchedRopeSpec(d["theta"], d["head_dim"], d["stretch"]),
+                             qk_norm=NormSpec(d["head_dim"], eps))
         ffn = GatedMLPSpec(h, d["intermediate_size"])
+        routed = RoutedSpec(h, d["expert_size"], d["experts"])
         norm = NormSpec(h, eps)
-        layers = (LayerSpec(attn, ffn, norm, norm), LayerSpec(RunningMeanSpec(h), ffn, norm, norm))
+        layers = (LayerSpec(attn, ffn, norm, norm), LayerSpec(RunningMeanSpec(h), routed, norm, norm))
         # layer 0 runs three times: with a cache of its own, again with another cache, and at the
         # end reading the keys its first run wrote; the stateful toy layer sits in between
         execution = (ExecStep(0, 0), ExecStep(1, 1), ExecStep(0, 2), ExecStep(0, 0, writes_cache=False))
@@ -93,7 +161,7 @@ def toy_plain(w, tokens):
     d = TOY
     cfg = dict(num_attention_heads=d["heads"], num_key_value_heads=d["kv_heads"], head_dim=d["head_dim"],
                rms_norm_eps=d["eps"], rope_theta=d["theta"], hidden_size=d["hidden_size"])
-    pos = list(range(len(tokens)))
+    pos = [i / d["stretch"] for i in range(len(tokens))]
     t = len(tokens)
 
     def attn_layer(x, kv_from=None):
@@ -118,7 +186,14 @@ def toy_plain(w, tokens):
     y = hn @ w[p + "self_attn.proj.weight"].T
     x = x + torch.cumsum(y, 0) / torch.arange(1, t + 1, dtype=x.dtype)[:, None]
     hn = plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], d["eps"])
-    x = x + plain.swiglu(hn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    gate = torch.softmax(hn @ w[p + "mlp.router.weight"].T, dim=-1)
+    routed = torch.zeros_like(x)
+    for i in range(t):
+        k = int(gate[i].argmax())
+        gu = w[p + f"mlp.experts.{k}.gate_up.weight"]
+        half = gu.shape[0] // 2
+        routed[i] = gate[i, k] * plain.swiglu(hn[i:i + 1], gu[:half], gu[half:], w[p + f"mlp.experts.{k}.down.weight"])[0]
+    x = x + routed
     x, _ = attn_layer(x)
     x, _ = attn_layer(x, kv_from=first_normed)          # reads the keys and values of the first run
     x = plain.rmsnorm(x, w["model.norm.weight"], d["eps"])
