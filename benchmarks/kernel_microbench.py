@@ -69,6 +69,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--prefix", type=int, default=0, help="attention_prefill: keys already in the cache before the tokens")
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -108,7 +109,7 @@ def main():
         if a.kernel == "attention_decode":
             lens, q_lens = [a.context] * a.batch, [1] * a.batch
         else:
-            lens, q_lens = [a.tokens], [a.tokens]
+            lens, q_lens = [a.prefix + a.tokens], [a.tokens]
         per = [(n + page - 1) // page for n in lens]
         copies = max(1, min(6, int(300e6 // (sum(lens) * hkv * d * 4)) + 1))
         kvs = [torch.randn(2, sum(per) + 1, hkv, page, d, device=dev).bfloat16() for _ in range(copies)]
@@ -139,8 +140,8 @@ def main():
             byts = sum(lens) * hkv * d * 2 * 2
             flops = 4.0 * sum(lens) * hq * d
         else:
-            byts = a.tokens * hkv * d * 2 * 2 + 2 * a.tokens * hq * d * 2
-            flops = 4.0 * d * hq * a.tokens * (a.tokens + 1) / 2
+            byts = (a.prefix + a.tokens) * hkv * d * 2 * 2 + 2 * a.tokens * hq * d * 2
+            flops = 4.0 * d * hq * (a.tokens * a.prefix + a.tokens * (a.tokens + 1) / 2)
         out.update(batch=len(lens), context=max(lens), us=us, gbs=byts / us / 1e3, tflops=flops / us / 1e6)
     else:
         from tinyinfer_b200 import EngineConfig

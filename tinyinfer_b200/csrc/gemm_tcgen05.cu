@@ -18,6 +18,7 @@
 // flag, and all warps fall through to the common exit, where tensor memory is freed.
 #include "sm100_ptx.cuh"
 #include <cstdlib>
+#include <type_traits>
 #include <mutex>
 #include <unordered_map>
 
@@ -258,36 +259,117 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 const int arrived = *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (arrived != p.splits - 1) continue;
-            }
-            // The last arriver's sum: for four columns at a time, the partials of up to sixteen splits are
-            // requested together (64 independent loads), then added in split order. One trip to L2 per
-            // group instead of one per split; the order of the additions, and so the result, is the same.
-            // Swapped tiles skip the columns beyond the last token: nothing of them is stored.
-            auto load_chunk = [&](int c, float* dst) {
-                if (p.splits > 1) {
+                // Swapped, not gated (the products of a decode step): the four warps share the columns
+                // (tokens), a lane takes four consecutive rows (output features). So every load is 16
+                // bytes and a warp reads a whole column of a partial at once; the partials of several
+                // columns and of all splits are in flight together and are added in split order.
+                if (p.swap && !p.gated && (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0 &&
+                    ((uintptr_t)p.residual & 7) == 0 && ((uintptr_t)p.bias & 15) == 0) {
+                    const int n0 = r0 + 4 * lane;
+                    const bool n_ok = n0 < p.N;                        // N is a multiple of 4: all four rows or none
+                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (p.bias && n_ok) b4 = *reinterpret_cast<const float4*>(p.bias + n0);
+                    const int cols_real = min(BN, p.M - c0);
+                    auto wide = [&](auto cols_tag, auto splits_tag) {
+                        constexpr int G = decltype(cols_tag)::value, SP = decltype(splits_tag)::value;
+                        for (int g0 = lane_group; g0 < cols_real; g0 += 4 * G) {
+                            float4 acc[G];
+                            uint2 res[G];
 #pragma unroll
-                    for (int i0 = 0; i0 < 16; i0 += 4) {
-                        float acc4[4] = {0.f, 0.f, 0.f, 0.f};
-                        if (!p.swap || c0 + c + i0 < p.M) {
-                            for (int sp0 = 0; sp0 < p.splits; sp0 += 16) {
-                                float part[16][4];
+                            for (int i = 0; i < G; ++i) {
+                                acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                res[i] = make_uint2(0u, 0u);
+                                const int col = g0 + 4 * i;
+                                if (p.residual && n_ok && col < cols_real)
+                                    res[i] = *reinterpret_cast<const uint2*>(p.residual + (size_t)(c0 + col) * p.N + n0);
+                            }
+                            for (int sp0 = 0; sp0 < p.splits; sp0 += SP) {
+                                float4 part[SP][G];
 #pragma unroll
-                                for (int sp = 0; sp < 16; ++sp) {
-                                    const bool in = sp0 + sp < p.splits;
-                                    const float* src = tile_partials + (size_t)(in ? sp0 + sp : 0) * BN * BM + row_in_tile;
+                                for (int sp = 0; sp < SP; ++sp) {
 #pragma unroll
-                                    for (int i = 0; i < 4; ++i) part[sp][i] = in ? __ldcg(src + (size_t)(c + i0 + i) * BM) : 0.f;
+                                    for (int i = 0; i < G; ++i) {
+                                        const int col = g0 + 4 * i;
+                                        const bool in = sp0 + sp < p.splits && col < cols_real;
+                                        part[sp][i] = in ? __ldcg(reinterpret_cast<const float4*>(
+                                                               tile_partials + ((size_t)(sp0 + sp) * BN + col) * BM + 4 * lane))
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+                                    }
                                 }
 #pragma unroll
-                                for (int sp = 0; sp < 16; ++sp) {
+                                for (int sp = 0; sp < SP; ++sp) {
 #pragma unroll
-                                    for (int i = 0; i < 4; ++i) acc4[i] += part[sp][i];
+                                    for (int i = 0; i < G; ++i) {
+                                        acc[i].x += part[sp][i].x; acc[i].y += part[sp][i].y;
+                                        acc[i].z += part[sp][i].z; acc[i].w += part[sp][i].w;
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < G; ++i) {
+                                const int col = g0 + 4 * i;
+                                if (!n_ok || col >= cols_real) continue;
+                                const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&res[i]);
+                                const float2 ra = __bfloat1622float2(r2[0]), rb = __bfloat1622float2(r2[1]);
+                                const float4 v4 = make_float4(acc[i].x + b4.x + ra.x, acc[i].y + b4.y + ra.y,
+                                                              acc[i].z + b4.z + rb.x, acc[i].w + b4.w + rb.y);
+                                const size_t idx = (size_t)(c0 + col) * p.N + n0;
+                                if (p.out_f32) {
+                                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + idx) = v4;
+                                } else {
+                                    uint2 o2;
+                                    __nv_bfloat162 lo2 = __floats2bfloat162_rn(v4.x, v4.y), hi2 = __floats2bfloat162_rn(v4.z, v4.w);
+                                    o2.x = *reinterpret_cast<uint32_t*>(&lo2);
+                                    o2.y = *reinterpret_cast<uint32_t*>(&hi2);
+                                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + idx) = o2;
                                 }
                             }
                         }
+                    };
+                    if (p.splits <= 4) wide(std::integral_constant<int, 4>{}, std::integral_constant<int, 4>{});
+                    else if (p.splits <= 8) wide(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{});
+                    else wide(std::integral_constant<int, 1>{}, std::integral_constant<int, 16>{});
+                    continue;
+                }
+            }
+            // The last arriver's sum: the partials of a group of columns and of all splits (16 at a time)
+            // are requested together, 64 independent loads, then added in split order: one trip to L2
+            // per group instead of one per split; the order of the additions, and so the result, is the
+            // same. The fewer the splits, the more columns share a trip. Swapped tiles skip the columns
+            // beyond the last token: nothing of them is stored.
+            auto sum_group = [&](int c, float* dst, auto cols_tag, auto splits_tag) {
+                constexpr int COLS = decltype(cols_tag)::value, SPLITS = decltype(splits_tag)::value;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) dst[i0 + i] = acc4[i];
+                for (int i0 = 0; i0 < 16; i0 += COLS) {
+                    float acc[COLS];
+#pragma unroll
+                    for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
+                    if (!p.swap || c0 + c + i0 < p.M) {
+                        for (int sp0 = 0; sp0 < p.splits; sp0 += SPLITS) {
+                            float part[SPLITS][COLS];
+#pragma unroll
+                            for (int sp = 0; sp < SPLITS; ++sp) {
+                                const bool in = sp0 + sp < p.splits;
+                                const float* src = tile_partials + (size_t)(in ? sp0 + sp : 0) * BN * BM + row_in_tile;
+#pragma unroll
+                                for (int i = 0; i < COLS; ++i) part[sp][i] = in ? __ldcg(src + (size_t)(c + i0 + i) * BM) : 0.f;
+                            }
+#pragma unroll
+                            for (int sp = 0; sp < SPLITS; ++sp) {
+#pragma unroll
+                                for (int i = 0; i < COLS; ++i) acc[i] += part[sp][i];
+                            }
+                        }
                     }
+#pragma unroll
+                    for (int i = 0; i < COLS; ++i) dst[i0 + i] = acc[i];
+                }
+            };
+            auto load_chunk = [&](int c, float* dst) {
+                if (p.splits > 1) {
+                    if (p.splits <= 4) sum_group(c, dst, std::integral_constant<int, 16>{}, std::integral_constant<int, 4>{});
+                    else if (p.splits <= 8) sum_group(c, dst, std::integral_constant<int, 8>{}, std::integral_constant<int, 8>{});
+                    else sum_group(c, dst, std::integral_constant<int, 4>{}, std::integral_constant<int, 16>{});
                 } else {
                     tmem_ld16(t_addr + c, dst);
                 }
@@ -455,11 +537,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 // leave most of the 148 SMs idle. Needs scratch for the partial sums.
 int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int num_counters) {
     if (tiles > num_counters) return 1;
+    const int per_sm = bn <= 64 ? 2 : 1;                  // Cfg<BN>::CTAS_PER_SM
     if (const char* forced = getenv("TINYINFER_B200_GEMM_SPLITS")) {     // experiments only
         const int s = atoi(forced);
         if (s >= 1 && num_kb / s >= 1 && (long long)tiles * s * bn * BM <= workspace_floats) return s;
     }
-    const int sms = ti_sm_count() * 2;                    // two small-batch CTAs share an SM
+    const int sms = ti_sm_count() * per_sm;               // CTAs that run side by side
     if (tiles * 2 >= sms) return 1;                       // every SM has a tile: cutting them only adds the merge
     int best = 1;
     double best_eff = 0.0;
@@ -513,11 +596,14 @@ TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bi
     p.splits = 1; p.partials = workspace; p.counters = counters;
     const int w_rows = gated ? 2 * N : N;
     CUtensorMap rows_map, cols_map;
-    if (M <= 64) {
-        // swapped: weights on the 128 accumulator lanes, tokens on the columns
+    // Up to 128 tokens the weights go on the 128 accumulator lanes and the tokens on the columns: with
+    // so few tokens the other orientation has one row of tiles, too few for 148 SMs, and no way to
+    // cut their k loops. (The gated form keeps its 64-column limit; it has tiles enough. Beyond 128
+    // tokens the partial sums of the cut k loops cost more than the idle SMs: measured.)
+    if (M <= 64 || (!gated && M <= 128 && workspace && counters)) {
         p.swap = 1;
         p.rows_total = N; p.cols_total = M;
-        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
         if (!ti_get_bf16_map(w, w_rows, K, gated ? BM / 2 : BM, &rows_map)) return -1;
         if (!ti_get_bf16_map(x, M, K, bn, &cols_map)) return -1;
         const int tiles = (N + (gated ? 64 : 128) - 1) / (gated ? 64 : 128);
@@ -525,13 +611,22 @@ TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bi
             p.splits = choose_splits(tiles, (K + BK - 1) / BK, bn, workspace_floats, num_counters);
         if (bn == 16) return launch<16>(rows_map, cols_map, p, tiles, stream);
         if (bn == 32) return launch<32>(rows_map, cols_map, p, tiles, stream);
-        return launch<64>(rows_map, cols_map, p, tiles, stream);
+        if (bn == 64) return launch<64>(rows_map, cols_map, p, tiles, stream);
+        return launch<128>(rows_map, cols_map, p, tiles, stream);
     }
     p.swap = 0;
     p.rows_total = M; p.cols_total = N;
     if (!ti_get_bf16_map(x, M, K, BM, &rows_map)) return -1;
     const int row_tiles = (M + BM - 1) / BM;
-    const bool wide = (gated ? 2 * N : N) >= 256;
+    // 256 columns a tile, unless the output is narrow or, with so few tiles that half the SMs would
+    // have none, twice as many tiles of 128 columns finish sooner (a tile of half the width does not
+    // run faster per k step, but twice as many SMs work)
+    bool wide = (gated ? 2 * N : N) >= 256;
+    if (wide) {
+        const int cpt256 = gated ? 128 : 256;
+        const long long tiles256 = (long long)row_tiles * ((N + cpt256 - 1) / cpt256);
+        if (tiles256 * 2 <= ti_sm_count()) wide = false;
+    }
     if (wide) {
         if (!ti_get_bf16_map(w, w_rows, K, gated ? 128 : 256, &cols_map)) return -1;
         const int cpt = gated ? 128 : 256;
