@@ -85,6 +85,8 @@ class BatchBuffers:
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
         self._copy_pending = False
         self.bytes_copied = 0              # host-to-device bytes of all steps so far
+        self._host_np = self.host.numpy()
+        self._last = None                  # what advance_decode() needs to know of the last fixed-layout step
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
               tables: Sequence[Sequence[Sequence[int]]], fixed_layout: bool = False,
@@ -163,7 +165,7 @@ class BatchBuffers:
             o, ln = offsets[name]
             return self.dev[o:o + ln]
 
-        return StepContext(
+        ctx = StepContext(
             num_tokens=t, num_seqs=s, num_logit_rows=len(rows),
             token_ids=view("ids"), positions=view("pos"), token_seq=view("seq"),
             cu_seqlens=view("cu"), q_starts=view("starts"), context_lens=view("ctx"),
@@ -172,3 +174,45 @@ class BatchBuffers:
             status=self.status, q_lens=q_lens, starts=list(starts), max_q_len=max(q_lens, default=0),
             max_context=max(ctx_lens, default=0), decode_rows=view("dec"), num_decode=len(decode_rows),
             prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4, num_real_seqs=num_real)
+        self._last = None
+        if fixed_layout and all(n == 1 for n in q_lens):
+            self._last = dict(key=(tuple(e.request_id for e in entries[:num_real]), s), ctx=ctx, words=n,
+                              offsets=offsets, widths=widths, num_real=num_real,
+                              table_lens=[[len(tb) for tb in tables[g][:num_real]] for g in range(self.num_groups)])
+        return ctx
+
+    def advance_decode(self, request_ids: Sequence, pad_to: int, tokens: Sequence[int], starts: Sequence[int],
+                       tables: Sequence[Sequence[Sequence[int]]]) -> Optional[StepContext]:
+        """The step after a step of single decoded tokens, for the same requests in the same order,
+        each with its next token: only the token ids, the positions and the pages that were added
+        change, so the staging buffer is patched instead of rebuilt. Block tables must only have
+        grown (no window gave pages back). Returns None if the last step was not such a step."""
+        last = self._last
+        if last is None or last["key"] != (tuple(request_ids), max(pad_to, len(request_ids))):
+            return None
+        n_real, off, host = last["num_real"], last["offsets"], self._host_np
+        if self._copy_pending:
+            self._copied.synchronize()
+        host[off["ids"][0]:off["ids"][0] + n_real] = tokens
+        host[off["pos"][0]:off["pos"][0] + n_real] = starts
+        host[off["starts"][0]:off["starts"][0] + n_real] = starts
+        ctx_lens = [st + 1 for st in starts]
+        host[off["ctx"][0]:off["ctx"][0] + n_real] = ctx_lens
+        for g in range(self.num_groups):
+            base, w, lens = off[f"bt{g}"][0], last["widths"][g], last["table_lens"][g]
+            for i, tb in enumerate(tables[g]):
+                if len(tb) != lens[i]:
+                    if len(tb) < lens[i] or len(tb) > w:
+                        self._last = None
+                        return None
+                    host[base + i * w + lens[i]:base + i * w + len(tb)] = tb[lens[i]:]
+                    lens[i] = len(tb)
+        n = last["words"]
+        self.dev[:n].copy_(self.host[:n], non_blocking=True)
+        self.bytes_copied += 4 * n
+        self._copied.record()
+        self._copy_pending = True
+        ctx = last["ctx"]
+        ctx.starts = list(starts)
+        ctx.max_context = max(ctx_lens)          # padding rows have context 1
+        return ctx

@@ -41,6 +41,7 @@ class ModelRunner:
         self.steps_run = 0
         self.cuda_graphs = (cuda_graphs and self.device.type == "cuda"
                             and all(b.mixer.graph_safe for b in model.blocks))
+        self._tables_only_grow = all(g.need.window is None for g in self.manager.groups)
         self._graphs = {}          # (requests, split bucket) -> (graph, static logits)
         self._graph_pool = None
         self.graph_replays = 0
@@ -92,10 +93,15 @@ class ModelRunner:
         pad_to = 0
         if decode_only:
             pad_to = min(graph_batch_size(len(entries)), self.buffers.max_seqs)
-        ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables,
-                                 fixed_layout=decode_only, pad_to=pad_to,
-                                 pad_pages=[CacheStorage.dump_page(self.manager, g) for g in range(num_groups)])
-        self._bind_views(ctx)
+        ctx = None
+        if decode_only and self._tables_only_grow:
+            # the same requests as in the step before, one more token each: patch the staged arrays
+            ctx = self.buffers.advance_decode(ids, pad_to, [int(e.tokens[0]) for e in entries], starts, tables)
+        if ctx is None:
+            ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables,
+                                     fixed_layout=decode_only, pad_to=pad_to,
+                                     pad_pages=[CacheStorage.dump_page(self.manager, g) for g in range(num_groups)])
+            self._bind_views(ctx)
         logits = self._graph_forward(ctx) if decode_only else self.model.forward(ctx)
         for e, start in zip(entries, starts):
             self.manager.commit(e.request_id, start + len(e.tokens))

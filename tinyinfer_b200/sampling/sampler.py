@@ -5,6 +5,7 @@ from __future__ import annotations
 
 from typing import List, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -15,6 +16,8 @@ class Sampler:
     def __init__(self, device, engine_seed: int = 0):
         self.device = torch.device(device)
         self.engine_seed = int(engine_seed)
+        self._staging = None               # pinned host words the per-row parameters are staged in
+        self._staging_np = None
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                stream_ids: Sequence[int], steps: Sequence[int], with_nll: bool = False):
@@ -38,17 +41,24 @@ class Sampler:
         vocab = logits.shape[1]
         if all(p.greedy for p in params):
             return ops.argmax(logits)
-        # the reference refuses top-k above the vocabulary (sampler.py:56-57); here it is 'off'
-        host = torch.tensor(
-            [[float(p.temperature) for p in params]], dtype=torch.float32)
-        ints = torch.tensor([
-            [0 if p.topk >= vocab else p.topk for p in params],
-            [1 if p.greedy else 0 for p in params],
-            [int(s) & 0x7FFFFFFF for s in stream_ids],
-            [int(s) & 0x7FFFFFFF for s in steps]], dtype=torch.int32)
-        seeds = torch.tensor([self.engine_seed if p.seed is None else int(p.seed) for p in params],
-                             dtype=torch.int64)
-        temp = host.to(self.device)[0].contiguous()
-        ints = ints.to(self.device)
-        return ops.sample(logits, temp, ints[0].contiguous(), ints[1].contiguous(),
-                          seeds.to(self.device), ints[2].contiguous(), ints[3].contiguous())
+        # the reference refuses top-k above the vocabulary (sampler.py:56-57); here it is 'off'.
+        # All per-row parameters travel in ONE staged array: [seed low/high words | temperature bits |
+        # top-k | greedy | stream | step], each a run of `width` 32-bit words.
+        width = (n + 3) // 4 * 4                                   # runs start on 16-byte boundaries
+        words = 7 * width
+        if self._staging is None or self._staging.numel() < words:
+            self._staging = torch.empty(max(words, 7 * 64), dtype=torch.int32,
+                                        pin_memory=self.device.type == "cuda")
+            self._staging_np = self._staging.numpy()
+        host = self._staging_np
+        seeds = np.asarray([self.engine_seed if p.seed is None else int(p.seed) for p in params], dtype=np.int64)
+        host[:2 * n] = seeds.view(np.int32)
+        host[2 * width:2 * width + n] = np.asarray([float(p.temperature) for p in params], dtype=np.float32).view(np.int32)
+        host[3 * width:3 * width + n] = [0 if p.topk >= vocab else p.topk for p in params]
+        host[4 * width:4 * width + n] = [1 if p.greedy else 0 for p in params]
+        host[5 * width:5 * width + n] = [int(x) & 0x7FFFFFFF for x in stream_ids]
+        host[6 * width:6 * width + n] = [int(x) & 0x7FFFFFFF for x in steps]
+        dev = self._staging[:words].to(self.device, non_blocking=True)
+        return ops.sample(logits, dev[2 * width:2 * width + n].view(torch.float32), dev[3 * width:3 * width + n],
+                          dev[4 * width:4 * width + n], dev[:2 * n].view(torch.int64),
+                          dev[5 * width:5 * width + n], dev[6 * width:6 * width + n])
