@@ -109,7 +109,10 @@ def test_linear_rows_do_not_depend_on_the_batch(ops, dtype):
 
 # the tensor-core path: tiles that wrap the pipeline, many tiles per CTA, every small-batch width
 TC_SHAPES = [(1, 4096, 4096), (8, 6144, 4096), (16, 1000, 512), (17, 520, 264), (33, 4096, 1024), (64, 389, 320),
-             (65, 256, 128), (128, 128, 64), (200, 1000, 4096), (2048, 4096, 512), (777, 1032, 1096), (3, 40, 8)]
+             (65, 256, 128), (128, 128, 64), (200, 1000, 4096), (2048, 4096, 512), (777, 1032, 1096), (3, 40, 8),
+             # 65..128 tokens with the weights on the accumulator lanes and a cut k loop; 256 x 256 tiles
+             # with ragged edges in every direction
+             (100, 4096, 4096), (128, 1000, 2048), (1500, 5000, 136)]
 
 
 @pytest.mark.parametrize("m,n,k", TC_SHAPES)
@@ -125,7 +128,7 @@ def test_linear_tensor_cores(ops, m, n, k):
 
 
 @pytest.mark.parametrize("m,inter,k", [(1, 12288, 4096), (8, 1000, 512), (20, 448, 320), (64, 100, 96), (65, 176, 96),
-                                       (300, 448, 320), (2048, 1024, 256), (130, 72, 40)])
+                                       (300, 448, 320), (2048, 1024, 256), (130, 72, 40), (1500, 2500, 136)])
 def test_gated_linear_tensor_cores(ops, m, inter, k):
     dtype = torch.bfloat16
     x, w = rnd(m, k, dtype=dtype), rnd(2 * inter, k, dtype=dtype, seed=1, std=k ** -0.5)

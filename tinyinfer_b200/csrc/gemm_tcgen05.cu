@@ -46,26 +46,32 @@ struct GemmParams {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.f + __expf(-g))) * u; }
 
-template <int BN>
+// TM: accumulators of 128 rows a tile holds. 1: tiles of 128 x BN with two accumulators in tensor memory,
+// so that the epilogue of a tile overlaps the MMAs of the next. 2 (only with BN = 256, many tokens): tiles of
+// 256 x 256, both accumulators belong to one tile and every tile of w is used by two MMAs: an SM takes in
+// about 64 bytes a cycle from L2, and a 128 x 256 tile needs 48 KB for 512 cycles of MMAs (it waits for
+// its operands a third of the time), a 256 x 256 tile 64 KB for 1024 cycles.
+template <int BN, int TM = 1>
 struct Cfg {
-    static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
-    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;        // two accumulators; a power of two
+    static_assert(TM == 1 || (TM == 2 && BN == 256), "tall tiles are 256 x 256");
+    static constexpr int STAGE_BYTES = (TM * BM + BN) * BK * 2;
+    static constexpr int TMEM_COLS = TM == 2 ? 512 : (2 * BN < 32 ? 32 : 2 * BN);   // two accumulators; a power of two
     static constexpr int EXCH_FLOATS = BN <= 64 ? 64 * (BN + 1) + 2 : 2;   // swapped gated epilogue (BN <= 64) + one word
     // small-batch tiles (BN <= 64) take half an SM's shared memory, so that two CTAs share an SM: one
     // streams weights while the other reduces and stores, and the next kernel's CTAs can move in early
     static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
-    static constexpr int BUDGET = SMEM_BUDGET / CTAS_PER_SM - EXCH_FLOATS * 4;
+    static constexpr int BUDGET = (TM == 2 ? 216 * 1024 : SMEM_BUDGET / CTAS_PER_SM) - EXCH_FLOATS * 4;
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 12 ? 12 : (BUDGET / STAGE_BYTES);
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EXCH_FLOATS * 4 + 256;
     static_assert(STAGES >= 2, "too little shared memory for a pipeline");
     static_assert(CTAS_PER_SM * (SMEM_BYTES + 1024) <= 227 * 1024, "the CTAs of an SM do not fit its shared memory");
 };
 
-template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, Cfg<BN>::CTAS_PER_SM)
+template <int BN, int TM>
+__global__ void __launch_bounds__(NUM_THREADS, Cfg<BN, TM>::CTAS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     const GemmParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, TM>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stages = smem;
@@ -84,7 +90,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     ti_grid_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // tiles: gated normal tiles hold BN/2 gate and BN/2 up columns; gated swapped tiles 64 + 64 rows
-    const int rows_per_tile = (p.gated && p.swap) ? BM / 2 : BM;
+    const int rows_per_tile = (p.gated && p.swap) ? BM / 2 : TM * BM;
     const int cols_per_tile = (p.gated && !p.swap) ? BN / 2 : BN;
     const int row_tiles = (p.rows_total + rows_per_tile - 1) / rows_per_tile;
     const int col_tiles = (p.cols_total + cols_per_tile - 1) / cols_per_tile;
@@ -117,7 +123,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 const int rt = tile % row_tiles, ct = tile / row_tiles;
                 const int r0 = rt * rows_per_tile, c0 = ct * cols_per_tile;
                 const uint32_t a_dst = smem_u32(stages + s * C::STAGE_BYTES);
-                const uint32_t b_dst = a_dst + BM * BK * 2;
+                const uint32_t b_dst = a_dst + TM * BM * BK * 2;      // tall tiles: one copy of 256 rows
                 if (rows_side) {
                     if (p.gated && p.swap) {          // 64 gate rows, then 64 up rows
                         tma_load_2d(a_dst, &map_rows, full_bar(s), kb * BK, r0);
@@ -188,7 +194,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 const int split = unit % p.splits;
                 const int kb0 = (int)((long long)split * num_kb / p.splits);
                 const int kb1 = (int)((long long)(split + 1) * num_kb / p.splits);
-                const uint32_t as = tile_i & 1u, aph = (tile_i >> 1) & 1u;
+                // tall tiles own all of tensor memory: one accumulator buffer, a phase per tile
+                const uint32_t as = TM == 2 ? 0u : (tile_i & 1u), aph = TM == 2 ? (tile_i & 1u) : ((tile_i >> 1) & 1u);
                 if (!mbar_wait(acc_empty_bar(as), aph ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
                 tmem_fence_after();
                 const uint32_t d_tmem = tmem_base + as * BN;
@@ -199,11 +206,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     tmem_fence_after();
                     const uint32_t a_addr = smem_u32(stages + s * C::STAGE_BYTES);
                     const uint64_t adesc = make_sw128_desc(a_addr);
-                    const uint64_t bdesc = make_sw128_desc(a_addr + BM * BK * 2);
+                    const uint64_t bdesc = make_sw128_desc(a_addr + TM * BM * BK * 2);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // 16 bf16 = 32 bytes along K inside the 128-byte swizzled row: +2 in 16-byte units
                         umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        if constexpr (TM == 2)      // rows 128..255 of the tile: 16 KB further in the stage, next 256 columns
+                            umma_bf16(d_tmem + BN, make_sw128_desc(a_addr + BM * BK * 2) + 2u * k, bdesc + 2u * k, idesc,
+                                      (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));           // the stage is free once these MMAs have read it
                 }
@@ -221,10 +231,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             const int tile = unit / p.splits, split = unit % p.splits;
             const int rt = tile % row_tiles, ct = tile / row_tiles;
             const int r0 = rt * rows_per_tile, c0 = ct * cols_per_tile;
-            const uint32_t as = tile_i & 1u, aph = (tile_i >> 1) & 1u;
+            const uint32_t as = TM == 2 ? 0u : (tile_i & 1u), aph = TM == 2 ? (tile_i & 1u) : ((tile_i >> 1) & 1u);
             if (!mbar_wait(acc_full_bar(as), aph, abort_flag, p.status, 14)) { ok = false; break; }
             tmem_fence_after();
-            const uint32_t t_addr = tmem_base + as * BN + ((uint32_t)(lane_group * 32) << 16);
+            const uint32_t t_addr0 = tmem_base + as * BN + ((uint32_t)(lane_group * 32) << 16);
+            const uint32_t t_addr = t_addr0;
             float v[16], u[16];
             bool released = false;
             // Split k range: every unit leaves its partial accumulator in scratch; the unit that
@@ -375,7 +386,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 }
             };
             if (!p.swap) {
-                const int m = r0 + row_in_tile;
+              for (int hm = 0; hm < TM; ++hm) {                 // the tile's accumulators of 128 rows, one after the other
+                const uint32_t t_addr = t_addr0 + hm * BN;
+                const int m = r0 + hm * BM + row_in_tile;
                 const bool row_ok = m < p.M;
                 if (!p.gated) {
                     for (int c = 0; c < BN; c += 16) {
@@ -459,6 +472,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                         }
                     }
                 }
+              }
             } else {
                 // swapped: this thread owns output feature n, the columns are tokens
                 if (!p.gated) {
@@ -557,18 +571,19 @@ int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int
     return best;
 }
 
-template <int BN>
+template <int BN, int TM = 1>
 int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmParams& p, int num_tiles, cudaStream_t stream) {
+    using C = Cfg<BN, TM>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
-        if (e != cudaSuccess) { ti_set_error("gemm_tcgen05: cannot get %d bytes of shared memory: %s", Cfg<BN>::SMEM_BYTES, cudaGetErrorString(e)); return (int)e; }
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) { ti_set_error("gemm_tcgen05: cannot get %d bytes of shared memory: %s", C::SMEM_BYTES, cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
     num_tiles *= p.splits;
-    const int slots = ti_sm_count() * Cfg<BN>::CTAS_PER_SM;
+    const int slots = ti_sm_count() * C::CTAS_PER_SM;
     const int grid = num_tiles < slots ? num_tiles : slots;
-    ti_launch(gemm_tcgen05_kernel<BN>, grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream, rows_map, cols_map, p);
+    ti_launch(gemm_tcgen05_kernel<BN, TM>, grid, NUM_THREADS, C::SMEM_BYTES, stream, rows_map, cols_map, p);
     TI_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }
@@ -630,6 +645,21 @@ TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bi
     if (wide) {
         if (!ti_get_bf16_map(w, w_rows, K, gated ? 128 : 256, &cols_map)) return -1;
         const int cpt = gated ? 128 : 256;
+        const long long col_tiles = (N + cpt - 1) / cpt;
+        // 256 x 256 tiles if they finish sooner: a wave of them was measured to take 1.77 times a wave of
+        // 128 x 256 tiles (twice the MMAs for 4/3 of the operand bytes, but three stages of 64 KB keep
+        // fewer bytes in flight than four of 48 KB, and no epilogue runs behind the next tile's MMAs).
+        // Inside a prefill step they paid from about 3,000 tokens on (4,096 tokens: 7.5 % off the step;
+        // 2,048 tokens: 2 % on, although the products alone were faster), hence the lower bound.
+        const int sms = ti_sm_count();
+        const long long tall_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * col_tiles;
+        const long long waves = (row_tiles * col_tiles + sms - 1) / sms, tall_waves = (tall_tiles + sms - 1) / sms;
+        static const int forced = [] { const char* e = getenv("TINYINFER_B200_GEMM_TALL"); return e ? atoi(e) : -1; }();
+        const bool tall = forced >= 0 ? (forced != 0 && M > BM) : (M >= 3072 && tall_waves * 177 < waves * 100);
+        if (tall) {
+            if (!ti_get_bf16_map(x, M, K, 2 * BM, &rows_map)) return -1;
+            return launch<256, 2>(rows_map, cols_map, p, (int)tall_tiles, stream);
+        }
         return launch<256>(rows_map, cols_map, p, row_tiles * ((N + cpt - 1) / cpt), stream);
     }
     if (!ti_get_bf16_map(w, w_rows, K, gated ? 64 : 128, &cols_map)) return -1;
