@@ -112,7 +112,7 @@ TC_SHAPES = [(1, 4096, 4096), (8, 6144, 4096), (16, 1000, 512), (17, 520, 264), 
              (65, 256, 128), (128, 128, 64), (200, 1000, 4096), (2048, 4096, 512), (777, 1032, 1096), (3, 40, 8),
              # 65..128 tokens with the weights on the accumulator lanes and a cut k loop; 256 x 256 tiles
              # with ragged edges in every direction
-             (100, 4096, 4096), (128, 1000, 2048), (1500, 5000, 136)]
+             (100, 4096, 4096), (128, 1000, 2048), (1500, 5000, 136), (3100, 2600, 72)]
 
 
 @pytest.mark.parametrize("m,n,k", TC_SHAPES)
@@ -128,7 +128,7 @@ def test_linear_tensor_cores(ops, m, n, k):
 
 
 @pytest.mark.parametrize("m,inter,k", [(1, 12288, 4096), (8, 1000, 512), (20, 448, 320), (64, 100, 96), (65, 176, 96),
-                                       (300, 448, 320), (2048, 1024, 256), (130, 72, 40), (1500, 2500, 136)])
+                                       (300, 448, 320), (2048, 1024, 256), (130, 72, 40), (1500, 2500, 136), (3100, 1300, 72)])
 def test_gated_linear_tensor_cores(ops, m, inter, k):
     dtype = torch.bfloat16
     x, w = rnd(m, k, dtype=dtype), rnd(2 * inter, k, dtype=dtype, seed=1, std=k ** -0.5)
