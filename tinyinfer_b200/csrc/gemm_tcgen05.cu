@@ -242,7 +242,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             // arrives last sums all partials of the tile in split order (so the result does not
             // depend on who was last) and runs the epilogue.
             float* tile_partials = nullptr;
-            if (p.splits > 1) {
+            if (p.splits > 1 && p.swap) {
                 tile_partials = p.partials + (size_t)tile * p.splits * BN * BM;
                 float* mine = tile_partials + (size_t)split * BN * BM + row_in_tile;
                 for (int c = 0; c < BN; c += 16) {
@@ -385,6 +385,135 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     tmem_ld16(t_addr + c, dst);
                 }
             };
+            // bias, residual and store of 16 consecutive outputs of row m (tokens on the lanes, not gated)
+            auto finish16 = [&](int m, int n0, float* v) {
+                const size_t base = (size_t)m * p.N + n0;
+                const bool full16 = n0 + 16 <= p.N;
+                if (p.bias) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) if (n0 + i < p.N) v[i] += p.bias[n0 + i];
+                }
+                if (p.residual) {
+                    if (full16 && (base & 7) == 0) {
+                        const uint4* r4 = reinterpret_cast<const uint4*>(p.residual + base);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint4 q = r4[h];
+                            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 f = __bfloat1622float2(b2[i]);
+                                v[h * 8 + 2 * i] += f.x;
+                                v[h * 8 + 2 * i + 1] += f.y;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) if (n0 + i < p.N) v[i] += __bfloat162float(p.residual[base + i]);
+                    }
+                }
+                if (p.out_f32) {
+                    float* o = reinterpret_cast<float*>(p.out) + base;
+                    if (full16 && (base & 3) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) if (n0 + i < p.N) o[i] = v[i];
+                    }
+                } else {
+                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + base;
+                    if (full16 && (base & 7) == 0) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint4 q;
+                            __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) b2[i] = __floats2bfloat162_rn(v[h * 8 + 2 * i], v[h * 8 + 2 * i + 1]);
+                            reinterpret_cast<uint4*>(o)[h] = q;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) if (n0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
+                    }
+                }
+            };
+            if (!p.swap && p.splits > 1) {
+                // Tokens on the lanes with a cut k loop (few tiles, many tokens): every unit of a tile
+                // leaves its partial accumulator in scratch, waits until the other units of the tile have
+                // done so (they all run at once: the host launches one CTA per unit and no more units than
+                // SMs), then adds up and finishes its share of the columns, every 16-column chunk c with
+                // c mod splits == split, in split order. The sum is spread over the units instead of being
+                // left to the last one.
+                // scratch layout [split][column / 4][row][4 columns]: the 32 lanes of a warp (32 rows) write and
+                // read 512 consecutive bytes with every 16-byte access
+                float4* tile_part = reinterpret_cast<float4*>(p.partials + (size_t)tile * p.splits * BM * BN);
+                float4* mine = tile_part + (size_t)split * (BN / 4) * BM + row_in_tile;
+                for (int c = 0; c < BN; c += 16) {
+                    tmem_ld16(t_addr0 + c, v);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        __stcg(mine + (size_t)(c / 4 + q) * BM, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                }
+                tmem_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(as));
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    __threadfence();
+                    atomicAdd(p.counters + tile, 1);
+                    int all_there = 1;
+                    const long long t_start = clock64();
+                    for (uint32_t spin = 1; *reinterpret_cast<volatile int*>(p.counters + tile) < p.splits; ++spin) {
+                        __nanosleep(100);
+                        if ((spin & 63u) == 0u && (*abort_flag || clock64() - t_start > 4000000000ll)) { all_there = 0; break; }
+                    }
+                    __threadfence();
+                    *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]) = all_there;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int all_there = *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!all_there) {                                  // a unit of the tile never came: give up, loudly
+                    *abort_flag = 1;
+                    if (p.status && threadIdx.x == 64) atomicExch(p.status, 15);
+                    ok = false;
+                    break;
+                }
+                const int m = r0 + row_in_tile;
+                for (int ch = split; ch < BN / 16; ch += p.splits) {
+                    const int n0 = c0 + ch * 16;
+                    if (n0 >= p.N) break;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
+                        float4 part[4][4];
+#pragma unroll
+                        for (int sp = 0; sp < 4; ++sp) {
+                            const bool in = sp0 + sp < p.splits;
+                            const float4* src = tile_part + ((size_t)(in ? sp0 + sp : 0) * (BN / 4) + ch * 4) * BM + row_in_tile;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) part[sp][q] = in ? __ldcg(src + (size_t)q * BM) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int sp = 0; sp < 4; ++sp) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                v[4 * q] += part[sp][q].x; v[4 * q + 1] += part[sp][q].y;
+                                v[4 * q + 2] += part[sp][q].z; v[4 * q + 3] += part[sp][q].w;
+                            }
+                        }
+                    }
+                    if (m < p.M) finish16(m, n0, v);
+                }
+                // second arrival: when every unit has read what it needs, the last one clears the counter
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    if (atomicAdd(p.counters + tile, 1) == 2 * p.splits - 1) p.counters[tile] = 0;
+                }
+                continue;
+            }
             if (!p.swap) {
               for (int hm = 0; hm < TM; ++hm) {                 // the tile's accumulators of 128 rows, one after the other
                 const uint32_t t_addr = t_addr0 + hm * BN;
@@ -395,57 +524,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                         tmem_ld16(t_addr + c, v);
                         const int n0 = c0 + c;
                         if (!row_ok || n0 >= p.N) continue;
-                        const size_t base = (size_t)m * p.N + n0;
-                        const bool full16 = n0 + 16 <= p.N;
-                        if (p.bias) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) if (n0 + i < p.N) v[i] += p.bias[n0 + i];
-                        }
-                        if (p.residual) {
-                            if (full16 && (base & 7) == 0) {
-                                const uint4* r4 = reinterpret_cast<const uint4*>(p.residual + base);
-#pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    const uint4 q = r4[h];
-                                    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-                                    for (int i = 0; i < 4; ++i) {
-                                        const float2 f = __bfloat1622float2(b2[i]);
-                                        v[h * 8 + 2 * i] += f.x;
-                                        v[h * 8 + 2 * i + 1] += f.y;
-                                    }
-                                }
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) if (n0 + i < p.N) v[i] += __bfloat162float(p.residual[base + i]);
-                            }
-                        }
-                        if (p.out_f32) {
-                            float* o = reinterpret_cast<float*>(p.out) + base;
-                            if (full16 && (base & 3) == 0) {
-#pragma unroll
-                                for (int i = 0; i < 4; ++i)
-                                    reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) if (n0 + i < p.N) o[i] = v[i];
-                            }
-                        } else {
-                            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + base;
-                            if (full16 && (base & 7) == 0) {
-#pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    uint4 q;
-                                    __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&q);
-#pragma unroll
-                                    for (int i = 0; i < 4; ++i) b2[i] = __floats2bfloat162_rn(v[h * 8 + 2 * i], v[h * 8 + 2 * i + 1]);
-                                    reinterpret_cast<uint4*>(o)[h] = q;
-                                }
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) if (n0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
-                            }
-                        }
+                        finish16(m, n0, v);
                     }
                 } else {
                     // columns [0, BN/2) hold the gate, [BN/2, BN) the up projection of the same outputs
@@ -640,7 +719,22 @@ TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bi
     if (wide) {
         const int cpt256 = gated ? 128 : 256;
         const long long tiles256 = (long long)row_tiles * ((N + cpt256 - 1) / cpt256);
-        if (tiles256 * 2 <= ti_sm_count()) wide = false;
+        // Few tiles, many tokens (about 130 to 700 of them): the k loops are cut so that as many units as
+        // there are SMs run at once, and the units of a tile add their partial sums up together.
+        static const bool spread = [] { const char* e = getenv("TINYINFER_B200_GEMM_SPREAD"); return !e || atoi(e) != 0; }();
+        const int sms = ti_sm_count(), num_kb = (K + BK - 1) / BK;
+        if (spread && !gated && workspace && counters && tiles256 <= num_counters && tiles256 * 2 <= sms) {
+            int cut = (int)(sms / tiles256);
+            cut = cut < 8 ? cut : 8;
+            cut = cut < num_kb / 8 ? cut : num_kb / 8;
+            while (cut > 1 && tiles256 * cut * BM * 256 > workspace_floats) --cut;
+            if (cut > 1) {
+                p.splits = cut;
+                if (!ti_get_bf16_map(w, w_rows, K, 256, &cols_map)) return -1;
+                return launch<256>(rows_map, cols_map, p, (int)tiles256, stream);
+            }
+        }
+        if (tiles256 * 2 <= sms) wide = false;
     }
     if (wide) {
         if (!ti_get_bf16_map(w, w_rows, K, gated ? 128 : 256, &cols_map)) return -1;
