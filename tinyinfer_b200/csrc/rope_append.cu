@@ -83,7 +83,7 @@ __global__ void qk_norm_rope_append_kernel(
 // Head sizes 64 and 128 with the rotation over the whole head (or none): a lane owns D / 32
 // neighbouring features, loads and stores them as one vector, and gets its rotation partner
 // (the feature D / 2 away) from the lane 16 further on.
-template <typename T, int D>
+template <typename T, int D, int HPW>
 __global__ void __launch_bounds__(RA_WARPS * 32) qk_norm_rope_append_vec_kernel(
     T* __restrict__ q_out, const T* __restrict__ qkv, T* __restrict__ k_cache, T* __restrict__ v_cache,
     const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
@@ -93,64 +93,76 @@ __global__ void __launch_bounds__(RA_WARPS * 32) qk_norm_rope_append_vec_kernel(
     int hq, int hkv, int page_size, int num_pages, int* __restrict__ status) {
     constexpr int VEC = D / 32;
     struct alignas(sizeof(T) * VEC) Pack { T e[VEC]; };
+    __shared__ float cos_sh[D / 2], sin_sh[D / 2];
     ti_grid_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.x * RA_WARPS + warp;
+    const int head0 = (blockIdx.x * RA_WARPS + warp) * HPW;        // a warp takes HPW heads of the token
     const int t = blockIdx.y;
     const int heads_total = hq + 2 * hkv;
-    if (head >= heads_total) return;
-    const bool is_q = head < hq;
-    const bool is_k = !is_q && head < hq + hkv;
-    if (!is_q && k_cache == nullptr) return;
-    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
-    float wv[VEC], fr[VEC];
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {                 // constants: read before the wait
-        wv[i] = w ? w[lane * VEC + i] : 1.f;
-        fr[i] = inv_freq ? inv_freq[(lane & 15) * VEC + i] : 0.f;
-    }
-    ti_grid_wait();
-    const Pack in = *reinterpret_cast<const Pack*>(qkv + ((size_t)t * heads_total + head) * D + lane * VEC);
-    float x[VEC];
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        x[i] = to_f32(in.e[i]);
-        ss += x[i] * x[i];
-    }
-    if (w != nullptr) {
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)D + eps);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) x[i] = wv[i] * x[i] * inv;
-    }
+    // The angles of a token are the same for all its heads: the block works them out once (sincosf is
+    // most of this kernel's arithmetic), from the step's positions, which were on the device before the
+    // step's first kernel began, so this happens before the wait for the kernel ahead.
     const int pos = positions[t];
-    if ((is_q || is_k) && inv_freq != nullptr) {
-        const float pos_f = (float)pos;
+    if (inv_freq != nullptr && threadIdx.x < D / 2 && blockIdx.x * RA_WARPS * HPW < hq + hkv)
+        sincosf((float)pos * inv_freq[threadIdx.x], &sin_sh[threadIdx.x], &cos_sh[threadIdx.x]);
+    __syncthreads();
+    if (head0 >= heads_total) return;
+    ti_grid_wait();
+    // all of the warp's loads first: with many tokens the kernel lives on the bytes it has in flight
+    Pack in[HPW];
+    bool live[HPW];
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        const int head = head0 + hh;
+        live[hh] = head < heads_total && (head < hq || k_cache != nullptr);
+        if (live[hh]) in[hh] = *reinterpret_cast<const Pack*>(qkv + ((size_t)t * heads_total + head) * D + lane * VEC);
+    }
+    int page = -2;                                                  // looked up when the first key or value head comes
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        if (!live[hh]) continue;
+        const int head = head0 + hh;
+        const bool is_q = head < hq;
+        const bool is_k = !is_q && head < hq + hkv;
+        const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+        float x[VEC];
+        float ss = 0.f;
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
-            float s, c;
-            sincosf(pos_f * fr[i], &s, &c);
-            x[i] = lane < 16 ? x[i] * c - other * s : x[i] * c + other * s;
+            x[i] = to_f32(in[hh].e[i]);
+            ss += x[i] * x[i];
         }
-    }
-    T* dst;
-    if (is_q) {
-        dst = q_out + ((size_t)t * hq + head) * D;
-    } else {
-        const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / page_size];
-        if (page < 0 || page >= num_pages) {
-            if (lane == 0 && status) atomicExch(status, 1);
-            return;
-        }
-        const int kvh = is_k ? head - hq : head - hq - hkv;
-        dst = (is_k ? k_cache : v_cache) + (((size_t)page * hkv + kvh) * page_size + pos % page_size) * D;
-    }
-    Pack o;
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)D + eps);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) o.e[i] = from_f32<T>(x[i]);
-    *reinterpret_cast<Pack*>(dst + lane * VEC) = o;
+            for (int i = 0; i < VEC; ++i) x[i] = w[lane * VEC + i] * x[i] * inv;
+        }
+        if ((is_q || is_k) && inv_freq != nullptr) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+                const float sn = sin_sh[(lane & 15) * VEC + i], cs = cos_sh[(lane & 15) * VEC + i];
+                x[i] = lane < 16 ? x[i] * cs - other * sn : x[i] * cs + other * sn;
+            }
+        }
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)t * hq + head) * D;
+        } else {
+            if (page == -2) page = block_table[(size_t)token_seq[t] * max_blocks + pos / page_size];
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0 && status) atomicExch(status, 1);
+                return;
+            }
+            const int kvh = is_k ? head - hq : head - hq - hkv;
+            dst = (is_k ? k_cache : v_cache) + (((size_t)page * hkv + kvh) * page_size + pos % page_size) * D;
+        }
+        Pack o;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o.e[i] = from_f32<T>(x[i]);
+        *reinterpret_cast<Pack*>(dst + lane * VEC) = o;
+    }
 }
 
 template <typename T>
@@ -161,12 +173,21 @@ static void launch_rope(T* q_out, const T* qkv, T* kc, size_t v_off, const float
     dim3 grid((hq + 2 * hkv + RA_WARPS - 1) / RA_WARPS, num_tokens);
     T* vc = kc ? kc + v_off : nullptr;
     const bool whole = inv_freq == nullptr || rotary_dim == d;
-    if (whole && d == 128)
-        ti_launch(qk_norm_rope_append_vec_kernel<T, 128>, grid, RA_WARPS * 32, 0, stream, q_out, qkv, kc, vc, q_norm_w,
-                  k_norm_w, eps, inv_freq, positions, token_seq, block_table, max_blocks, hq, hkv, page_size, num_pages, status);
+    // a warp takes one head of a token when tokens are few (a decode step wants the kernel short),
+    // four when they are many (more bytes in flight per warp)
+    const bool many = num_tokens >= 256;
+    const dim3 grid4((hq + 2 * hkv + 4 * RA_WARPS - 1) / (4 * RA_WARPS), num_tokens);
+#define TI_ROPE_ARGS q_out, qkv, kc, vc, q_norm_w, k_norm_w, eps, inv_freq, positions, token_seq, block_table, max_blocks, \
+                     hq, hkv, page_size, num_pages, status
+    if (whole && d == 128 && many)
+        ti_launch(qk_norm_rope_append_vec_kernel<T, 128, 4>, grid4, RA_WARPS * 32, 0, stream, TI_ROPE_ARGS);
+    else if (whole && d == 128)
+        ti_launch(qk_norm_rope_append_vec_kernel<T, 128, 1>, grid, RA_WARPS * 32, 0, stream, TI_ROPE_ARGS);
+    else if (whole && d == 64 && many)
+        ti_launch(qk_norm_rope_append_vec_kernel<T, 64, 4>, grid4, RA_WARPS * 32, 0, stream, TI_ROPE_ARGS);
     else if (whole && d == 64)
-        ti_launch(qk_norm_rope_append_vec_kernel<T, 64>, grid, RA_WARPS * 32, 0, stream, q_out, qkv, kc, vc, q_norm_w,
-                  k_norm_w, eps, inv_freq, positions, token_seq, block_table, max_blocks, hq, hkv, page_size, num_pages, status);
+        ti_launch(qk_norm_rope_append_vec_kernel<T, 64, 1>, grid, RA_WARPS * 32, 0, stream, TI_ROPE_ARGS);
+#undef TI_ROPE_ARGS
     else
         ti_launch(qk_norm_rope_append_kernel<T>, grid, RA_WARPS * 32, 0, stream, q_out, qkv, kc, vc, q_norm_w, k_norm_w,
                   eps, inv_freq, rotary_dim, positions, token_seq, block_table, max_blocks, hq, hkv, d, page_size,
