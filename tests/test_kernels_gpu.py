@@ -127,6 +127,39 @@ def test_linear_tensor_cores(ops, m, n, k):
     ops.check_kernel_status()
 
 
+@pytest.mark.parametrize("m,k0,h,inter,eps", [(1, 512, 1024, 768, 1e-6), (8, 4096, 4096, 1536, 1e-6),
+                                            (33, 1024, 520, 200, 1e-5), (64, 1024, 2048, 1000, 1e-6)])
+def test_rmsnorm_shared_between_two_products(ops, m, k0, h, inter, eps):
+    """For few tokens the product that makes a residual stream x also leaves x * g and the sums of squares
+    of x's rows; the products behind the norm read x * g and scale their rows by 1 / rms: the same
+    results as product, norm kernel, product."""
+    dtype = torch.bfloat16
+    a, w0 = rnd(m, k0, dtype=dtype), rnd(h, k0, dtype=dtype, seed=1, std=k0 ** -0.5)
+    res = rnd(m, h, dtype=dtype, seed=2)
+    g = (1 + 0.1 * rnd(h, dtype=torch.float32, seed=3)).contiguous()
+    x, link = ops.linear(a, w0, residual=res, next_norm_weight=g)
+    close(x, ref.linear(a, w0, residual=res), dtype)
+    assert link is not None, "this shape was expected to cut its k loop and leave a link"
+    torch.testing.assert_close(link.sums[:link.parts].sum(dim=0), (x.float() ** 2).sum(dim=1), rtol=1e-4, atol=1e-4)
+    close(link.scaled, (x.float() * g).to(dtype), dtype)
+    # the plain statement with the norm's result NOT rounded to bfloat16 in between: the shared norm rounds
+    # x * g where the norm kernel rounds x * g / rms, so either differs from this by one rounding of the input
+    normed = ref.rmsnorm(x.float(), g, eps)
+    w1 = rnd(inter, h, dtype=dtype, seed=4, std=h ** -0.5)
+    bias = rnd(inter, dtype=torch.float32, seed=5)
+    close(ops.linear(link.scaled, w1, bias=bias, link=link, link_eps=eps),
+          ref.linear(normed, w1.float(), bias=bias).to(dtype), dtype)
+    res2 = rnd(m, inter, dtype=dtype, seed=7)
+    close(ops.linear(link.scaled, w1, residual=res2, link=link, link_eps=eps),
+          ref.linear(normed, w1.float(), residual=res2.float()).to(dtype), dtype)
+    w2 = rnd(2 * inter, h, dtype=dtype, seed=6, std=h ** -0.5)
+    close(ops.gated_linear(link.scaled, w2, link=link, link_eps=eps), ref.gated_linear(normed, w2.float()).to(dtype), dtype)
+    # more tokens than a link takes: no link, the plain product
+    big, none = ops.linear(rnd(65, k0, dtype=dtype), w0, next_norm_weight=g)
+    assert none is None and big.shape == (65, h)
+    ops.check_kernel_status()
+
+
 @pytest.mark.parametrize("m,inter,k", [(1, 12288, 4096), (8, 1000, 512), (20, 448, 320), (64, 100, 96), (65, 176, 96),
                                        (300, 448, 320), (2048, 1024, 256), (130, 72, 40), (1500, 2500, 136), (3100, 1300, 72)])
 def test_gated_linear_tensor_cores(ops, m, inter, k):

@@ -41,6 +41,17 @@ struct GemmParams {
     int splits;             // swapped only: the k range of a tile is cut into this many work units
     float* partials;        // [tile][split][col][128] float32 scratch for splits > 1
     int* counters;          // [tile] arrivals; zero before the launch and again after it
+    // Weights on the lanes only: an RMSNorm spread over two products. The product that makes a residual
+    // stream x also stores x * g (g: the weights of the norm that follows, rounded to bfloat16 like x) and,
+    // per 128 outputs and token, the sum of squares of x as rounded (emit_*). The product behind the norm
+    // reads x * g as its input and multiplies every output row by rsqrt(mean(x^2) + eps) (scale_*): the
+    // norm kernel between the two, and the hop it costs in a decode step, are gone.
+    const float* emit_g;            // [N] or null
+    __nv_bfloat16* emit_xg;         // [M, N]
+    float* emit_sums;               // [row tiles][M]
+    const float* scale_sums;        // [scale_parts][M] or null
+    int scale_parts, scale_dim;     // the rows of x had scale_dim elements
+    float scale_eps;
     int* status;
 };
 
@@ -85,6 +96,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + 2 + a); };
     __shared__ uint32_t tmem_base_sh;
     __shared__ int abort_sh;
+    __shared__ float row_scale_sh[128];     // scale_*: 1 / rms of every token of the tile (1 if no scale)
     volatile int* abort_flag = &abort_sh;
 
     ti_grid_launch_dependents();
@@ -227,6 +239,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         const int row_in_tile = lane_group * 32 + lane;
         uint32_t tile_i = 0;
         bool ok = true;
+        if (p.swap) {                                    // tokens are columns: at most BN <= 128 of them, one column tile
+            float sc = 1.f;
+            if (p.scale_sums != nullptr && row_in_tile < p.M) {
+                float ss = 0.f;
+                for (int part = 0; part < p.scale_parts; ++part) ss += p.scale_sums[(size_t)part * p.M + row_in_tile];
+                sc = rsqrtf(ss / (float)p.scale_dim + p.scale_eps);
+            }
+            row_scale_sh[row_in_tile] = sc;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++tile_i) {
             const int tile = unit / p.splits, split = unit % p.splits;
             const int rt = tile % row_tiles, ct = tile / row_tiles;
@@ -278,14 +300,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     ((uintptr_t)p.residual & 7) == 0 && ((uintptr_t)p.bias & 15) == 0) {
                     const int n0 = r0 + 4 * lane;
                     const bool n_ok = n0 < p.N;                        // N is a multiple of 4: all four rows or none
-                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), g4 = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (p.bias && n_ok) b4 = *reinterpret_cast<const float4*>(p.bias + n0);
+                    if (p.emit_g && n_ok) g4 = *reinterpret_cast<const float4*>(p.emit_g + n0);
                     const int cols_real = min(BN, p.M - c0);
                     auto wide = [&](auto cols_tag, auto splits_tag) {
                         constexpr int G = decltype(cols_tag)::value, SP = decltype(splits_tag)::value;
                         for (int g0 = lane_group; g0 < cols_real; g0 += 4 * G) {
                             float4 acc[G];
                             uint2 res[G];
+                            float sq[G];
+#pragma unroll
+                            for (int i = 0; i < G; ++i) sq[i] = 0.f;
 #pragma unroll
                             for (int i = 0; i < G; ++i) {
                                 acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -322,8 +348,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                 if (!n_ok || col >= cols_real) continue;
                                 const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&res[i]);
                                 const float2 ra = __bfloat1622float2(r2[0]), rb = __bfloat1622float2(r2[1]);
-                                const float4 v4 = make_float4(acc[i].x + b4.x + ra.x, acc[i].y + b4.y + ra.y,
-                                                              acc[i].z + b4.z + rb.x, acc[i].w + b4.w + rb.y);
+                                const float sc = row_scale_sh[col];
+                                const float4 v4 = make_float4(acc[i].x * sc + b4.x + ra.x, acc[i].y * sc + b4.y + ra.y,
+                                                              acc[i].z * sc + b4.z + rb.x, acc[i].w * sc + b4.w + rb.y);
                                 const size_t idx = (size_t)(c0 + col) * p.N + n0;
                                 if (p.out_f32) {
                                     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + idx) = v4;
@@ -333,6 +360,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                     o2.x = *reinterpret_cast<uint32_t*>(&lo2);
                                     o2.y = *reinterpret_cast<uint32_t*>(&hi2);
                                     *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + idx) = o2;
+                                    if (p.emit_g != nullptr) {           // x * g of the rounded x, and the squares of x
+                                        const float2 xa = __bfloat1622float2(lo2), xb = __bfloat1622float2(hi2);
+                                        sq[i] = xa.x * xa.x + xa.y * xa.y + xb.x * xb.x + xb.y * xb.y;
+                                        __nv_bfloat162 ga = __floats2bfloat162_rn(xa.x * g4.x, xa.y * g4.y);
+                                        __nv_bfloat162 gb = __floats2bfloat162_rn(xb.x * g4.z, xb.y * g4.w);
+                                        uint2 e2;
+                                        e2.x = *reinterpret_cast<uint32_t*>(&ga);
+                                        e2.y = *reinterpret_cast<uint32_t*>(&gb);
+                                        *reinterpret_cast<uint2*>(p.emit_xg + idx) = e2;
+                                    }
+                                }
+                            }
+                            if (p.emit_g != nullptr) {
+                                // the warp holds all 128 outputs of the tile for this token
+#pragma unroll
+                                for (int i = 0; i < G; ++i) {
+                                    const int col = g0 + 4 * i;                  // the same for the whole warp
+                                    if (col >= cols_real) continue;
+                                    float t = sq[i];
+#pragma unroll
+                                    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+                                    if (lane == 0) p.emit_sums[(size_t)rt * p.M + c0 + col] = t;
                                 }
                             }
                         }
@@ -572,7 +621,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                         for (int i = 0; i < 16; ++i) {
                             const int m = c0 + c + i;
                             if (m < p.M) {
-                                const float val = v[i] + b + u[i];
+                                const float val = v[i] * row_scale_sh[c + i] + b + u[i];
                                 const size_t idx = (size_t)m * p.N + n;
                                 if (p.out_f32) reinterpret_cast<float*>(p.out)[idx] = val;
                                 else reinterpret_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(val);
@@ -586,6 +635,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     const int jj = row_in_tile & 63;
                     for (int c = 0; c < BN; c += 16) {
                         load_chunk(c, v);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] *= row_scale_sh[c + i];        // gate and up alike
                         if (is_up) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) exch[jj * (BN + 1) + c + i] = v[i];
@@ -676,10 +727,54 @@ TI_API int ti_gemm_bf16_supported(int M, int N, int K) { return (M > 0 && N > 0 
 // out [M, N] = silu(x.gate) * (x.up). out_f32: out is float32. status: device word set if a wait ran out.
 // workspace / counters: float32 scratch and zeroed int32 words for the split-k path of small M (may be
 // null: then no tile is split). Calls that share them must be ordered on one stream.
+struct NormLink {                  // an RMSNorm spread over two products (see GemmParams)
+    const float* scale_sums = nullptr;
+    int scale_parts = 0, scale_dim = 0;
+    float scale_eps = 0.f;
+    const float* emit_g = nullptr;
+    void* emit_xg = nullptr;
+    float* emit_sums = nullptr;
+    int* emitted_parts = nullptr;  // host: how many parts of emit_sums were written (0: this shape cannot)
+};
+
+static int gemm_entry(void* out, const void* x, const void* w, const float* bias, const void* residual,
+                      int M, int N, int K, int gated, int out_f32, float* workspace, long long workspace_floats,
+                      int* counters, int num_counters, const NormLink& link, int* status, cudaStream_t stream);
+
 TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bias, const void* residual,
                         int M, int N, int K, int gated, int out_f32, float* workspace, long long workspace_floats,
                         int* counters, int num_counters, int* status, cudaStream_t stream) {
+    return gemm_entry(out, x, w, bias, residual, M, N, K, gated, out_f32, workspace, workspace_floats, counters,
+                      num_counters, NormLink(), status, stream);
+}
+
+// The same product for at most 64 tokens as one half of an RMSNorm spread over two products.
+// scale_sums (may be null): x holds rows of scale_dim elements times the norm's weights, NOT divided by their
+// rms; scale_sums [scale_parts][M] are partial sums of squares of the rows before the weights; every output
+// row is multiplied by rsqrt(sum / scale_dim + scale_eps) (before bias and residual).
+// emit_g (may be null): the weights [N] of the norm that follows this product; emit_xg [M, N] receives
+// out * emit_g (of out as rounded to bfloat16), emit_sums [ceil(N / 128)][M] the sums of squares of out per
+// 128 outputs; *emitted_parts says how many parts were written, 0 if this shape does not take the path
+// that can (then the caller runs the norm kernel).
+TI_API int ti_gemm_bf16_linked(void* out, const void* x, const void* w, const float* bias, const void* residual,
+                               int M, int N, int K, int gated, float* workspace, long long workspace_floats,
+                               int* counters, int num_counters, const float* scale_sums, int scale_parts,
+                               int scale_dim, float scale_eps, const float* emit_g, void* emit_xg, float* emit_sums,
+                               int* emitted_parts, int* status, cudaStream_t stream) {
+    NormLink link;
+    link.scale_sums = scale_sums; link.scale_parts = scale_parts; link.scale_dim = scale_dim; link.scale_eps = scale_eps;
+    link.emit_g = emit_g; link.emit_xg = emit_xg; link.emit_sums = emit_sums; link.emitted_parts = emitted_parts;
+    return gemm_entry(out, x, w, bias, residual, M, N, K, gated, 0, workspace, workspace_floats, counters,
+                      num_counters, link, status, stream);
+}
+
+static int gemm_entry(void* out, const void* x, const void* w, const float* bias, const void* residual,
+                      int M, int N, int K, int gated, int out_f32, float* workspace, long long workspace_floats,
+                      int* counters, int num_counters, const NormLink& link, int* status, cudaStream_t stream) {
+    if (link.emitted_parts) *link.emitted_parts = 0;
     TI_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_bf16: bad sizes M=%d N=%d K=%d", M, N, K);
+    TI_REQUIRE(link.scale_sums == nullptr || (M <= 64 && link.scale_parts > 0 && link.scale_dim > 0),
+               "gemm_bf16: rows can be scaled by their rms for at most 64 tokens");
     TI_REQUIRE(K % 8 == 0, "gemm_bf16: K=%d is not a multiple of 8 (rows must start on 16-byte boundaries)", K);
     TI_REQUIRE(!(gated && (bias || residual || out_f32)), "gemm_bf16: the gated form takes no bias, residual or float32 output");
     TI_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
@@ -688,6 +783,9 @@ TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bi
     p.out = out; p.bias = bias; p.residual = (const __nv_bfloat16*)residual;
     p.M = M; p.N = N; p.K = K; p.gated = gated; p.out_f32 = out_f32; p.status = status;
     p.splits = 1; p.partials = workspace; p.counters = counters;
+    p.scale_sums = link.scale_sums; p.scale_parts = link.scale_parts; p.scale_dim = link.scale_dim;
+    p.scale_eps = link.scale_eps;
+    p.emit_g = nullptr; p.emit_xg = nullptr; p.emit_sums = nullptr;
     const int w_rows = gated ? 2 * N : N;
     CUtensorMap rows_map, cols_map;
     // Up to 128 tokens the weights go on the 128 accumulator lanes and the tokens on the columns: with
@@ -703,6 +801,13 @@ TI_API int ti_gemm_bf16(void* out, const void* x, const void* w, const float* bi
         const int tiles = (N + (gated ? 64 : 128) - 1) / (gated ? 64 : 128);
         if (workspace && counters)
             p.splits = choose_splits(tiles, (K + BK - 1) / BK, bn, workspace_floats, num_counters);
+        // the scaled rows and the sums are written by the last unit of a cut k loop, on its 16-byte path
+        if (link.emit_g && link.emit_xg && link.emit_sums && !gated && !out_f32 && p.splits > 1 && (N & 3) == 0 &&
+            ((uintptr_t)out & 15) == 0 && ((uintptr_t)residual & 7) == 0 && ((uintptr_t)bias & 15) == 0 &&
+            ((uintptr_t)link.emit_g & 15) == 0 && ((uintptr_t)link.emit_xg & 7) == 0) {
+            p.emit_g = link.emit_g; p.emit_xg = (__nv_bfloat16*)link.emit_xg; p.emit_sums = link.emit_sums;
+            if (link.emitted_parts) *link.emitted_parts = tiles;
+        }
         if (bn == 16) return launch<16>(rows_map, cols_map, p, tiles, stream);
         if (bn == 32) return launch<32>(rows_map, cols_map, p, tiles, stream);
         if (bn == 64) return launch<64>(rows_map, cols_map, p, tiles, stream);

@@ -95,8 +95,11 @@ class DecoderModel:
         """Runs the tokens of ``step`` (a StepContext) and returns float32 logits [N, V] at
         ``step.logit_rows``."""
         x = ops.embedding(step.token_ids, self.embedding)
-        for entry in self.spec.execution:
-            x = self.blocks[entry.layer].forward(x, step, step.cache_view(entry))
+        link = None        # what a block's last product leaves for the next block's first norm (see parts.base)
+        order = self.spec.execution
+        for i, entry in enumerate(order):
+            after = self.blocks[order[i + 1].layer].mixer_norm if i + 1 < len(order) else None
+            x, link = self.blocks[entry.layer].forward_linked(x, link, after, step, step.cache_view(entry))
         if step.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.forward_rows(x, step.logit_rows)

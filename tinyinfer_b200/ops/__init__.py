@@ -11,6 +11,7 @@ norm weights, biases and logits are float32, indices are int32, and everything i
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -46,7 +47,11 @@ _SIGNATURES = {
 _SIGNATURES["sm100"] = {
     "ti_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                      c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p],
+    "ti_gemm_bf16_linked": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                            c_void_p, c_ll, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_void_p, c_void_p],
 }
+NORM_LINK_MAX_TOKENS = 64   # up to here two products can share an RMSNorm between them (see linear)
 _SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
@@ -199,10 +204,53 @@ def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------- matrix products
+class NormLink:
+    """What a product leaves for the RMSNorm behind it, when that norm is spread over the two products
+    around it: ``scaled`` = x * g in x's dtype (x: the product's output as rounded, g: the norm's weight),
+    ``sums`` float32 [parts, M]: per token, partial sums of squares of x; ``weight`` is g itself (kept to
+    tell which norm the link was made for), ``size`` the length of a row of x."""
+
+    def __init__(self, scaled, sums, parts, weight, size):
+        self.scaled, self.sums, self.parts, self.weight, self.size = scaled, sums, parts, weight, size
+
+
+def norm_link_ok(x: torch.Tensor) -> bool:
+    """True if the products around an RMSNorm of ``x`` can share it (bfloat16 on the tensor cores, at
+    most 64 rows): the norm kernel between them, a hop of a decode step, is then left out."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= NORM_LINK_MAX_TOKENS
+            and os.environ.get("TINYINFER_B200_NORM_LINK", "1") != "0")
+
+
+def _gemm_linked(out, x, w, bias, residual, m, n, k, gated, scale, emit_weight):
+    ws, counters = _gemm_scratch(x.device)
+    scaled = sums = None
+    if emit_weight is not None:
+        scaled = torch.empty((m, n), dtype=x.dtype, device=x.device)
+        sums = torch.empty(((n + 127) // 128, m), dtype=torch.float32, device=x.device)
+    written = ctypes.c_int(0)
+    _run("sm100", "ti_gemm_bf16_linked", out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual),
+         m, n, k, gated, ws.data_ptr(), ws.numel(), counters.data_ptr(), counters.numel(),
+         scale[0].sums.data_ptr() if scale else None, scale[0].parts if scale else 0,
+         scale[0].size if scale else 0, float(scale[1]) if scale else 0.0,
+         _ptr(emit_weight), _ptr(scaled), _ptr(sums), ctypes.addressof(written),
+         kernel_status(x.device).data_ptr(), _stream())
+    if emit_weight is None or written.value == 0:
+        return None
+    return NormLink(scaled, sums, written.value, emit_weight, n)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           residual: Optional[torch.Tensor] = None, out_float32: bool = False) -> torch.Tensor:
+           residual: Optional[torch.Tensor] = None, out_float32: bool = False, *,
+           link: Optional[NormLink] = None, link_eps: float = 0.0,
+           next_norm_weight: Optional[torch.Tensor] = None):
     """x [M, K] . w [N, K]^T (+ bias [N]) (+ residual [M, N]), float32 accumulation.
-    ``out_float32`` stores the accumulator unrounded (logits)."""
+    ``out_float32`` stores the accumulator unrounded (logits).
+
+    An RMSNorm between two products of at most 64 tokens can be spread over them.
+    ``next_norm_weight`` (float32 [N]): the weight of the norm that follows THIS product; the result is
+    then (out, NormLink or None): the link, if the kernel could make it, holds out * weight and the
+    sums of squares of out's rows. ``link`` (with ``link_eps``): x is ``link.scaled`` of the norm BEFORE
+    this product, and every output row is multiplied by rsqrt(mean(x_before^2) + eps) here."""
     _check(x, "x", None, 2)
     _check(w, "w", x.dtype, 2)
     m, k = x.shape
@@ -216,20 +264,31 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         if tuple(residual.shape) != (m, n):
             raise KernelError("linear: residual shape differs from the output's")
     out = torch.empty((m, n), dtype=torch.float32 if out_float32 else x.dtype, device=x.device)
+    wants_link = next_norm_weight is not None
+    if link is not None or wants_link:
+        if out_float32 or not (_tensor_core_ok(x, w) and norm_link_ok(x)):
+            if link is not None:
+                raise KernelError("linear: a norm link needs the tensor-core product of at most 64 rows")
+        else:
+            made = _gemm_linked(out, x, w, bias, residual, m, n, k, 0, (link, link_eps) if link else None,
+                                next_norm_weight)
+            return (out, made) if wants_link else out
     if _tensor_core_ok(x, w):
         ws, counters = _gemm_scratch(x.device)
         _run("sm100", "ti_gemm_bf16", out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual),
              m, n, k, 0, int(out_float32), ws.data_ptr(), ws.numel(), counters.data_ptr(), counters.numel(),
              kernel_status(x.device).data_ptr(), _stream())
-        return out
+        return (out, None) if wants_link else out
     _run("core", "ti_gemm_simt", out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual),
          m, n, k, 0, int(out_float32 and x.dtype != torch.float32), _dtype_code(x), _stream())
-    return out
+    return (out, None) if wants_link else out
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, *, link: Optional[NormLink] = None,
+                 link_eps: float = 0.0) -> torch.Tensor:
     """silu(x.Wg^T) * (x.Wu^T) with ``w_gate_up`` = [Wg; Wu] of shape [2I, K] -> [M, I]; the
-    activation and the product act on the float32 accumulators, one rounding."""
+    activation and the product act on the float32 accumulators, one rounding. ``link``: as in
+    ``linear`` (both halves are scaled before the activation)."""
     _check(x, "x", None, 2)
     _check(w_gate_up, "w_gate_up", x.dtype, 2)
     m, k = x.shape
@@ -237,6 +296,11 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         raise KernelError("gated_linear: weight must be [2I, K]")
     inter = w_gate_up.shape[0] // 2
     out = torch.empty((m, inter), dtype=x.dtype, device=x.device)
+    if link is not None:
+        if not (_tensor_core_ok(x, w_gate_up) and norm_link_ok(x)):
+            raise KernelError("gated_linear: a norm link needs the tensor-core product of at most 64 rows")
+        _gemm_linked(out, x, w_gate_up, None, None, m, inter, k, 1, (link, link_eps), None)
+        return out
     if _tensor_core_ok(x, w_gate_up):
         ws, counters = _gemm_scratch(x.device)
         _run("sm100", "ti_gemm_bf16", out.data_ptr(), x.data_ptr(), w_gate_up.data_ptr(), None, None,

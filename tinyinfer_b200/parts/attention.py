@@ -58,9 +58,10 @@ class Attention(Mixer):
                                     tensors["v_proj.bias"]]).contiguous()
             self.b_o = tensors["o_proj.bias"]
 
-    def _attend(self, x, step, cache):
+    def _attend(self, x, step, cache, link=None, link_eps=0.0):
         s = self.spec
-        qkv = ops.linear(x, self.w_qkv, bias=self.b_qkv)
+        qkv = (ops.linear(x, self.w_qkv, bias=self.b_qkv) if link is None
+               else ops.linear(x, self.w_qkv, bias=self.b_qkv, link=link, link_eps=link_eps))
         q = ops.qk_norm_rope_append(
             qkv, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
             q_norm_weight=self.q_norm, k_norm_weight=self.k_norm,
@@ -78,6 +79,21 @@ class Attention(Mixer):
 
     def forward_residual(self, x, residual, step, cache):
         return ops.linear(self._attend(x, step, cache), self.w_o, bias=self.b_o, residual=residual)
+
+    def forward_prenorm(self, x, norm, link, next_norm, step, cache):
+        rms = norm.as_rms()
+        if rms is None or not ops.norm_link_ok(x):
+            return super().forward_prenorm(x, norm, link, next_norm, step, cache)
+        # few tokens: the packed projection takes the norm's second half (if the product before left the
+        # first), and the output projection leaves the first half of the norm that follows
+        if link is not None and link.weight is rms[0]:
+            attended = self._attend(link.scaled, step, cache, link=link, link_eps=rms[1])
+        else:
+            attended = self._attend(norm.forward(x), step, cache)
+        after = next_norm.as_rms() if next_norm is not None else None
+        if after is None:
+            return ops.linear(attended, self.w_o, bias=self.b_o, residual=x), None
+        return ops.linear(attended, self.w_o, bias=self.b_o, residual=x, next_norm_weight=after[0])
 
 
 register_mixer("attention", Attention)

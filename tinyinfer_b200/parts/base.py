@@ -67,6 +67,11 @@ class Norm(Part):
         """Norm of the selected rows only. Parts without a fused kernel may gather first."""
         return self.forward(x.index_select(0, rows.long()))
 
+    def as_rms(self):
+        """(weight float32 [size], eps) if this norm is y = weight * x * rsqrt(mean(x^2) + eps), so
+        that the products around it may share it between them (``ops.linear``); None otherwise."""
+        return None
+
 
 class PositionEncoding(Part):
     """Owned by a mixer; what it offers is up to the pair (the rotary part hands out inv_freq)."""
@@ -93,6 +98,13 @@ class Mixer(Part):
         from .. import ops
         return ops.add(residual, self.forward(x, step, cache))
 
+    def forward_prenorm(self, x, norm: "Norm", link, next_norm: Optional["Norm"], step, cache):
+        """x + forward(norm(x)) for ``x`` BEFORE its norm. ``link``: None, or what the part that made x
+        left for this norm (an ``ops.NormLink``); ``next_norm``: the norm the result will pass through
+        next, if known. Returns (result, link for that next norm or None). Parts whose products can
+        share a norm between them override this; the default runs the norm on its own."""
+        return self.forward_residual(norm.forward(x), x, step, cache), None
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
@@ -101,6 +113,10 @@ class FeedForward(Part):
     def forward_residual(self, x, residual, step) -> torch.Tensor:
         from .. import ops
         return ops.add(residual, self.forward(x, step))
+
+    def forward_prenorm(self, x, norm: "Norm", link, next_norm: Optional["Norm"], step):
+        """As ``Mixer.forward_prenorm``, without a cache."""
+        return self.forward_residual(norm.forward(x), x, step), None
 
 
 class Block:
@@ -116,6 +132,11 @@ class Block:
 
     def forward(self, x, step, cache):
         raise NotImplementedError
+
+    def forward_linked(self, x, link, next_norm: Optional[Norm], step, cache):
+        """``forward`` that also takes what the block before left for this block's first norm and
+        returns what this block leaves for ``next_norm`` (the first norm behind it): (x, link)."""
+        return self.forward(x, step, cache), None
 
 
 # ------------------------------------------------------------------ registries

@@ -8,9 +8,14 @@ from .base import Block, register_block
 
 class PreNormBlock(Block):
     def forward(self, x, step, cache):
-        x = self.mixer.forward_residual(self.mixer_norm.forward(x), x, step, cache)
-        x = self.feed_forward.forward_residual(self.feed_forward_norm.forward(x), x, step)
-        return x
+        return self.forward_linked(x, None, None, step, cache)[0]
+
+    def forward_linked(self, x, link, next_norm, step, cache):
+        # each part gets its input before the norm, with the norm and with the norm that comes after it:
+        # parts whose products can share a norm between them do so (a decode step saves the norm kernels)
+        x, link = self.mixer.forward_prenorm(x, self.mixer_norm, link, self.feed_forward_norm, step, cache)
+        x, link = self.feed_forward.forward_prenorm(x, self.feed_forward_norm, link, next_norm, step)
+        return x, link
 
 
 register_block("pre_norm", PreNormBlock)

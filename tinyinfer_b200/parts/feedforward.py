@@ -36,5 +36,18 @@ class GatedMLP(FeedForward):
     def forward_residual(self, x, residual, step=None):
         return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down, residual=residual)
 
+    def forward_prenorm(self, x, norm, link, next_norm, step=None):
+        rms = norm.as_rms()
+        if rms is None or not ops.norm_link_ok(x):
+            return super().forward_prenorm(x, norm, link, next_norm, step)
+        if link is not None and link.weight is rms[0]:
+            hidden = ops.gated_linear(link.scaled, self.w_gate_up, link=link, link_eps=rms[1])
+        else:
+            hidden = ops.gated_linear(norm.forward(x), self.w_gate_up)
+        after = next_norm.as_rms() if next_norm is not None else None
+        if after is None:
+            return ops.linear(hidden, self.w_down, residual=x), None
+        return ops.linear(hidden, self.w_down, residual=x, next_norm_weight=after[0])
+
 
 register_feed_forward("gated_mlp", GatedMLP)

@@ -24,5 +24,8 @@ class RMSNorm(Norm):
     def forward_rows(self, x, rows):
         return ops.rmsnorm(x, self.weight, self.spec.eps, rows=rows)
 
+    def as_rms(self):
+        return self.weight, self.spec.eps
+
 
 register_norm("rmsnorm", RMSNorm)
