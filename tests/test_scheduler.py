@@ -196,3 +196,26 @@ def test_a_preempted_request_finds_its_own_pages_again():
     assert b.num_preemptions >= 1 and b.num_cached_tokens >= 4   # the head of its pages outlived a's growth
     assert a.num_completion_tokens == 12 and b.num_completion_tokens == 12
     assert m.groups[0].pool.num_free == 6
+
+
+def test_begun_prompts_are_finished_before_new_ones_are_begun():
+    """More waiting prompts than the pool has pages for: those that hold pages are continued first, so
+    they get to decode and to end. Taken in turn instead, every prompt would be begun, the pool would be
+    shared out among prompts none of which can go on, and preemption would move pages around for ever."""
+    s, m = make(num_pages=48, page=4, max_num_batched_tokens=16, max_num_seqs=4)
+    seqs = [seq(i, 30, max_tokens=6) for i in range(12)]
+    for q in seqs:
+        s.add(q)
+    begun = []
+    for _ in range(400):
+        if s.is_finished():
+            break
+        for item in run_step_stored(s):
+            if item[3] and item[1] == 0:
+                begun.append(item[0])
+            # a prompt is never begun while an older one that holds pages still waits for its turn
+        held_waiting = [q.seq_id for q in s.waiting if q.admitted]
+        assert len(held_waiting) <= 2, held_waiting
+    assert s.is_finished() and all(q.num_completion_tokens == 6 for q in seqs)
+    assert begun == sorted(begun) and s.num_preemptions <= 2
+    assert m.groups[0].pool.num_free == 48

@@ -4,7 +4,8 @@ a token budget, decodes round-robin, finishes and frees.
 The policy is the reference's (tinyinfer/engine/scheduler.py:63-166 schedule, :169-236
 postprocess): decode first, in round-robin order; while anything waits, decoding may take at
 most max_num_seqs - 1 requests and 80 % of the token budget (:69-70); then portions of waiting
-prompts with what is left, a prompt's pages being taken when it is admitted (:134-137). Added:
+prompts with what is left, a prompt's pages being taken when it is admitted (:134-137). Unlike the
+reference, prompts that were begun are continued, oldest first, before new ones are admitted. Added:
 a cap on one request's portion (``prefill_chunk``; the reference has a TODO there, :143), and a
 decided behaviour when pages run out, which the reference lacks (it stops with "scheduler made
 no progress", tinyinfer/engine/llm_engine.py:199-200):
@@ -90,11 +91,16 @@ class Scheduler:
             decode_token_budget -= 1
             decode_seq_budget -= 1
 
-        # phase B: portions of waiting prompts with the remaining budget
-        for _ in range(len(self.waiting)):
+        # phase B: portions of waiting prompts with the remaining budget. Prompts that already hold
+        # pages go first, in the order they arrived, then new ones are admitted: a prompt that was begun
+        # is finished before another is begun, so the pages it holds soon serve a request that decodes
+        # and ends. (Taking the waiting requests in turn, as the reference does, scheduler.py:126-164,
+        # begins every prompt before it finishes any; with more prompts than pages for them all, each
+        # holds its share of the pool, none can go on, and preemption only moves the pages around.)
+        order = [q for q in self.waiting if q.admitted] + [q for q in self.waiting if not q.admitted]
+        for seq in order:
             if token_budget <= 0 or seq_budget <= 0:
                 break
-            seq = self.waiting[0]
             if not seq.admitted:
                 if not self.manager.can_admit():
                     break
@@ -103,7 +109,6 @@ class Scheduler:
                 rc = self.manager.admit(seq.seq_id, seq.token_ids[:seq.num_prefill_tokens])
                 if not self.manager.can_extend(seq.seq_id, seq.num_prefill_tokens):
                     self.manager.release(seq.seq_id)       # its pages are not there yet: it waits
-                    self.waiting.rotate(-1)
                     continue
                 self.manager.extend(seq.seq_id, seq.num_prefill_tokens)
                 seq.admitted = True
@@ -119,7 +124,6 @@ class Scheduler:
                                        sample_after=start + chunk == seq.num_prefill_tokens))
             token_budget -= chunk
             seq_budget -= 1
-            self.waiting.rotate(-1)
         return items
 
     def _make_room(self) -> bool:
