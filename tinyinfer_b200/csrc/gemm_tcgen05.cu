@@ -6,21 +6,27 @@
 // the MMAs of tile i+1 fill the other half of tensor memory.
 //
 // Two orientations share the code. "Rows" are the 128 accumulator lanes, "cols" the BN columns:
-//   normal (many tokens):  rows = tokens of x, cols = output features of w;
-//   swapped (M <= 64):     rows = output features of w, cols = tokens of x (padded to BN), so a
-//                          decode step streams every weight once with full 128-row MMAs.
+//   tokens on the lanes (many tokens):  rows = tokens of x, cols = output features of w; tiles of
+//       128 x 256 (or 128 x 128), and of 256 x 256 for very large steps (two accumulators of one tile);
+//       with few tiles and 130 to 700 tokens the k loops are cut and the units of a tile add their
+//       partial sums up together, each its share of the columns;
+//   weights on the lanes (M <= 128, gated form M <= 64): rows = output features of w, cols = tokens of x
+//       (padded to BN), so a decode step streams every weight once with full 128-row MMAs; the k
+//       loops are cut to fill the SMs and the last unit of a tile adds the partial sums up.
 // Epilogues, all on the float32 accumulators with one rounding: + bias[n], + residual[m,n],
-// float32 output (logits), and the gated form out[m,j] = silu(x.w[j]) * (x.w[J+j]) of the
-// reference's MLP kernel (tinyinfer/csrc/mlp.cu:116-141). A row's result does not depend on
-// which other rows share its tile: every output element is one fixed-order k loop.
+// float32 output (logits), the gated form out[m,j] = silu(x.w[j]) * (x.w[J+j]) of the
+// reference's MLP kernel (tinyinfer/csrc/mlp.cu:116-141), and the two halves of an RMSNorm that is
+// spread over the products around it (see GemmParams). A row's result does not depend on
+// which other rows share its tile: every output element is one k loop in a fixed order, or a
+// fixed number of partial k loops added in a fixed order.
 //
-// Every wait on an mbarrier is bounded; a wait that runs out sets *status, raises the CTA's abort
-// flag, and all warps fall through to the common exit, where tensor memory is freed.
+// Every wait is bounded: those on mbarriers, and the one where the units of a tile wait for each other
+// on a counter in global memory (about two seconds, by the SM's clock). A wait that runs out sets
+// *status, raises the CTA's abort flag, and all warps fall through to the common exit, where tensor
+// memory is freed.
 #include "sm100_ptx.cuh"
 #include <cstdlib>
 #include <type_traits>
-#include <mutex>
-#include <unordered_map>
 
 namespace {
 
