@@ -112,7 +112,9 @@ TC_SHAPES = [(1, 4096, 4096), (8, 6144, 4096), (16, 1000, 512), (17, 520, 264), 
              (65, 256, 128), (128, 128, 64), (200, 1000, 4096), (2048, 4096, 512), (777, 1032, 1096), (3, 40, 8),
              # 65..128 tokens with the weights on the accumulator lanes and a cut k loop; 256 x 256 tiles
              # with ragged edges in every direction
-             (100, 4096, 4096), (128, 1000, 2048), (1500, 5000, 136), (3100, 2600, 72)]
+             (100, 4096, 4096), (128, 1000, 2048), (1500, 5000, 136), (3100, 2600, 72),
+             # 16 tokens and more: the units of a cut k loop add up together (9 and 12 cuts)
+             (16, 4096, 4096), (48, 2048, 12288), (64, 4096, 4096)]
 
 
 @pytest.mark.parametrize("m,n,k", TC_SHAPES)

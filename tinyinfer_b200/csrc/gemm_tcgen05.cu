@@ -44,7 +44,9 @@ struct GemmParams {
     int rows_total;         // extent of the rows operand that tiles walk over
     int cols_total;         // extent of the cols operand
     int gated, out_f32, swap;
-    int splits;             // swapped only: the k range of a tile is cut into this many work units
+    int splits;             // the k range of a tile is cut into this many work units
+    int share_sum;          // weights on the lanes, splits > 1: every unit of a tile adds up its share of the
+                            // tokens once all units have arrived (all units run at once), not the last alone
     float* partials;        // [tile][split][col][128] float32 scratch for splits > 1
     int* counters;          // [tile] arrivals; zero before the launch and again after it
     // Weights on the lanes only: an RMSNorm spread over two products. The product that makes a residual
@@ -289,14 +291,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 64) {
                     __threadfence();
-                    const int arrived = atomicAdd(p.counters + tile, 1);
-                    if (arrived == p.splits - 1) p.counters[tile] = 0;     // leave the counter ready for the next launch
+                    int arrived = atomicAdd(p.counters + tile, 1);
+                    if (p.share_sum) {
+                        // every unit of the tile takes a share of the sum: wait for the others (they all
+                        // run at once: the host launches one CTA per unit, no more than fit the SMs)
+                        arrived = p.splits - 1;
+                        const long long t_start = clock64();
+                        for (uint32_t spin = 1; *reinterpret_cast<volatile int*>(p.counters + tile) < p.splits; ++spin) {
+                            __nanosleep(64);
+                            if ((spin & 63u) == 0u && (*abort_flag || clock64() - t_start > 4000000000ll)) { arrived = -1; break; }
+                        }
+                    } else if (arrived == p.splits - 1) {
+                        p.counters[tile] = 0;     // leave the counter ready for the next launch
+                    }
                     __threadfence();
                     *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]) = arrived;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 const int arrived = *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (arrived < 0) {                                 // a unit of the tile never came: give up, loudly
+                    *abort_flag = 1;
+                    if (p.status && threadIdx.x == 64) atomicExch(p.status, 16);
+                    ok = false;
+                    break;
+                }
                 if (arrived != p.splits - 1) continue;
                 // Swapped, not gated (the products of a decode step): the four warps share the columns
                 // (tokens), a lane takes four consecutive rows (output features). So every load is 16
@@ -310,9 +329,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     if (p.bias && n_ok) b4 = *reinterpret_cast<const float4*>(p.bias + n0);
                     if (p.emit_g && n_ok) g4 = *reinterpret_cast<const float4*>(p.emit_g + n0);
                     const int cols_real = min(BN, p.M - c0);
+                    // the tokens this unit finishes: all of them, or with a shared sum those with
+                    // token mod splits == split
+                    const int col_first = p.share_sum ? split : 0, col_step = p.share_sum ? p.splits : 1;
                     auto wide = [&](auto cols_tag, auto splits_tag) {
                         constexpr int G = decltype(cols_tag)::value, SP = decltype(splits_tag)::value;
-                        for (int g0 = lane_group; g0 < cols_real; g0 += 4 * G) {
+                        for (int g0 = col_first + lane_group * col_step; g0 < cols_real; g0 += 4 * G * col_step) {
                             float4 acc[G];
                             uint2 res[G];
                             float sq[G];
@@ -322,7 +344,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                             for (int i = 0; i < G; ++i) {
                                 acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                                 res[i] = make_uint2(0u, 0u);
-                                const int col = g0 + 4 * i;
+                                const int col = g0 + 4 * i * col_step;
                                 if (p.residual && n_ok && col < cols_real)
                                     res[i] = *reinterpret_cast<const uint2*>(p.residual + (size_t)(c0 + col) * p.N + n0);
                             }
@@ -332,7 +354,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                 for (int sp = 0; sp < SP; ++sp) {
 #pragma unroll
                                     for (int i = 0; i < G; ++i) {
-                                        const int col = g0 + 4 * i;
+                                        const int col = g0 + 4 * i * col_step;
                                         const bool in = sp0 + sp < p.splits && col < cols_real;
                                         part[sp][i] = in ? __ldcg(reinterpret_cast<const float4*>(
                                                                tile_partials + ((size_t)(sp0 + sp) * BN + col) * BM + 4 * lane))
@@ -350,7 +372,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                             }
 #pragma unroll
                             for (int i = 0; i < G; ++i) {
-                                const int col = g0 + 4 * i;
+                                const int col = g0 + 4 * i * col_step;
                                 if (!n_ok || col >= cols_real) continue;
                                 const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&res[i]);
                                 const float2 ra = __bfloat1622float2(r2[0]), rb = __bfloat1622float2(r2[1]);
@@ -382,7 +404,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                 // the warp holds all 128 outputs of the tile for this token
 #pragma unroll
                                 for (int i = 0; i < G; ++i) {
-                                    const int col = g0 + 4 * i;                  // the same for the whole warp
+                                    const int col = g0 + 4 * i * col_step;                  // the same for the whole warp
                                     if (col >= cols_real) continue;
                                     float t = sq[i];
 #pragma unroll
@@ -395,6 +417,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     if (p.splits <= 4) wide(std::integral_constant<int, 4>{}, std::integral_constant<int, 4>{});
                     else if (p.splits <= 8) wide(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{});
                     else wide(std::integral_constant<int, 1>{}, std::integral_constant<int, 16>{});
+                    if (p.share_sum) {
+                        // second arrival: when every unit has read what it needs, the last one clears the counter
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (threadIdx.x == 64) {
+                            if (atomicAdd(p.counters + tile, 1) == 2 * p.splits - 1) p.counters[tile] = 0;
+                        }
+                    }
                     continue;
                 }
             }
@@ -685,7 +714,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 // How many work units to cut a tile's k range into, so that the units fill the SMs evenly:
 // a decode step is bound by how fast all SMs together can stream the weights, and 32 or 48 tiles
 // leave most of the 148 SMs idle. Needs scratch for the partial sums.
-int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int num_counters) {
+// share_sum: the units of a tile add up together (see GemmParams), so the sum costs little and as many
+// units as run side by side pay (measured at 64 tokens, 4096 x 4096: 9 cuts 12.6 us, 4 cuts 15.1 us,
+// 4 cuts added up by the last unit alone 17.9 us).
+int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int num_counters, bool share_sum) {
     if (tiles > num_counters) return 1;
     const int per_sm = bn <= 64 ? 2 : 1;                  // Cfg<BN>::CTAS_PER_SM
     if (const char* forced = getenv("TINYINFER_B200_GEMM_SPLITS")) {     // experiments only
@@ -694,6 +726,13 @@ int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int
     }
     const int sms = ti_sm_count() * per_sm;               // CTAs that run side by side
     if (tiles * 2 >= sms) return 1;                       // every SM has a tile: cutting them only adds the merge
+    if (share_sum) {
+        int s = sms / tiles;
+        s = s < 12 ? s : 12;
+        s = s < num_kb / 4 ? s : num_kb / 4;
+        while (s > 1 && (long long)tiles * s * bn * BM > workspace_floats) --s;
+        return s > 1 ? s : 1;
+    }
     int best = 1;
     double best_eff = 0.0;
     for (int s = 1; s <= 8; ++s) {
@@ -788,7 +827,7 @@ static int gemm_entry(void* out, const void* x, const void* w, const float* bias
     GemmParams p;
     p.out = out; p.bias = bias; p.residual = (const __nv_bfloat16*)residual;
     p.M = M; p.N = N; p.K = K; p.gated = gated; p.out_f32 = out_f32; p.status = status;
-    p.splits = 1; p.partials = workspace; p.counters = counters;
+    p.splits = 1; p.share_sum = 0; p.partials = workspace; p.counters = counters;
     p.scale_sums = link.scale_sums; p.scale_parts = link.scale_parts; p.scale_dim = link.scale_dim;
     p.scale_eps = link.scale_eps;
     p.emit_g = nullptr; p.emit_xg = nullptr; p.emit_sums = nullptr;
@@ -805,8 +844,17 @@ static int gemm_entry(void* out, const void* x, const void* w, const float* bias
         if (!ti_get_bf16_map(w, w_rows, K, gated ? BM / 2 : BM, &rows_map)) return -1;
         if (!ti_get_bf16_map(x, M, K, bn, &cols_map)) return -1;
         const int tiles = (N + (gated ? 64 : 128) - 1) / (gated ? 64 : 128);
+        // From 16 tokens on the sum over the cut k loops is shared out among the units of a tile (the
+        // last unit alone makes a trip to L2 per few tokens, one after the other; up to 8 tokens that is
+        // one trip and sharing only adds the wait: measured). Needs every unit running at once, and the
+        // 16-byte path of the sum.
+        static const int share_from = [] { const char* e = getenv("TINYINFER_B200_GEMM_SHARE_SUM"); return e ? atoi(e) : 16; }();
+        const bool may_share = share_from > 0 && M >= share_from && !gated && (N & 3) == 0 && ((uintptr_t)out & 15) == 0 &&
+                               ((uintptr_t)residual & 7) == 0 && ((uintptr_t)bias & 15) == 0;
         if (workspace && counters)
-            p.splits = choose_splits(tiles, (K + BK - 1) / BK, bn, workspace_floats, num_counters);
+            p.splits = choose_splits(tiles, (K + BK - 1) / BK, bn, workspace_floats, num_counters, may_share);
+        if (may_share && p.splits > 1 && (long long)tiles * p.splits <= (long long)ti_sm_count() * (bn <= 64 ? 2 : 1))
+            p.share_sum = 1;
         // the scaled rows and the sums are written by the last unit of a cut k loop, on its 16-byte path
         if (link.emit_g && link.emit_xg && link.emit_sums && !gated && !out_f32 && p.splits > 1 && (N & 3) == 0 &&
             ((uintptr_t)out & 15) == 0 && ((uintptr_t)residual & 7) == 0 && ((uintptr_t)bias & 15) == 0 &&
