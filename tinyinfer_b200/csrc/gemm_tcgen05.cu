@@ -12,7 +12,8 @@
 //       partial sums up together, each its share of the columns;
 //   weights on the lanes (M <= 128, gated form M <= 64): rows = output features of w, cols = tokens of x
 //       (padded to BN), so a decode step streams every weight once with full 128-row MMAs; the k
-//       loops are cut to fill the SMs and the last unit of a tile adds the partial sums up.
+//       loops are cut to fill the SMs; up to 15 tokens the last unit of a tile adds the partial sums
+//       up, from 16 tokens on the units of a tile do so together, each its share of the tokens.
 // Epilogues, all on the float32 accumulators with one rounding: + bias[n], + residual[m,n],
 // float32 output (logits), the gated form out[m,j] = silu(x.w[j]) * (x.w[J+j]) of the
 // reference's MLP kernel (tinyinfer/csrc/mlp.cu:116-141), and the two halves of an RMSNorm that is
