@@ -35,7 +35,7 @@ constexpr int BM = 128;          // accumulator lanes = rows of the "rows" opera
 constexpr int BK = 64;           // bf16 elements per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_BUDGET = 212 * 1024;
 
 struct GemmParams {
     void* out;
@@ -76,7 +76,7 @@ struct Cfg {
     static_assert(TM == 1 || (TM == 2 && BN == 256), "tall tiles are 256 x 256");
     static constexpr int STAGE_BYTES = (TM * BM + BN) * BK * 2;
     static constexpr int TMEM_COLS = TM == 2 ? 512 : (2 * BN < 32 ? 32 : 2 * BN);   // two accumulators; a power of two
-    static constexpr int EXCH_FLOATS = BN <= 64 ? 64 * (BN + 1) + 2 : 2;   // swapped gated epilogue (BN <= 64) + one word
+    static constexpr int EXCH_FLOATS = BN <= 64 ? 64 * 17 + 2 : 2;   // swapped gated epilogue (BN <= 64): 16 tokens at a time; + one word
     // small-batch tiles (BN <= 64) take half an SM's shared memory, so that two CTAs share an SM: one
     // streams weights while the other reduces and stores, and the next kernel's CTAs can move in early
     static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
@@ -675,7 +675,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                         for (int i = 0; i < 16; ++i) v[i] *= row_scale_sh[c + i];        // gate and up alike
                         if (is_up) {
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) exch[jj * (BN + 1) + c + i] = v[i];
+                            for (int i = 0; i < 16; ++i) exch[jj * 17 + i] = v[i];
                         }
                         asm volatile("bar.sync 1, 128;" ::: "memory");
                         if (!is_up) {
@@ -686,7 +686,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                     const int m = c0 + c + i;
                                     if (m >= p.M) break;
                                     reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + j] =
-                                        __float2bfloat16_rn(silu_mul(v[i], exch[jj * (BN + 1) + c + i]));
+                                        __float2bfloat16_rn(silu_mul(v[i], exch[jj * 17 + i]));
                                 }
                             }
                         }
