@@ -272,6 +272,34 @@ def test_paged_attention(ops, dtype, hq, hkv, d, page, window, work):
     close(out, want, dtype)
 
 
+@pytest.mark.parametrize("hq,hkv,d,page,window,lens,chunk", [
+    (32, 8, 128, 64, None, [4096, 3000, 1, 257, 513, 4000, 2048, 1025], 512),
+    (8, 8, 64, 16, None, [9000, 8193, 700, 8192], None),
+    (8, 4, 128, 128, 2500, [6000, 2501, 2500, 5121, 40, 4608, 3000, 5632, 5633, 6000, 2600, 4097, 777, 5120], -1024)])
+def test_decode_attention_with_larger_splits(ops, monkeypatch, hq, hkv, d, page, window, lens, chunk):
+    """Many long contexts are cut into splits of 512 keys and more: the same results, at the edges of the
+    larger splits too (a context that ends on one, one key past it, a window that starts inside one).
+    chunk: what the plan is expected to say; None: anything above 256; negative: forced here (a window
+    keeps the visible keys few, so the plan would not choose it)."""
+    dtype = torch.bfloat16
+    key = (len(lens), hq, hkv, d, max(lens), window or 0)
+    if chunk is not None and chunk < 0:
+        monkeypatch.setitem(ops._decode_chunks, key, -chunk)
+    planned = ops.decode_chunk(*key)
+    assert planned > 256 and planned % 256 == 0 and (chunk is None or planned == abs(chunk))
+    bt, kv = paged_setup(dtype, lens, hq, hkv, d, page, seed=5)
+    fill_cache(kv, bt, lens, hkv, d, page, dtype)
+    pos = torch.tensor([c - 1 for c in lens], dtype=torch.int32, device=dev())
+    seq = torch.arange(len(lens), dtype=torch.int32, device=dev())
+    q = rnd(len(lens), hq, d, dtype=dtype, seed=8)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    args = dict(positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5, window=window)
+    out = ops.paged_attention(q, kv, status=status, **args)
+    assert int(status.item()) == 0
+    close(out, ref.paged_attention(q, kv, **args), dtype)
+    ops.check_kernel_status()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("d,page,window,ctx,far", [(64, 16, None, 700, 3), (128, 64, None, 900, 64),
                                                    (32, 8, 100, 500, 400), (128, 64, 256, 1000, 744),

@@ -15,6 +15,7 @@
 // else is in the batch. Partial results (unnormalised output, maximum, sum per split) go to float32
 // scratch and a second kernel merges them. (Prompt portions: attention_prefill_tcgen05.cu.)
 #include "sm100_ptx.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -33,7 +34,7 @@ struct AttnParams {
     const int* positions;
     const int* token_seq;
     const int* block_table;
-    int max_blocks, hq, hkv, page_size, num_pages, window, max_splits, num_rows;
+    int max_blocks, hq, hkv, page_size, num_pages, window, max_splits, num_rows, chunk;
     float scale_log2;              // softmax scale times log2(e)
     int* status;
 };
@@ -157,8 +158,8 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
         it.row = p.rows[it.r];
         const int ctx = p.positions[it.row] + 1;
         const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
-        it.k_begin = max(it.split * CHUNK, lo);
-        it.k_end = min(ctx, (it.split + 1) * CHUNK);
+        it.k_begin = max(it.split * p.chunk, lo);
+        it.k_end = min(ctx, (it.split + 1) * p.chunk);
         return it.k_begin < it.k_end;
     };
 
@@ -331,7 +332,7 @@ __global__ void decode_merge_kernel(const AttnParams p) {
     const int row = p.rows[r];
     const int ctx = p.positions[row] + 1;
     const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
-    const int s0 = lo / CHUNK, s1 = (ctx - 1) / CHUNK;
+    const int s0 = lo / p.chunk, s1 = (ctx - 1) / p.chunk;
     const size_t base = ((size_t)r * p.hq + h) * p.max_splits;
     float m_run = -INFINITY, acc = 0.f, l_all = 0.f;
     for (int sb = s0; sb <= s1; sb += 16) {
@@ -386,16 +387,53 @@ TI_API int ti_attention_bf16_supported(int hq, int hkv, int d, int page_size) {
 }
 TI_API int ti_attention_decode_chunk() { return CHUNK; }
 
+namespace {
+// CTAs of the decode kernel that run side by side.
+int decode_slots(int d, int group) {
+    if (d == 128) return ti_sm_count() * (Smem<128>::decode_bytes(group) <= 113 * 1024 ? 2 : 1);
+    const int bytes = Smem<64>::decode_bytes(group);
+    return ti_sm_count() * (bytes <= 56 * 1024 ? 4 : (bytes <= 75 * 1024 ? 3 : 2));
+}
+}  // namespace
+
+// Keys per split for a decode step of num_rows requests whose longest context is max_context: 256, or a
+// larger power-of-two multiple of it where that is expected to be at least 5 % faster. A work item (row,
+// kv head, split) costs about 52 keys' worth of time beyond its keys, the items run in rounds over the
+// resident CTAs, and the merge makes one trip to L2 per 16 splits (measured on a B200 at 8 x 4,096 keys:
+// 32.1 us with splits of 256, 29.3 with 512; 1 x 32,768: 43.1 and 29.7 with 1,024; with fewer items than
+// CTAs the larger split loses, 1 x 4,096: 9.8 and 13.1 us). Smaller splits also even out requests of
+// different lengths, hence the margin.
+TI_API int ti_attention_decode_plan(int num_rows, int hq, int hkv, int d, int max_context, int window) {
+    if (const char* e = getenv("TINYINFER_B200_DECODE_CHUNK")) {          // experiments only
+        const int c = atoi(e);
+        if (c >= CHUNK && c % CHUNK == 0) return c;
+    }
+    if (num_rows <= 0 || hkv <= 0 || hq % hkv != 0 || (d != 64 && d != 128)) return CHUNK;
+    const int slots = decode_slots(d, hq / hkv);
+    const long long visible = window > 0 && window < max_context ? window : max_context;
+    int best = CHUNK;
+    double best_cost = 0.0;
+    for (int c = CHUNK; c <= 8 * CHUNK; c *= 2) {
+        const long long splits = (visible + c - 1) / c;
+        const long long items = (long long)num_rows * hkv * splits;
+        const double cost = (double)((items + slots - 1) / slots) * (c + 52) + (double)((splits + 15) / 16) * 60.0;
+        if (c == CHUNK || cost < 0.95 * best_cost) { best = c; best_cost = cost; }
+    }
+    return best;
+}
+
 // Decode: `rows` lists the flat rows of the step whose request brings exactly one token.
 // Scratch: part_o float32 [num_rows * hq * max_splits * d], part_ml float32 [num_rows * hq * max_splits * 2];
-// max_splits >= ceil(longest context / 256). Calls that share the scratch must not overlap.
+// chunk: keys per split, a multiple of 256 (ti_attention_decode_plan suggests one); max_splits >=
+// ceil(longest context / chunk). Calls that share the scratch must not overlap.
 TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cache, float* part_o, float* part_ml,
                                     const int* rows, int num_rows, const int* positions, const int* token_seq,
                                     const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,
-                                    int num_pages, float scale, int window, int max_splits, int* status,
+                                    int num_pages, float scale, int window, int chunk, int max_splits, int* status,
                                     cudaStream_t stream) {
     if (check_shape(hq, hkv, d, page_size, "attention_decode")) return -1;
     TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && max_splits > 0 && max_splits <= 65535, "attention_decode: bad sizes");
+    TI_REQUIRE(chunk >= CHUNK && chunk % CHUNK == 0, "attention_decode: splits of %d keys are not a multiple of %d", chunk, CHUNK);
     if (num_rows == 0) return 0;
     CUtensorMap map;
     if (!ti_get_bf16_map(kv_cache, 2ll * num_pages * hkv * page_size, d, page_size < TK ? page_size : TK, &map)) return -1;
@@ -403,6 +441,7 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
     p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q; p.part_o = part_o; p.part_ml = part_ml;
     p.rows = rows; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
     p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
+    p.chunk = chunk;
     p.window = window; p.max_splits = max_splits; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
     p.num_rows = num_rows;
     const int group = hq / hkv;
@@ -479,5 +518,5 @@ TI_API int ti_attention_decode_bf16_noalloc(void* out, const void* q, const void
     float* part_ml = part_o + (long long)num_rows * hq * max_splits * d;
     return ti_attention_decode_bf16(out, q, kv_cache, part_o, part_ml, rows, num_rows, positions, token_seq,
                                     block_table, max_blocks, hq, hkv, d, page_size, num_pages, scale, window,
-                                    max_splits, status, stream);
+                                    CHUNK, max_splits, status, stream);
 }
