@@ -145,11 +145,10 @@ def main():
         out.update(batch=len(lens), context=max(lens), us=us, gbs=byts / us / 1e3, tflops=flops / us / 1e6)
     else:
         from tinyinfer_b200 import EngineConfig
-        from tinyinfer_b200.cli import PRESETS
-        from tinyinfer_b200.config import Qwen3Config
+        from tinyinfer_b200.cli import preset_config
         from tinyinfer_b200.engine.batch import StepEntry
         from tinyinfer_b200.engine.llm import LLM
-        cfg = Qwen3Config.from_dict(dict(PRESETS["8b"], architectures=["Qwen3ForCausalLM"], num_hidden_layers=a.layers))
+        cfg = preset_config("8b", num_hidden_layers=a.layers)
         eng = EngineConfig(max_num_batched_tokens=max(2048, a.tokens), max_num_seqs=a.batch, max_model_len=a.context,
                            kvcache_block_size=a.page_size, dtype="bfloat16", cuda_graphs=not a.no_graph,
                            num_kvcache_blocks=(a.context // a.page_size) * a.batch + 8 + a.tokens // a.page_size)

@@ -168,8 +168,12 @@ def collect(session, steps) -> Dict[str, Dict[int, np.ndarray]]:
     return got
 
 
-def plain_logits(folder, requests) -> Dict[str, np.ndarray]:
+def plain_logits(folder, requests, matrices_as=None) -> Dict[str, np.ndarray]:
+    """``matrices_as=torch.bfloat16``: the matrices of the folder (every tensor of two dimensions)
+    are rounded to that type first, as an engine does that loads a 32-bit folder to run in bfloat16."""
     cfg, w = plain.read_model_folder(folder, torch.float64)
+    if matrices_as is not None:
+        w = {n: t.to(matrices_as).to(torch.float64) if t.dim() == 2 else t for n, t in w.items()}
     return {rid: plain.forward(cfg, w, toks).numpy() for rid, toks in requests.items()}
 
 

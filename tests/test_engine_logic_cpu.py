@@ -51,3 +51,56 @@ def test_every_cut_matches_plain_on_cpu(tmp_path, cpu_ops, name, page):
         if tag == "mixed":
             stats = session.runner.manager.stats()["groups"]
             assert all(g["pages_taken"] > g["pages"] for g in stats), "pages were not used again"
+
+
+def test_a_step_takes_pages_for_all_its_entries_or_for_none(tmp_path, cpu_ops):
+    """A step whose second entry cannot get its pages leaves the cache as it was: the first entry's
+    pages are not kept, and a request that the step itself would have admitted is not live."""
+    from tinyinfer_b200.cache import CacheExhausted
+    from tinyinfer_b200.engine.batch import StepEntry
+    cfg = helpers.TINY_A
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=3)
+    session = session_for(folder, max_tokens=64, page_size=4)          # 16 pages
+    runner = session.runner
+    runner.step([StepEntry("old", list(range(20)), [19])])             # 5 pages held
+    before = runner.manager.stats()
+    with pytest.raises(CacheExhausted):
+        # 'old' could grow by 12 tokens (3 pages) alone, and 'new' could get 36 tokens (9 pages) alone: not both
+        runner.step([StepEntry("old", list(range(12)), [11]), StepEntry("new", list(range(36)), [35])])
+    assert runner.manager.stats() == before
+    assert "new" not in runner.manager and runner.manager.get("old").length == 20
+    runner.manager.check_consistency()
+    with pytest.raises(ValueError):                                    # a bad token is seen before anybody is admitted
+        runner.step([StepEntry("late", [1, 2, cfg["vocab_size"]], [2])])
+    assert "late" not in runner.manager and runner.manager.stats() == before
+    logits = runner.step([StepEntry("old", list(range(12)), [11])])    # the step that fits still runs
+    assert logits.shape == (1, cfg["vocab_size"])
+
+
+def test_patching_the_last_decode_step_needs_the_same_admissions():
+    """The staged arrays of a decode step are patched for the next one only if the requests are the
+    same admissions: an id that ended and came back holds other pages and another state slot."""
+    from tinyinfer_b200.engine.batch import BatchBuffers, StepEntry
+    buffers = BatchBuffers("cpu", max_tokens=8, max_seqs=4, max_blocks=4, num_groups=1)
+    entries = [StepEntry("a", [5], [0]), StepEntry("b", [6], [0])]
+    ctx = buffers.build(entries, [3, 9], [0, 1], [[[7], [2, 4, 8]]], fixed_layout=True, admissions=[1, 2])
+    assert ctx.block_tables[0].tolist() == [[7, -1, -1, -1], [2, 4, 8, -1]]
+    same = buffers.advance_decode([1, 2], 0, [11, 12], [4, 10], [[[7, 3], [2, 4, 8]]])
+    assert same is ctx and ctx.block_tables[0].tolist() == [[7, 3, -1, -1], [2, 4, 8, -1]]
+    assert ctx.positions.tolist() == [4, 10] and ctx.token_ids.tolist() == [11, 12]
+    # 'a' ended and a new 'a' (admission 3) brings one token: tables of equal length, other pages
+    assert buffers.advance_decode([3, 2], 0, [1, 13], [0, 11], [[[5], [2, 4, 8]]]) is None
+    # without admission numbers nothing is remembered to patch
+    buffers.build(entries, [3, 9], [0, 1], [[[7], [2, 4, 8]]], fixed_layout=True)
+    assert buffers.advance_decode([1, 2], 0, [11, 12], [4, 10], [[[7, 3], [2, 4, 8]]]) is None
+
+
+def test_an_id_that_comes_back_is_another_admission(tmp_path, cpu_ops):
+    from tinyinfer_b200.engine.batch import StepEntry
+    folder = helpers.make_model_folder(tmp_path / "m", helpers.TINY_A, seed=3)
+    runner = session_for(folder, max_tokens=64, page_size=4).runner
+    runner.step([StepEntry("a", [1, 2, 3], [])])
+    first = runner.manager.get("a").serial
+    runner.release("a")
+    runner.step([StepEntry("a", [4], [])])
+    assert runner.manager.get("a").serial != first

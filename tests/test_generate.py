@@ -227,3 +227,25 @@ def test_prefix_cache_is_off_where_a_window_gives_pages_back(tmp_path):
     assert LLM(folder, **kw).config.enable_prefix_caching is False
     with pytest.raises(ValueError, match="enable_prefix_caching"):
         LLM(folder, enable_prefix_caching=True, **kw)
+
+
+def test_a_kernel_status_that_is_set_stops_generation(tmp_path, monkeypatch):
+    """The kernels' status words come home with the sampled tokens; a step during which one was set
+    (here by hand: nothing on a CPU sets it) raises instead of handing its tokens on."""
+    from tinyinfer_b200 import ops
+    import tinyinfer_b200.engine.llm as llm_mod
+    for name in torch_ops.ALL:
+        monkeypatch.setattr(ops, name, getattr(torch_ops, name))
+    monkeypatch.setattr(llm_mod, "require_cuda", lambda d: torch.device("cpu"))
+    folder = helpers.make_model_folder(tmp_path / "m", helpers.TINY_A, seed=3)
+    llm = llm_mod.LLM(folder, dtype="float32", device="cpu", max_num_batched_tokens=24, max_num_seqs=3,
+                      kvcache_block_size=4, num_kvcache_blocks=30, max_model_len=128)
+    llm.add_request([5, 6, 7], SamplingParams(greedy=True, max_tokens=4))
+    llm.step()
+    words = ops.status_words(torch.device("cpu"))
+    for word, code, text in ((0, 15, "gave up waiting"), (1, 1, "without a page")):
+        words[word] = code
+        with pytest.raises(ops.KernelError, match=text):
+            llm.step()
+        assert words.tolist() == [0, 0]                      # reported once, then cleared
+    words.zero_()

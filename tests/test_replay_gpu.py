@@ -106,29 +106,92 @@ def test_graph_replay_equals_eager_steps(tmp_path):
     assert helpers.first_bad(out[True], want, TOL["bfloat16"]) is None
 
 
+def test_an_id_that_comes_back_gets_its_own_pages(tmp_path):
+    """With CUDA graphs on, a decode step for the same requests as the step before patches the staged
+    arrays instead of rebuilding them. A request that ends after such a step and whose id comes back
+    in the next one, with one token, is another request: other pages, another state slot. Both live
+    requests are compared with the plain implementation while the pool hands the ended request's page
+    out again."""
+    from tinyinfer_b200.engine.replay import TraceSession
+    cfg = helpers.TINY["C"]
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=7, dtype="bfloat16")
+    rng = np.random.default_rng(4)
+    first = [int(t) for t in rng.integers(0, cfg["vocab_size"], 12)]       # one page of 16
+    again = [int(t) for t in rng.integers(0, cfg["vocab_size"], 76)]
+    other = [int(t) for t in rng.integers(0, cfg["vocab_size"], 40 + 4 + 76)]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": first[:8], "want": [7]},
+                                     {"id": "b", "tokens": other[:40], "want": [39]}], "end": []}]
+    for i in range(4):                                                     # decode-only steps of "a" and "b"
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [first[8 + i]], "want": [0]},
+                                                      {"id": "b", "tokens": [other[40 + i]], "want": [0]}],
+                      "end": ["a"] if i == 3 else []})
+    for i in range(76):                                                    # the id "a" is back, one token a step
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [again[i]], "want": [0]},
+                                                      {"id": "b", "tokens": [other[44 + i]], "want": [0]}], "end": []})
+    session = TraceSession(folder, "bfloat16", 192, page_size=16, poison_cache=True, cuda_graphs=True)
+    got, upto, names = {}, {}, {}
+    for st in steps:
+        out = session.run_step(st)
+        for row, e in enumerate(st["entries"]):
+            name = names.setdefault(e["id"], e["id"])
+            s0 = upto.get(name, 0)
+            got.setdefault(name, {})[s0 + e["want"][0]] = out[row]
+            upto[name] = s0 + len(e["tokens"])
+        for rid in st["end"]:
+            names[rid] = rid + "2"                                         # what comes under this id now is another request
+        session.runner.manager.check_consistency()
+    assert session.runner.graph_replays > 60
+    assert session.runner.manager.stats()["groups"][0]["pages_taken"] > 12, "the ended request's page was not used again"
+    want = helpers.plain_logits(folder, {"a": first, "a2": again, "b": other})
+    bad = helpers.first_bad(got, want, TOL["bfloat16"])
+    assert bad is None, bad
+
+
 BIG = dict(
-    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=4099, hidden_size=4096,
-    num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096,
+    num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
     intermediate_size=12288, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_bias=False,
     tie_word_embeddings=False, max_position_embeddings=4096)
 
 
+@pytest.fixture(scope="module")
+def benchmark_sized_model(tmp_path_factory):
+    """Two layers with every width of the benchmark model (hidden 4096, 32/8 heads of 128, feed-forward
+    12288, vocabulary 151,936, untied head), written once in 32-bit, with the plain implementation's
+    logits for four short requests: from the weights as written, and from the matrices rounded to
+    bfloat16, which is what an engine run in bfloat16 holds after loading this folder."""
+    folder = helpers.make_model_folder(tmp_path_factory.mktemp("big") / "m", BIG, seed=6, dtype="float32", std=0.02)
+    requests = helpers.random_requests(BIG, [150, 70, 33, 190], seed=2)
+    want = {"float32": helpers.plain_logits(folder, requests),
+            "bfloat16": helpers.plain_logits(folder, requests, matrices_as=torch.bfloat16)}
+    return folder, requests, want
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_layer_sizes_of_the_benchmark_model(tmp_path, dtype):
-    """One layer with the sizes of the benchmark model (hidden 4096, 32/8 heads of 128, feed-forward
-    12288; a small odd vocabulary): the shapes the tensor-core kernels are tuned for, checked through
-    the engine in every kind of step, in both dtypes."""
+def test_widths_of_the_benchmark_model_in_every_cut(benchmark_sized_model, dtype):
+    """The shapes the tensor-core kernels are tuned for (and the 32-bit kernels at the same widths),
+    through the engine in all four ways of cutting the work, with pages of 64 that are used again."""
     from tinyinfer_b200.engine.replay import TraceSession
-    folder = helpers.make_model_folder(tmp_path / "m", BIG, seed=6, dtype=dtype, std=0.02)
-    requests = helpers.random_requests(BIG, [130, 70, 33, 200], seed=2)
-    want = helpers.plain_logits(folder, requests)
-    for tag, steps in (("tail", helpers.trace_decode_tail(requests, tail=20)),
-                       ("mixed", helpers.trace_mixed(requests, seed=4, max_live=3))):
-        session = TraceSession(folder, dtype, helpers.peak_tokens(steps), page_size=64, poison_cache=True)
+    folder, requests, want = benchmark_sized_model
+    cuts = {"whole": helpers.trace_whole(requests),
+            "tail": helpers.trace_decode_tail(requests, tail=32),
+            "chunked": helpers.trace_chunked(requests, seed=3),
+            "mixed": helpers.trace_mixed(requests, seed=4, max_live=3)}
+    model = None
+    for tag, steps in cuts.items():
+        session = TraceSession(folder, dtype, helpers.peak_tokens(steps), page_size=64, poison_cache=True,
+                               model=model)
+        model = session.model                      # six gigabytes of weights are loaded once for the four cuts
         got = helpers.collect(session, steps)
         session.runner.check_status()
-        bad = helpers.first_bad(got, want, TOL[dtype])
+        assert {r: len(v) for r, v in got.items()} == {r: len(t) for r, t in requests.items()}, tag
+        bad = helpers.first_bad(got, want[dtype], TOL[dtype])
         assert bad is None, (tag, bad)
+        session.runner.manager.check_consistency()
+        if tag == "mixed":
+            stats = session.runner.manager.stats()["groups"]
+            assert all(g["pages_taken"] > g["pages"] for g in stats), "pages were not used again"
+        del got, session
 
 
 def run_trace_program(folder, dtype, out, steps, max_tokens, page_size=16):

@@ -55,7 +55,14 @@ def gated_linear(x, w_gate_up):
 
 
 def qk_norm_rope_append(qkv, *, num_heads, num_kv_heads, head_dim, q_norm_weight, k_norm_weight, eps,
-                        inv_freq, rotary_dim, positions, token_seq, kv_cache, block_table, status=None):
+                        positions, token_seq, kv_cache, block_table, rotation=None, inv_freq=None, rotary_dim=0,
+                        status=None):
+    """``rotation``: an object with rotary_dim, inv_freq or cos_sin, interleaved (ops.Rotation);
+    ``inv_freq`` + ``rotary_dim`` alone mean the half-split rotation by position * inv_freq."""
+    interleaved, cos_sin = False, None
+    if rotation is not None:
+        inv_freq, rotary_dim = rotation.inv_freq, rotation.rotary_dim
+        interleaved, cos_sin = rotation.interleaved, rotation.cos_sin
     t = qkv.shape[0]
     x = _acc(qkv).view(t, num_heads + 2 * num_kv_heads, head_dim)
     q, k, v = x[:, :num_heads], x[:, num_heads:num_heads + num_kv_heads], x[:, num_heads + num_kv_heads:]
@@ -66,11 +73,19 @@ def qk_norm_rope_append(qkv, *, num_heads, num_kv_heads, head_dim, q_norm_weight
         return w.to(a.dtype) * a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + eps)
 
     def rot(a):
-        if inv_freq is None:
+        if inv_freq is None and cos_sin is None:
             return a
         half = rotary_dim // 2
-        ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
-        cos, sin = ang.cos().to(a.dtype)[:, None, :], ang.sin().to(a.dtype)[:, None, :]
+        if cos_sin is not None:
+            rows = cos_sin[positions.long()]
+            cos, sin = rows[:, None, :half].to(a.dtype), rows[:, None, half:].to(a.dtype)
+        else:
+            ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
+            cos, sin = ang.cos().to(a.dtype)[:, None, :], ang.sin().to(a.dtype)[:, None, :]
+        if interleaved:
+            a1, a2 = a[..., 0:rotary_dim:2], a[..., 1:rotary_dim:2]
+            turned = torch.stack((a1 * cos - a2 * sin, a2 * cos + a1 * sin), dim=-1).flatten(-2)
+            return torch.cat((turned, a[..., rotary_dim:]), dim=-1)
         a1, a2 = a[..., :half], a[..., half:rotary_dim]
         return torch.cat((a1 * cos - a2 * sin, a2 * cos + a1 * sin, a[..., rotary_dim:]), dim=-1)
 
@@ -107,17 +122,22 @@ def paged_attention(q, kv_cache, *, positions, token_seq, block_table, scale, wi
     return out.view(t, hq * d)
 
 
-def argmax(logits):
-    return torch.argmax(logits, dim=-1).to(torch.int32)
+def _with_extra(tokens, extra):
+    """``extra``: words that ride behind the tokens (the kernels' status words)."""
+    return tokens if extra is None else torch.cat((tokens, extra.to(tokens.device, torch.int32)))
 
 
-def sample(logits, temperature, topk, greedy, seed, stream_id, step):
+def argmax(logits, extra=None):
+    return _with_extra(torch.argmax(logits, dim=-1).to(torch.int32), extra)
+
+
+def sample(logits, temperature, topk, greedy, seed, stream_id, step, extra=None):
     out = []
     for r in range(logits.shape[0]):
         out.append(plain.sample(logits[r].detach().cpu().numpy(), greedy=bool(greedy[r]),
                                 temperature=float(temperature[r]), topk=int(topk[r]),
                                 seed=int(seed[r]), stream=int(stream_id[r]), step=int(step[r])))
-    return torch.tensor(out, dtype=torch.int32, device=logits.device)
+    return _with_extra(torch.tensor(out, dtype=torch.int32, device=logits.device), extra)
 
 
 def token_nll(logits, tokens):

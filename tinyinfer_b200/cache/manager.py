@@ -121,6 +121,7 @@ class RequestCache:
     length: int = 0                                          # tokens whose keys are stored
     tables: List[List[int]] = field(default_factory=list)    # per group: logical page -> id or -1
     page_hashes: List[int] = field(default_factory=list)     # prefix cache: chain over its full pages
+    serial: int = 0                                          # which admission this is: ids may come back, serials never do
 
 
 def group_cache_needs(needs: Sequence[Tuple[Optional[CacheNeed], Optional[StateNeed]]]):
@@ -178,6 +179,7 @@ class CacheManager:
         self._free_slots = deque(range(max_requests))
         self._fresh_slots: List[int] = []
         self._requests: Dict[Hashable, RequestCache] = {}
+        self._admissions = 0
         self.prefix_caching = prefix_caching
         # prefix cache: page -> (hash, hash of the pages before, its tokens) and hash -> page
         self._page_key: Dict[int, Tuple[int, int, Tuple[int, ...]]] = {}
@@ -210,8 +212,9 @@ class CacheManager:
             raise RuntimeError(f"request {request_id!r} is already live")
         if not self._free_slots:
             raise CacheExhausted("no free state slot: too many live requests")
+        self._admissions += 1
         rc = RequestCache(request_id, self._free_slots.popleft(),
-                          tables=[[] for _ in self.groups])
+                          tables=[[] for _ in self.groups], serial=self._admissions)
         self._fresh_slots.append(rc.state_slot)
         self._requests[request_id] = rc
         if self.prefix_caching and token_ids is not None:
@@ -294,6 +297,23 @@ class CacheManager:
         for m, g, table in zip(missing, self.groups, rc.tables):
             for _ in range(m):
                 table.append(g.pool.take(request_id))
+
+    def extend_many(self, wanted: Sequence[Tuple[Hashable, int]]) -> None:
+        """``extend`` for several requests at once, all or none: the pages that all of them lack
+        are counted against the free ones first, and CacheExhausted leaves every table as it was."""
+        lacking = [0] * len(self.groups)
+        for request_id, new_length in wanted:
+            rc = self._requests[request_id]
+            if new_length < rc.length:
+                raise ValueError("a request's cache cannot shrink")
+            for gi, m in enumerate(self._missing(rc, new_length)):
+                lacking[gi] += m
+        for gi, (m, g) in enumerate(zip(lacking, self.groups)):
+            if m > g.pool.num_free:
+                raise CacheExhausted(f"KV cache exhausted: the step needs {m} more pages in group {gi}, "
+                                     f"{g.pool.num_free} are free")
+        for request_id, new_length in wanted:
+            self.extend(request_id, new_length)
 
     def commit(self, request_id, new_length: int) -> None:
         """Records that keys of positions < new_length are stored, and gives back every page a

@@ -14,33 +14,14 @@ import random
 import sys
 from typing import List, Optional
 
-from .config import EngineConfig, Qwen3Config, parse_dtype
-
-PRESETS = {
-    # sizes of the benchmark configurations; weights are random
-    "tiny": dict(vocab_size=256, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
-                 num_key_value_heads=2, head_dim=16, intermediate_size=128, rms_norm_eps=1e-6,
-                 rope_theta=10000.0, tie_word_embeddings=True, max_position_embeddings=512),
-    "1.7b": dict(vocab_size=151936, hidden_size=2048, num_hidden_layers=28, num_attention_heads=16,
-                 num_key_value_heads=8, head_dim=128, intermediate_size=6144, rms_norm_eps=1e-6,
-                 rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=40960),
-    "8b": dict(vocab_size=151936, hidden_size=4096, num_hidden_layers=36, num_attention_heads=32,
-               num_key_value_heads=8, head_dim=128, intermediate_size=12288, rms_norm_eps=1e-6,
-               rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=40960),
-    "32b": dict(vocab_size=151936, hidden_size=5120, num_hidden_layers=64, num_attention_heads=64,
-                num_key_value_heads=8, head_dim=128, intermediate_size=25600, rms_norm_eps=1e-6,
-                rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=40960),
-}
-
-
-def preset_config(name: str) -> Qwen3Config:
-    return Qwen3Config.from_dict(dict(PRESETS[name], architectures=["Qwen3ForCausalLM"]))
+from . import models  # noqa: F401  (registers the built-in architecture and its presets)
+from .config import EngineConfig, known_presets, parse_dtype, preset_config  # noqa: F401
 
 
 def add_engine_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--model", help="folder with config.json and *.safetensors")
-    ap.add_argument("--random-config", choices=sorted(PRESETS),
-                    help="instead of --model: a Qwen3 shape with random weights")
+    ap.add_argument("--random-config", choices=sorted(known_presets()),
+                    help="instead of --model: a size that a registered architecture offers, with random weights")
     ap.add_argument("--seed", type=int, default=0, help="seed of the random weights")
     ap.add_argument("--dtype", default="bfloat16", help="bfloat16 (bf16) or float32 (fp32)")
     ap.add_argument("--max-num-batched-tokens", type=int, default=4096)
@@ -84,7 +65,7 @@ def build_llm(args):
 
 
 def main(argv: Optional[List[str]] = None) -> int:
-    ap = argparse.ArgumentParser(prog="tinyinfer_b200", description="Generate with a Qwen3 dense model on one B200.")
+    ap = argparse.ArgumentParser(prog="tinyinfer_b200", description="Generate with a model of a registered architecture on one B200.")
     add_engine_options(ap)
     ap.add_argument("--prompt", action="append", default=[], help="text prompt (needs a tokenizer in --model)")
     ap.add_argument("--prompt-ids", action="append", default=[], help="prompt as comma-separated token ids")

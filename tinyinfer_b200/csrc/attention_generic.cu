@@ -38,7 +38,8 @@ __global__ void __launch_bounds__(AG_THREADS) attention_generic_kernel(
         float s = -INFINITY;
         long long off = -1;
         if (j <= pos) {
-            const int page = table[j / page_size];
+            const int logical = j / page_size;
+            const int page = logical < max_blocks ? table[logical] : -1;
             if (page >= 0 && page < num_pages) {
                 off = (((long long)page * hkv + kvh) * page_size + j % page_size) * d;
                 const T* krow = k_cache + off;

@@ -332,7 +332,12 @@ __global__ void decode_merge_kernel(const AttnParams p) {
     const int row = p.rows[r];
     const int ctx = p.positions[row] + 1;
     const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
-    const int s0 = lo / p.chunk, s1 = (ctx - 1) / p.chunk;
+    const int s0 = lo / p.chunk;
+    int s1 = (ctx - 1) / p.chunk;
+    if (s1 >= p.max_splits) {                              // the caller gave fewer splits than the context needs:
+        if (d == 0 && p.status) atomicExch(p.status, 23);  // say so, and read nothing that is not this row's
+        s1 = p.max_splits - 1;
+    }
     const size_t base = ((size_t)r * p.hq + h) * p.max_splits;
     float m_run = -INFINITY, acc = 0.f, l_all = 0.f;
     for (int sb = s0; sb <= s1; sb += 16) {
@@ -388,6 +393,16 @@ TI_API int ti_attention_bf16_supported(int hq, int hkv, int d, int page_size) {
 TI_API int ti_attention_decode_chunk() { return CHUNK; }
 
 namespace {
+// Shared memory that decode_attention_kernel<128> (which 0) or <64> (which 1) was last allowed on the
+// current device: the attribute is kept per device, so the record is too. nullptr: no current device.
+int* configured_bytes(int which) {
+    constexpr int MAX_DEVICES = 64;
+    static int bytes[2][MAX_DEVICES] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+    return &bytes[which][dev];
+}
+
 // CTAs of the decode kernel that run side by side.
 int decode_slots(int d, int group) {
     if (d == 128) return ti_sm_count() * (Smem<128>::decode_bytes(group) <= 113 * 1024 ? 2 : 1);
@@ -425,7 +440,9 @@ TI_API int ti_attention_decode_plan(int num_rows, int hq, int hkv, int d, int ma
 // Decode: `rows` lists the flat rows of the step whose request brings exactly one token.
 // Scratch: part_o float32 [num_rows * hq * max_splits * d], part_ml float32 [num_rows * hq * max_splits * 2];
 // chunk: keys per split, a multiple of 256 (ti_attention_decode_plan suggests one); max_splits >=
-// ceil(longest context / chunk). Calls that share the scratch must not overlap.
+// ceil(longest context / chunk): a row whose context needs more sets *status to 23 and is computed from
+// the keys the splits cover, reading nothing outside its own partials. Calls that share the scratch must
+// not overlap.
 TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cache, float* part_o, float* part_ml,
                                     const int* rows, int num_rows, const int* positions, const int* token_seq,
                                     const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,
@@ -449,16 +466,18 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
     TI_REQUIRE(items < (1ll << 31), "attention_decode: too many work items");
     if (d == 128) {
         const int bytes = Smem<128>::decode_bytes(group);
-        static int configured = 0;
-        if (configured < bytes) { if (set_smem(decode_attention_kernel<128>, bytes, "attention_decode")) return -1; configured = bytes; }
+        int* configured = configured_bytes(0);
+        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
+        if (*configured < bytes) { if (set_smem(decode_attention_kernel<128>, bytes, "attention_decode")) return -1; *configured = bytes; }
         const int slots = ti_sm_count() * (bytes <= 113 * 1024 ? 2 : 1);
         ti_launch(decode_attention_kernel<128>, (int)(items < slots ? items : slots), THREADS, bytes, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
         ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
     } else {
         const int bytes = Smem<64>::decode_bytes(group);
-        static int configured = 0;
-        if (configured < bytes) { if (set_smem(decode_attention_kernel<64>, bytes, "attention_decode")) return -1; configured = bytes; }
+        int* configured = configured_bytes(1);
+        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
+        if (*configured < bytes) { if (set_smem(decode_attention_kernel<64>, bytes, "attention_decode")) return -1; *configured = bytes; }
         const int slots = ti_sm_count() * (bytes <= 56 * 1024 ? 4 : (bytes <= 75 * 1024 ? 3 : 2));
         ti_launch(decode_attention_kernel<64>, (int)(items < slots ? items : slots), THREADS, bytes, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");

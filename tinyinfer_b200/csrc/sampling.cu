@@ -106,13 +106,15 @@ __device__ __forceinline__ void for_each_logit(const float* x, int vocab, F f) {
 __global__ void __launch_bounds__(SK_THREADS) sample_kernel(
     int* __restrict__ out, const float* __restrict__ logits, int vocab,
     const float* __restrict__ temperature, const int* __restrict__ topk, const int* __restrict__ greedy,
-    const long long* __restrict__ seed, const int* __restrict__ stream_id, const int* __restrict__ step) {
+    const long long* __restrict__ seed, const int* __restrict__ stream_id, const int* __restrict__ step,
+    const int* __restrict__ extra, int num_extra) {
     __shared__ Best sh_best[SK_THREADS / 32];
     __shared__ unsigned hist[256];
     __shared__ unsigned sel_prefix, sel_remaining;
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
+    if (row == 0 && tid < num_extra) out[gridDim.x + tid] = extra[tid];   // words that ride home with the tokens
     const float* x = logits + (size_t)row * vocab;
 
     if (greedy == nullptr || greedy[row]) {
@@ -195,12 +197,16 @@ __global__ void __launch_bounds__(SK_THREADS) sample_kernel(
 }
 
 // greedy == nullptr: every row is an argmax and the other per-row arrays are not read.
+// extra / num_extra: device words (the kernels' status words, say) copied to out[num_rows ...] so that
+// one device-to-host copy brings them home with the tokens; out then has num_rows + num_extra entries.
 TI_API int ti_sample(int* out, const float* logits, int num_rows, int vocab, const float* temperature,
                      const int* topk, const int* greedy, const long long* seed, const int* stream_id,
-                     const int* step, cudaStream_t stream) {
+                     const int* step, const int* extra, int num_extra, cudaStream_t stream) {
     TI_REQUIRE(num_rows >= 0 && vocab > 0, "sample: bad sizes");
+    TI_REQUIRE(num_extra >= 0 && num_extra <= 32 && (num_extra == 0 || extra != nullptr), "sample: bad extra words");
     if (num_rows == 0) return 0;
-    ti_launch(sample_kernel, num_rows, SK_THREADS, 0, stream, out, logits, vocab, temperature, topk, greedy, seed, stream_id, step);
+    ti_launch(sample_kernel, num_rows, SK_THREADS, 0, stream, out, logits, vocab, temperature, topk, greedy, seed, stream_id, step,
+              extra, num_extra);
     TI_CHECK_LAUNCH("sample");
     return 0;
 }
@@ -213,12 +219,13 @@ constexpr int AM_PARTS = 32;
 
 __global__ void __launch_bounds__(SP_THREADS) argmax_parts_kernel(
     int* __restrict__ out, const float* __restrict__ logits, int vocab, float* __restrict__ part_val,
-    int* __restrict__ part_idx, int* __restrict__ counters) {
+    int* __restrict__ part_idx, int* __restrict__ counters, const int* __restrict__ extra, int num_extra) {
     __shared__ Best sh_best[SP_THREADS / 32];
     __shared__ int last_sh;
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int part = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+    if (part == 0 && row == 0 && tid < num_extra) out[gridDim.y + tid] = extra[tid];
     const float* x = logits + (size_t)row * vocab;
     const int chunk = ((vocab + AM_PARTS - 1) / AM_PARTS + 3) & ~3;
     const int begin = part * chunk, end = min(vocab, begin + chunk);
@@ -258,13 +265,14 @@ __global__ void __launch_bounds__(SP_THREADS) argmax_parts_kernel(
 TI_API int ti_argmax_parts() { return AM_PARTS; }
 
 // part_val / part_idx: scratch of num_rows * ti_argmax_parts() entries; counters: num_rows zeroed ints
-// (left zeroed). Calls that share them must be ordered on one stream.
+// (left zeroed). Calls that share them must be ordered on one stream. extra / num_extra: as in ti_sample.
 TI_API int ti_argmax(int* out, const float* logits, int num_rows, int vocab, float* part_val, int* part_idx,
-                     int* counters, cudaStream_t stream) {
+                     int* counters, const int* extra, int num_extra, cudaStream_t stream) {
     TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && vocab > 0, "argmax: bad sizes");
+    TI_REQUIRE(num_extra >= 0 && num_extra <= 32 && (num_extra == 0 || extra != nullptr), "argmax: bad extra words");
     if (num_rows == 0) return 0;
     ti_launch(argmax_parts_kernel, dim3(AM_PARTS, num_rows), SP_THREADS, 0, stream, out, logits, vocab, part_val,
-              part_idx, counters);
+              part_idx, counters, extra, num_extra);
     TI_CHECK_LAUNCH("argmax");
     return 0;
 }

@@ -81,7 +81,11 @@ class BatchBuffers:
                  + max_seqs + 4 * (max_tokens // 64 + max_seqs) + 128)   # tiles: at most one per 64 tokens plus one per request
         self.host = torch.empty(words, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self.dev = torch.empty(words, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if self.device.type == "cuda":
+            from ..ops import page_status
+            self.status = page_status(self.device)      # read by whoever reads the device's status words
+        else:
+            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
         self._copy_pending = False
         self.bytes_copied = 0              # host-to-device bytes of all steps so far
@@ -90,14 +94,18 @@ class BatchBuffers:
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
               tables: Sequence[Sequence[Sequence[int]]], fixed_layout: bool = False,
-              pad_to: int = 0, pad_pages: Sequence[int] = ()) -> StepContext:
+              pad_to: int = 0, pad_pages: Sequence[int] = (),
+              admissions: Optional[Sequence[int]] = None) -> StepContext:
         """``starts[i]``: tokens entry i's request already holds; ``slots[i]``: its state slot;
         ``tables[g][i]``: its block table in cache group g. ``fixed_layout`` pads every block
         table to the widest possible, so that two steps with the same numbers of tokens and
         requests put every array at the same address (what a captured CUDA graph needs).
         ``pad_to`` fills the step up to that many requests with padding rows (token 0 at position 0
         of a request whose only page is ``pad_pages[g]``, a page no real request holds), so that one
-        captured graph serves a range of batch sizes; their logits come last and are dropped."""
+        captured graph serves a range of batch sizes; their logits come last and are dropped.
+        ``admissions[i]``: a number that tells entry i's request from every other request there ever
+        was (the cache manager's admission serial); with it a step of single decoded tokens can be
+        followed by ``advance_decode``."""
         num_real = len(entries)
         if pad_to > num_real:
             extra = pad_to - num_real
@@ -175,20 +183,21 @@ class BatchBuffers:
             max_context=max(ctx_lens, default=0), decode_rows=view("dec"), num_decode=len(decode_rows),
             prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4, num_real_seqs=num_real)
         self._last = None
-        if fixed_layout and all(n == 1 for n in q_lens):
-            self._last = dict(key=(tuple(e.request_id for e in entries[:num_real]), s), ctx=ctx, words=n,
+        if fixed_layout and admissions is not None and all(n == 1 for n in q_lens):
+            self._last = dict(key=(tuple(admissions), s), ctx=ctx, words=n,
                               offsets=offsets, widths=widths, num_real=num_real,
                               table_lens=[[len(tb) for tb in tables[g][:num_real]] for g in range(self.num_groups)])
         return ctx
 
-    def advance_decode(self, request_ids: Sequence, pad_to: int, tokens: Sequence[int], starts: Sequence[int],
+    def advance_decode(self, admissions: Sequence[int], pad_to: int, tokens: Sequence[int], starts: Sequence[int],
                        tables: Sequence[Sequence[Sequence[int]]]) -> Optional[StepContext]:
-        """The step after a step of single decoded tokens, for the same requests in the same order,
-        each with its next token: only the token ids, the positions and the pages that were added
+        """The step after a step of single decoded tokens, for the same requests (the same admissions,
+        not merely the same ids: a request that ended and whose id came back holds other pages and
+        another state slot) in the same order, each with its next token: only the token ids, the positions and the pages that were added
         change, so the staging buffer is patched instead of rebuilt. Block tables must only have
         grown (no window gave pages back). Returns None if the last step was not such a step."""
         last = self._last
-        if last is None or last["key"] != (tuple(request_ids), max(pad_to, len(request_ids))):
+        if last is None or last["key"] != (tuple(admissions), max(pad_to, len(admissions))):
             return None
         n_real, off, host = last["num_real"], last["offsets"], self._host_np
         if self._copy_pending:
@@ -210,8 +219,9 @@ class BatchBuffers:
         n = last["words"]
         self.dev[:n].copy_(self.host[:n], non_blocking=True)
         self.bytes_copied += 4 * n
-        self._copied.record()
-        self._copy_pending = True
+        if self._copied is not None:
+            self._copied.record()
+            self._copy_pending = True
         ctx = last["ctx"]
         ctx.starts = list(starts)
         ctx.max_context = max(ctx_lens)          # padding rows have context 1

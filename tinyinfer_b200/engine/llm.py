@@ -47,6 +47,7 @@ class LLM:
         page = self.config.kvcache_block_size
         num_pages = self.config.num_kvcache_blocks
         if num_pages == 0:
+            torch.cuda.empty_cache()        # what loading held for a moment counts as free again
             free, _total = torch.cuda.mem_get_info(device)
             num_pages = pages_that_fit(self.model, page, free, self.config.gpu_memory_utilization,
                                        self.config.max_num_batched_tokens, self.config.max_num_seqs)
@@ -81,6 +82,10 @@ class LLM:
         self._ids = count()
         self.sequences: Dict[int, Sequence] = {}
 
+    def close(self) -> None:
+        """Gives the device memory back (weights, cache, graphs); the engine cannot be used afterwards."""
+        self.runner.close()
+
     # ------------------------------------------------------------------ requests
     def add_request(self, token_ids: Seq[int], params: Optional[SamplingParams] = None) -> int:
         vocab = self.model.spec.vocab_size
@@ -93,7 +98,9 @@ class LLM:
         return seq.seq_id
 
     def step(self) -> List[ScheduledItem]:
-        """schedule -> run -> sample -> postprocess; returns what was scheduled."""
+        """schedule -> run -> sample -> postprocess; returns what was scheduled. The kernels' status
+        words come home with the sampled tokens: a step whose kernels gave up on a wait or met a token
+        without a page raises KernelError instead of handing on tokens drawn from its logits."""
         items = self.scheduler.schedule()
         if not items:
             return items
@@ -106,7 +113,7 @@ class LLM:
         tokens = self.sampler.sample(
             logits, [it.seq.sampling_params for it in sampling],
             [it.seq.seq_id for it in sampling], [it.seq.num_completion_tokens for it in sampling],
-            with_nll=self.config.track_nll)
+            with_nll=self.config.track_nll, status=self.runner.status_words())
         if self.config.track_nll:
             tokens, nlls = tokens
             for it, nll in zip(sampling, nlls):

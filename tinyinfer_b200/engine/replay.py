@@ -48,6 +48,7 @@ class TraceSession:
         entries = [StepEntry(e["id"], list(e["tokens"]), list(e.get("want", ())))
                    for e in step.get("entries", [])]
         logits = self.runner.step(entries)
+        self.runner.check_status()              # a step whose kernels gave up must not hand out logits
         for rid in step.get("end", []):
             if rid in self.runner.manager:
                 self.runner.release(rid)

@@ -61,22 +61,17 @@ class ModelRunner:
         """Runs the entries' tokens and returns float32 logits [N, V] on the device, N being the
         number of wanted places, in the order of the entries and of each ``want``.
         A request id not seen before is admitted. Raises CacheExhausted before anything runs
-        if the pages do not suffice."""
+        if the pages do not suffice for ALL entries; the cache is then as it was before the call."""
         entries = [e for e in entries if len(e.tokens) > 0]
         ids = [e.request_id for e in entries]
         if len(set(ids)) != len(ids):
             raise ValueError("a request may appear once in a step")
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
-        for rid in ids:
-            if rid not in self.manager:
-                self.admit(rid)
-        for slot in self.manager.take_fresh_slots():      # whoever admitted them: their state starts clean
-            self.storage.reset_state_slot(slot)
         vocab = self.model.spec.vocab_size
         starts: List[int] = []
         for e in entries:
-            start = self.manager.get(e.request_id).length
+            start = self.manager.get(e.request_id).length if e.request_id in self.manager else 0
             if start + len(e.tokens) > self.max_model_len:
                 raise ValueError(f"request {e.request_id!r} would reach {start + len(e.tokens)} tokens, "
                                  f"the limit is {self.max_model_len}")
@@ -84,11 +79,24 @@ class ModelRunner:
                 if not 0 <= int(tok) < vocab:
                     raise ValueError(f"token id {tok} is outside the vocabulary of {vocab}")
             starts.append(start)
-        for e, start in zip(entries, starts):
-            self.manager.extend(e.request_id, start + len(e.tokens))
+        admitted_here = [rid for rid in ids if rid not in self.manager]
+        try:
+            for rid in admitted_here:
+                self.admit(rid)
+            self.manager.extend_many([(e.request_id, start + len(e.tokens)) for e, start in zip(entries, starts)])
+        except Exception:
+            for rid in admitted_here:          # a step that cannot run leaves the cache as it found it
+                if rid in self.manager:
+                    self.manager.release(rid)
+            raise
+        for slot in self.manager.take_fresh_slots():      # whoever admitted them: their state starts clean
+            self.storage.reset_state_slot(slot)
         caches = [self.manager.get(rid) for rid in ids]
         num_groups = len(self.manager.groups)
         tables = [[rc.tables[g] for rc in caches] for g in range(num_groups)] or [[[] for _ in caches]]
+        # a request is told from its namesakes of earlier by the serial of its admission: an id may
+        # come back after its request has ended, with other pages and another state slot
+        serials = [rc.serial for rc in caches]
         decode_only = self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         pad_to = 0
         if decode_only:
@@ -96,10 +104,10 @@ class ModelRunner:
         ctx = None
         if decode_only and self._tables_only_grow:
             # the same requests as in the step before, one more token each: patch the staged arrays
-            ctx = self.buffers.advance_decode(ids, pad_to, [int(e.tokens[0]) for e in entries], starts, tables)
+            ctx = self.buffers.advance_decode(serials, pad_to, [int(e.tokens[0]) for e in entries], starts, tables)
         if ctx is None:
             ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables,
-                                     fixed_layout=decode_only, pad_to=pad_to,
+                                     fixed_layout=decode_only, pad_to=pad_to, admissions=serials,
                                      pad_pages=[CacheStorage.dump_page(self.manager, g) for g in range(num_groups)])
             self._bind_views(ctx)
         logits = self._graph_forward(ctx) if decode_only else self.model.forward(ctx)
@@ -150,14 +158,37 @@ class ModelRunner:
                 block_table=ctx.block_tables[g] if g is not None else None,
                 page_size=self.manager.page_size, writes=True, state=self.storage.state[entry])
 
+    def close(self) -> None:
+        """Lets go of the device memory this runner holds (cache pages, captured graphs and their pool,
+        the model's tensors), so that another engine can be built in the same process."""
+        from .. import ops
+        self._graphs.clear()
+        self._graph_pool = None
+        self.buffers._last = None
+        self.storage.kv.clear()
+        self.storage.state.clear()
+        for block in self.model.blocks:
+            for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
+                for name, value in list(vars(part).items()):
+                    if isinstance(value, torch.Tensor):
+                        setattr(part, name, None)
+        self.model.embedding = self.model.head = None
+        ops.release_scratch(self.device)
+        if self.device.type == "cuda":
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+
+    def status_words(self) -> torch.Tensor:
+        """The device's two status words (``ops.status_words``): kernels of a step set them when a
+        bounded wait ran out or a token or key had no page. A sampler can take them home with the tokens."""
+        from .. import ops
+        return ops.status_words(self.device)
+
     def check_status(self) -> None:
-        """Reads the word kernels set when they met an index without a page (synchronises)."""
+        """Reads the status words and raises if a kernel of an earlier step set one (synchronises)."""
         from .. import ops
         ops.check_kernel_status()
-        code = int(self.buffers.status.item())
-        if code:
-            self.buffers.status.zero_()
-            raise RuntimeError(f"a kernel met a token or key without a page (status {code})")
 
 
 _GRAPH_BATCH_SIZES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024)

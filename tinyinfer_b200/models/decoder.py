@@ -59,8 +59,12 @@ class DecoderModel:
         tinyinfer/utils/loader.py:103-105 of the reference)."""
         return [self.spec.names.head] if self.spec.tie_embeddings else []
 
-    def load_tensors(self, tensors: Dict[str, torch.Tensor]) -> None:
-        """``tensors``: every name of ``expected_tensors()``, on the device, role applied."""
+    def load_tensors(self, tensors) -> None:
+        """``tensors[name]``: the tensor of that name of ``expected_tensors()``, on the device, role
+        applied. Every name is asked for once, in the order of ``expected_tensors()``, and a part's
+        tensors are let go of as soon as the part has packed them: a mapping that makes each tensor
+        when it is asked for (a reader of a file, a random draw) never has more than one part's
+        tensors alive beside the model, which is what lets a model of 65 GB load into 180 GB."""
         spec = self.spec
         self.embedding = tensors[spec.names.embedding].contiguous()
         for i in range(len(self.blocks)):

@@ -31,7 +31,7 @@ _SIGNATURES = {
         "ti_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
         "ti_add": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p],
         "ti_qk_norm_rope_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
-                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
         "ti_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
@@ -39,8 +39,8 @@ _SIGNATURES = {
         "ti_gemm_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                          c_int, c_int, c_int, c_void_p],
         "ti_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                      c_void_p, c_void_p, c_void_p],
-        "ti_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                      c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+        "ti_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "ti_token_nll": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
 }
@@ -65,22 +65,50 @@ _bound = {}
 _status = {}
 
 
-def kernel_status(device) -> torch.Tensor:
-    """The int32 device word that kernels with bounded waits set when a wait runs out."""
+def status_words(device) -> torch.Tensor:
+    """The two int32 device words through which kernels report what they could not do:
+    [0] a bounded wait that ran out (the number of the wait), [1] a token or key whose request holds no
+    page for it, or a context longer than the splits it was given. Zero means all is well."""
     key = torch.device(device)
     t = _status.get(key)
     if t is None:
-        t = _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
+        t = _status[key] = torch.zeros(2, dtype=torch.int32, device=key)
     return t
 
 
+def kernel_status(device) -> torch.Tensor:
+    """The word that kernels with bounded waits set when a wait runs out."""
+    return status_words(device)[0:1]
+
+
+def page_status(device) -> torch.Tensor:
+    """The word that kernels set when they meet a token or a key without a page."""
+    return status_words(device)[1:2]
+
+
+def status_message(wait_code: int, page_code: int) -> Optional[str]:
+    """What two status words say, or None if both are zero."""
+    said = []
+    if wait_code:
+        said.append(f"a kernel gave up waiting on a barrier (status {wait_code}); the step's results are not to be used")
+    if page_code:
+        said.append(f"a kernel met a token or key without a page (status {page_code})")
+    return "; ".join(said) or None
+
+
+def raise_on_status(device, wait_code: int, page_code: int) -> None:
+    """Raises KernelError (and clears the words) if either code, read from ``device``, is set."""
+    msg = status_message(wait_code, page_code)
+    if msg is not None:
+        status_words(device).zero_()
+        raise KernelError(msg)
+
+
 def check_kernel_status() -> None:
-    """Raises if any kernel reported a wait that ran out (synchronises)."""
-    for t in _status.values():
-        code = int(t.item())
-        if code:
-            t.zero_()
-            raise KernelError(f"a kernel gave up waiting on a barrier (status {code})")
+    """Raises if any kernel reported a wait that ran out or a missing page (synchronises)."""
+    for device, t in list(_status.items()):
+        wait_code, page_code = t.tolist()
+        raise_on_status(device, wait_code, page_code)
 
 
 _WORKSPACE_FLOATS = 12 * 1024 * 1024     # 48 MB of float32 partial tiles for the stream-k cuts of matrix products
@@ -314,15 +342,40 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, *, link: Optional[Nor
 
 
 # ---------------------------------------------------------------------- attention
+class Rotation:
+    """How a position turns the features of a head: what a position-encoding part hands to a mixer, which
+    passes it on to ``qk_norm_rope_append`` unread. The first ``rotary_dim`` features of every head are
+    rotated in pairs, (j, j + rotary_dim / 2) or, ``interleaved``, (2j, 2j + 1), pair j of position p by
+    the angle p * inv_freq[j] (``inv_freq`` float32 [rotary_dim / 2]) or by the angle whose cosine and
+    sine stand in ``cos_sin`` (float32 [positions, rotary_dim]: a row holds the rotary_dim / 2 cosines,
+    then the sines; any encoding whose angles depend on the position alone). Exactly one of the two."""
+
+    def __init__(self, rotary_dim: int, inv_freq: Optional[torch.Tensor] = None,
+                 cos_sin: Optional[torch.Tensor] = None, interleaved: bool = False):
+        if (inv_freq is None) == (cos_sin is None):
+            raise KernelError("a rotation needs inverse frequencies or a table of cosines and sines, one of them")
+        if rotary_dim <= 0 or rotary_dim % 2:
+            raise KernelError(f"rotary_dim must be positive and even, got {rotary_dim}")
+        if inv_freq is not None:
+            if inv_freq.dtype != torch.float32 or tuple(inv_freq.shape) != (rotary_dim // 2,):
+                raise KernelError("inv_freq must be float32 with rotary_dim / 2 entries")
+        elif cos_sin.dtype != torch.float32 or cos_sin.dim() != 2 or cos_sin.shape[1] != rotary_dim:
+            raise KernelError("cos_sin must be float32 [positions, rotary_dim]")
+        self.rotary_dim, self.inv_freq, self.cos_sin, self.interleaved = rotary_dim, inv_freq, cos_sin, bool(interleaved)
+
+
 def qk_norm_rope_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
                         q_norm_weight: Optional[torch.Tensor], k_norm_weight: Optional[torch.Tensor],
-                        eps: float, inv_freq: Optional[torch.Tensor], rotary_dim: int,
-                        positions: torch.Tensor, token_seq: torch.Tensor,
+                        eps: float, positions: torch.Tensor, token_seq: torch.Tensor,
                         kv_cache: Optional[torch.Tensor], block_table: torch.Tensor,
+                        rotation: Optional[Rotation] = None,
+                        inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0,
                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Splits ``qkv`` [T, (Hq + 2 Hkv) D] by heads; norms q and k per head, rotates them by
     their positions, returns q [T, Hq, D] and writes k and v into the pages of
-    ``kv_cache`` [2, pages, Hkv, page, D] (None: the entry only reads the cache)."""
+    ``kv_cache`` [2, pages, Hkv, page, D] (None: the entry only reads the cache).
+    ``rotation``: a ``Rotation`` or None (positions are not used); ``inv_freq`` with ``rotary_dim``
+    is short for the half-split rotation by position * inv_freq."""
     _check(qkv, "qkv", None, 2)
     t = qkv.shape[0]
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
@@ -335,10 +388,12 @@ def qk_norm_rope_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int,
             _check(w, name, torch.float32, 1)
             if w.shape[0] != head_dim:
                 raise KernelError(f"{name} must have head_dim entries")
-    if inv_freq is not None:
-        _check(inv_freq, "inv_freq", torch.float32, 1)
-        if inv_freq.shape[0] * 2 != rotary_dim:
-            raise KernelError("inv_freq must have rotary_dim / 2 entries")
+    if rotation is None and inv_freq is not None:
+        rotation = Rotation(rotary_dim, inv_freq=inv_freq)
+    if rotation is not None:
+        if rotation.rotary_dim > head_dim:
+            raise KernelError(f"rotary_dim {rotation.rotary_dim} exceeds head_dim {head_dim}")
+        _check(rotation.inv_freq if rotation.inv_freq is not None else rotation.cos_sin, "the rotation's tensor")
     page_size = num_pages = 1
     if kv_cache is not None:
         _check(kv_cache, "kv_cache", qkv.dtype, 5)
@@ -346,9 +401,12 @@ def qk_norm_rope_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int,
             raise KernelError(f"kv_cache shape {tuple(kv_cache.shape)} is not [2, pages, Hkv, page, D]")
         num_pages, page_size = kv_cache.shape[1], kv_cache.shape[3]
     q = torch.empty((t, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    rot = rotation
     _run("core", "ti_qk_norm_rope_append", q.data_ptr(), qkv.data_ptr(), _ptr(kv_cache),
-         _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), _ptr(inv_freq),
-         rotary_dim if inv_freq is not None else 0, positions.data_ptr(), token_seq.data_ptr(),
+         _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps),
+         _ptr(rot.inv_freq) if rot else None, _ptr(rot.cos_sin) if rot else None,
+         rot.cos_sin.shape[0] if rot and rot.cos_sin is not None else 0, int(rot.interleaved) if rot else 0,
+         rot.rotary_dim if rot else 0, positions.data_ptr(), token_seq.data_ptr(),
          block_table.data_ptr(), block_table.shape[1], t, num_heads, num_kv_heads, head_dim,
          page_size, num_pages, _ptr(status), _dtype_code(qkv), _stream())
     return q
@@ -381,6 +439,23 @@ def attention_tensor_cores_ok(q: torch.Tensor, kv_cache: torch.Tensor) -> bool:
             and (page in (16, 32) or page % 64 == 0))
 
 
+_generic_warned = set()
+
+
+def _warn_generic_attention(hq: int, hkv: int, d: int, page_size: int) -> None:
+    """Says once per shape that a bfloat16 model runs its attention on the generic float32-arithmetic
+    kernel: right, but many times slower than the tensor-core kernels."""
+    key = (hq, hkv, d, page_size)
+    if key in _generic_warned:
+        return
+    _generic_warned.add(key)
+    import warnings
+    warnings.warn(f"tinyinfer_b200: attention with {hq} query heads over {hkv} kv heads, head_dim {d}, pages of "
+                  f"{page_size} runs on the generic kernel (the tensor-core kernels take head_dim 64 or 128, at most "
+                  f"16 query heads per kv head, pages of 16, 32 or a multiple of 64): correct, but far slower",
+                  RuntimeWarning, stacklevel=3)
+
+
 _attn_scratch = {}
 _attn_scratch_outgrown = []     # kept alive: captured graphs may still write their partials there
 
@@ -407,6 +482,16 @@ def decode_chunk(num_rows: int, hq: int, hkv: int, head_dim: int, max_context: i
     if c is None:
         c = _decode_chunks[key] = int(_fn("sm100", "ti_attention_decode_plan")(*key))
     return c
+
+
+def release_scratch(device) -> None:
+    """Drops the scratch buffers kept for ``device`` (they are made again when next needed). Only when no
+    captured graph that uses them will be replayed again."""
+    key = torch.device(device)
+    _attn_scratch.pop(key, None)
+    _attn_scratch_outgrown.clear()
+    _workspace.pop(key, None)
+    _argmax_scratch.pop(key, None)
 
 
 def reserve_decode_scratch(device, num_rows: int, num_heads: int, head_dim: int, max_context: int) -> None:
@@ -436,6 +521,8 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
     if t == 0:
         return out
     if not attention_tensor_cores_ok(q, kv_cache):
+        if q.dtype == torch.bfloat16:
+            _warn_generic_attention(hq, hkv, d, page_size)
         _run("core", "ti_attention_generic", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              t, hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), _ptr(status),
@@ -486,11 +573,14 @@ _ARGMAX_PARTS = 32
 _argmax_scratch = {}
 
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
-    """Index of the largest logit of every row (first index on ties), int32 [N]."""
+def argmax(logits: torch.Tensor, extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Index of the largest logit of every row (first index on ties), int32 [N]. ``extra``: int32 device
+    words (at most 32) that the kernel copies behind the tokens, so that one copy to the host brings both;
+    the result then has N + len(extra) entries."""
     _check(logits, "logits", torch.float32, 2)
     n = logits.shape[0]
-    out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    num_extra = _check_extra(extra)
+    out = torch.empty((n + num_extra,), dtype=torch.int32, device=logits.device)
     key = torch.device(logits.device)
     scratch = _argmax_scratch.get(key)
     if scratch is None or scratch[2].numel() < n:
@@ -500,15 +590,25 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
             torch.empty(rows * _ARGMAX_PARTS, dtype=torch.int32, device=key),
             torch.zeros(rows, dtype=torch.int32, device=key))
     _run("core", "ti_argmax", out.data_ptr(), logits.data_ptr(), n, logits.shape[1], scratch[0].data_ptr(),
-         scratch[1].data_ptr(), scratch[2].data_ptr(), _stream())
+         scratch[1].data_ptr(), scratch[2].data_ptr(), _ptr(extra), num_extra, _stream())
     return out
 
 
+def _check_extra(extra: Optional[torch.Tensor]) -> int:
+    if extra is None:
+        return 0
+    _check(extra, "extra", torch.int32, 1)
+    if extra.shape[0] > 32:
+        raise KernelError("at most 32 extra words travel with the tokens")
+    return extra.shape[0]
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, topk: torch.Tensor, greedy: torch.Tensor,
-           seed: torch.Tensor, stream_id: torch.Tensor, step: torch.Tensor) -> torch.Tensor:
+           seed: torch.Tensor, stream_id: torch.Tensor, step: torch.Tensor,
+           extra: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of float32 logits [N, V]. Per row: ``greedy`` (int32 0/1),
     ``temperature`` (float32 > 0), ``topk`` (int32, 0 = off), and the random stream
-    (``seed`` int64, ``stream_id`` int32, ``step`` int32)."""
+    (``seed`` int64, ``stream_id`` int32, ``step`` int32). ``extra``: as in ``argmax``."""
     _check(logits, "logits", torch.float32, 2)
     n = logits.shape[0]
     for name, t, dt in (("temperature", temperature, torch.float32), ("topk", topk, torch.int32),
@@ -517,10 +617,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, topk: torch.Tensor, 
         _check(t, name, dt, 1)
         if t.shape[0] != n:
             raise KernelError(f"{name} must have one entry per row")
-    out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    num_extra = _check_extra(extra)
+    out = torch.empty((n + num_extra,), dtype=torch.int32, device=logits.device)
     _run("core", "ti_sample", out.data_ptr(), logits.data_ptr(), n, logits.shape[1],
          temperature.data_ptr(), topk.data_ptr(), greedy.data_ptr(), seed.data_ptr(),
-         stream_id.data_ptr(), step.data_ptr(), _stream())
+         stream_id.data_ptr(), step.data_ptr(), _ptr(extra), num_extra, _stream())
     return out
 
 

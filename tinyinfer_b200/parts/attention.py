@@ -21,6 +21,7 @@ class Attention(Mixer):
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.position = build_position(spec.position, dtype, device)
+        self._rotation = self.position.rotation()      # opaque here: the kernel reads it
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
         self.q_norm = self.k_norm = None
 
@@ -66,8 +67,7 @@ class Attention(Mixer):
             qkv, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
             q_norm_weight=self.q_norm, k_norm_weight=self.k_norm,
             eps=s.qk_norm.eps if s.qk_norm is not None else 0.0,
-            inv_freq=self.position.inv_freq, rotary_dim=self.position.rotary_dim,
-            positions=step.positions, token_seq=step.token_seq,
+            rotation=self._rotation, positions=step.positions, token_seq=step.token_seq,
             kv_cache=cache.kv if cache.writes else None, block_table=cache.block_table,
             status=step.status)
         return ops.paged_attention(q, cache.kv, positions=step.positions, token_seq=step.token_seq,

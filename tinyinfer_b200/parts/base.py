@@ -74,7 +74,19 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """Owned by a mixer; what it offers is up to the pair (the rotary part hands out inv_freq)."""
+    """Owned by a mixer, to which it hands ``rotation()``: an ``ops.Rotation`` (which features are paired,
+    and each pair's angle at every position, as inverse frequencies or as a table of cosines and sines)
+    or None if positions are not used. The mixer passes it to the fused norm + rotation + append kernel
+    without looking inside. A part that sets ``inv_freq`` (float32 [rotary_dim / 2]) and ``rotary_dim``
+    gets the half-split rotation by position * inv_freq from the default below."""
+    inv_freq = None
+    rotary_dim = 0
+
+    def rotation(self):
+        if self.inv_freq is None:
+            return None
+        from .. import ops
+        return ops.Rotation(self.rotary_dim, inv_freq=self.inv_freq)
 
 
 class Mixer(Part):

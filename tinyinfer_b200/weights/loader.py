@@ -87,16 +87,34 @@ def load_weights(model, folder) -> LoadReport:
         raise WeightError(missing, unexpected, wrong, where=str(folder))
 
     report = LoadReport(skipped_tied=sorted(n for n in index if n in ignored))
-    by_file: Dict[Path, List[str]] = {}
-    for name in expected:
-        by_file.setdefault(index[name][0], []).append(name)
-    tensors: Dict[str, torch.Tensor] = {}
-    for file, names in by_file.items():
-        with safe_open(str(file), framework="pt", device="cpu") as f:
-            for name in names:
-                t = apply_role(f.get_tensor(name), expected[name].role, model.dtype)
-                tensors[name] = t.to(model.device)
-                report.loaded.append(name)
-                report.bytes_on_device += t.numel() * t.element_size()
-    model.load_tensors(tensors)
+    reader = _TensorReader(index, expected, model.dtype, model.device, report)
+    try:
+        model.load_tensors(reader)
+    finally:
+        reader.close()
     return report
+
+
+class _TensorReader:
+    """``reader[name]``: the checkpoint's tensor of that name, role applied, on the device. Read when
+    asked for and not kept, so that a model that packs tensors as it loads them never has the packed
+    and the unpacked copy of more than one part on the device."""
+
+    def __init__(self, index, expected, dtype, device, report: LoadReport):
+        self.index, self.expected, self.dtype, self.device, self.report = index, expected, dtype, device, report
+        self._open = {}
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        file = self.index[name][0]
+        handle = self._open.get(file)
+        if handle is None:
+            handle = self._open[file] = safe_open(str(file), framework="pt", device="cpu").__enter__()
+        t = apply_role(handle.get_tensor(name), self.expected[name].role, self.dtype).to(self.device)
+        self.report.loaded.append(name)
+        self.report.bytes_on_device += t.numel() * t.element_size()
+        return t
+
+    def close(self) -> None:
+        for handle in self._open.values():
+            handle.__exit__(None, None, None)
+        self._open.clear()
