@@ -353,6 +353,11 @@ def reference_arm(args) -> int:
     def unavailable(why):
         print(json.dumps({"impl": "reference", "unavailable": " ".join(str(why).split())[:400]}))
         return 0
+    import faulthandler
+    faulthandler.enable()                       # a crash inside the reference's extension names the Python line
+
+    def say(what):
+        print(f"[reference arm] {what}", file=sys.stderr, flush=True)
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "tinyinfer").is_dir():
         return unavailable("baseline/_ref holds no install of the reference")
@@ -396,13 +401,21 @@ def reference_arm(args) -> int:
         tok.save(str(folder / "tokenizer.json"))
         (folder / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "PreTrainedTokenizerFast"}))
         write_s = time.perf_counter() - t0
+        say(f"model folder written in {write_s:.1f} s")
+        # The reference's feed-forward binding warns when a step has more than 32 tokens, and on this image
+        # that warning crashes the process (SIGSEGV inside mlp_forward at 33 tokens, none at 32): its
+        # token budget is therefore 32, prompts go through in portions of 32, and batches above 32 are left out.
+        if batch > args.ref_step_tokens:
+            return unavailable(f"a decode step of {batch} tokens is beyond the {args.ref_step_tokens} tokens a step that "
+                               "the reference's feed-forward binding survives on this image")
         batches = [batch] if args.skip_points else sorted({1, batch, 64})
         t0 = time.perf_counter()
         engine = tinyinfer.LLM(RefConfig(
-            model=str(folder), max_num_batched_tokens=2048, max_num_seqs=max(batches), max_model_len=ctx_len,
+            model=str(folder), max_num_batched_tokens=args.ref_step_tokens, max_num_seqs=max(batches), max_model_len=ctx_len,
             kvcache_block_size=args.ref_block_size, gpu_memory_utilization=0.90, attention_backend="flash"))
         torch.cuda.synchronize()
         build_s = time.perf_counter() - t0
+        say(f"engine built in {build_s:.1f} s, {engine.config.num_kvcache_blocks} cache blocks")
 
         greedy_one = tinyinfer.SamplingParams(greedy=True, max_tokens=1, ignore_eos=True)
         engine.generate_token_ids([[rng.randrange(vocab) for _ in range(64)]], greedy_one)       # first launches
@@ -414,6 +427,7 @@ def reference_arm(args) -> int:
             torch.cuda.synchronize()
             pf.append((time.perf_counter() - t0) * 1e3)
         prefill_ms = min(pf)
+        say(f"prefill of 2,048 tokens: {prefill_ms:.0f} ms")
         pf_flops = prefill_flops(cfg, layers, 2048, 1)
         prefill = {"value": 2048 / (prefill_ms / 1e3), "tokens": 2048, "ms": prefill_ms,
                    "frac": pf_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12),
@@ -429,6 +443,7 @@ def reference_arm(args) -> int:
                 engine.add_request([rng.randrange(vocab) for _ in range(prompt_len)], params)
             while engine.scheduler.waiting:                 # prompts, in portions, until all decode
                 engine.step()
+            say(f"batch {b}: prompts of {prompt_len} tokens are in the cache")
             if sampler is not None:
                 sampler.start()
             for _ in range(warmup - 1):
@@ -450,6 +465,10 @@ def reference_arm(args) -> int:
             if b == batch:
                 continue
             prefill_s = b * ctx_len / prefill["value"]
+            if b > args.ref_step_tokens:
+                skipped[f"decode_b{b}"] = (f"more than {args.ref_step_tokens} tokens in a step crash the reference's "
+                                           "feed-forward binding on this image (SIGSEGV on its warning path)")
+                continue
             if prefill_s > args.ref_point_limit:
                 skipped[f"decode_b{b}"] = f"its prompts alone would take about {prefill_s:.0f} s to prefill"
                 continue
@@ -468,6 +487,7 @@ def reference_arm(args) -> int:
                    "head_dim": cfg.resolved_head_dim, "intermediate": cfg.intermediate_size, "vocab": vocab,
                    "global_batch": batch, "seq_len": ctx_len, "prefill_tokens": 2048,
                    "page_size": args.ref_block_size, "parallelism": "single-gpu", "attention_backend": "flash",
+                   "max_num_batched_tokens": args.ref_step_tokens,
                    "l2": f"inputs>L2 (weights {numbers['weight_bytes'] / 1e9:.1f} GB read per step)",
                    "cache_fill": "real prefill through the reference's scheduler",
                    "timing": "larger of CUDA events and wall clock around K calls of LLM.step()"},
@@ -501,6 +521,8 @@ def main() -> int:
     ap.add_argument("--skip-extras", action="store_true", help="leave out the 'configs' of the line")
     ap.add_argument("--extras", default="32b,mix,cpu", help="which of the other configurations to run")
     ap.add_argument("--ref-block-size", type=int, default=256, help="reference arm: its kvcache_block_size (its default)")
+    ap.add_argument("--ref-step-tokens", type=int, default=32,
+                    help="reference arm: its max_num_batched_tokens (more than 32 tokens in a step crash its binding here)")
     ap.add_argument("--ref-point-limit", type=float, default=240.0,
                     help="reference arm: skip a batch size whose prompts would take longer than this many seconds")
     args = ap.parse_args()

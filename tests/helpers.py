@@ -12,14 +12,20 @@ import torch
 
 import plain_qwen3 as plain
 
-# Two tiny configurations that differ in every size and option, plus two whose head sizes reach
-# the tensor-core kernels.
+# Two tiny configurations that differ in every size and option (A and B: the two the benchmark's
+# correctness workloads name, B with a head size that is not hidden / heads and three kv heads), the
+# same B with a sliding-window layer (Bw), and two whose head sizes reach the tensor-core kernels.
 TINY_A = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=256, hidden_size=64,
     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
     intermediate_size=128, rms_norm_eps=1e-6, rope_theta=10000.0, attention_bias=False,
     tie_word_embeddings=True, max_position_embeddings=512)
 TINY_B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=384, hidden_size=96,
+    num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=3, head_dim=32,
+    intermediate_size=160, rms_norm_eps=1e-5, rope_theta=1000000.0, attention_bias=False,
+    tie_word_embeddings=False, max_position_embeddings=1024)
+TINY_BW = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=389, hidden_size=96,
     num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=2, head_dim=32,
     intermediate_size=176, rms_norm_eps=1e-5, rope_theta=1000000.0, attention_bias=False,
@@ -36,7 +42,7 @@ TINY_D = dict(
     intermediate_size=384, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_bias=False,
     tie_word_embeddings=True, max_position_embeddings=2048, sliding_window=96,
     use_sliding_window=True, max_window_layers=1)
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+TINY = {"A": TINY_A, "B": TINY_B, "Bw": TINY_BW, "C": TINY_C, "D": TINY_D}
 
 
 def make_model_folder(folder, cfg: dict, seed: int, dtype: str = "float32", std: float = 0.05) -> Path:

@@ -13,7 +13,7 @@ import tinyinfer_b200.models  # noqa: F401
 
 
 def test_config_reads_its_own_keys_and_defaults():
-    cfg = Qwen3Config.from_dict(helpers.TINY_B)
+    cfg = Qwen3Config.from_dict(helpers.TINY_BW)
     assert cfg.resolved_head_dim == 32 and cfg.hidden_size // cfg.num_attention_heads == 16
     spec = cfg.model_spec()
     assert [l.mixer.window for l in spec.layers] == [None, 40, None]
@@ -29,8 +29,8 @@ def test_config_reads_its_own_keys_and_defaults():
     spec = Qwen3Config.from_dict(helpers.TINY_D).model_spec()
     assert [l.mixer.window for l in spec.layers] == [None, 96]
     # a round trip through to_dict
-    again = Qwen3Config.from_dict(Qwen3Config.from_dict(helpers.TINY_B).to_dict())
-    assert again.model_spec() == Qwen3Config.from_dict(helpers.TINY_B).model_spec()
+    again = Qwen3Config.from_dict(Qwen3Config.from_dict(helpers.TINY_BW).to_dict())
+    assert again.model_spec() == Qwen3Config.from_dict(helpers.TINY_BW).model_spec()
 
 
 @pytest.mark.parametrize("change,word", [
@@ -84,7 +84,7 @@ def cpu_model(folder):
 
 
 def test_random_folder_loads_and_is_reproducible(tmp_path):
-    cfg = Qwen3Config.from_dict(helpers.TINY_B)
+    cfg = Qwen3Config.from_dict(helpers.TINY_BW)
     a = write_random_model(tmp_path / "a", cfg, seed=7)
     b = write_random_model(tmp_path / "b", cfg, seed=7)
     c = write_random_model(tmp_path / "c", cfg, seed=8, dtype="bfloat16")
@@ -125,7 +125,7 @@ def test_tied_and_untied_heads(tmp_path):
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
-    folder = write_random_model(tmp_path / "m", Qwen3Config.from_dict(helpers.TINY_B), seed=1)
+    folder = write_random_model(tmp_path / "m", Qwen3Config.from_dict(helpers.TINY_BW), seed=1)
     tensors = load_file(str(folder / "model.safetensors"))
     del tensors["model.layers.0.self_attn.k_proj.weight"]
     del tensors["lm_head.weight"]

@@ -28,7 +28,7 @@ def session_for(folder, max_tokens, page_size, poison=True):
     return TraceSession(None, "float32", max_tokens, page_size=page_size, model=model, poison_cache=poison)
 
 
-@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8)])
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("Bw", 8)])
 def test_every_cut_matches_plain_on_cpu(tmp_path, cpu_ops, name, page):
     cfg = helpers.TINY[name]
     folder = helpers.make_model_folder(tmp_path / name, cfg, seed=3)

@@ -79,7 +79,7 @@ def test_the_package_refuses_to_run_without_cuda(tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 3e-2)])
-@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("D", 64)])
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("Bw", 8), ("D", 64)])
 def test_greedy_generation_on_the_gpu(tmp_path, name, page, dtype, tol):
     from tinyinfer_b200 import LLM
     cfg = helpers.TINY[name]
@@ -220,7 +220,7 @@ def test_shared_prompt_heads_are_taken_from_the_prefix_cache(tmp_path, dtype, to
 @pytest.mark.gpu
 def test_prefix_cache_is_off_where_a_window_gives_pages_back(tmp_path):
     from tinyinfer_b200 import LLM
-    cfg = helpers.TINY["B"]                     # has sliding-window layers
+    cfg = helpers.TINY["Bw"]                    # has sliding-window layers
     folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=2, dtype="float32")
     kw = dict(dtype="float32", max_num_batched_tokens=32, max_num_seqs=2, kvcache_block_size=8,
               num_kvcache_blocks=32, max_model_len=96)

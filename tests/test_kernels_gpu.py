@@ -221,6 +221,115 @@ def test_qk_norm_rope_append(ops, dtype, hq, hkv, d, page, rot, norm):
     assert torch.equal(q2, q) and torch.equal(torch.nan_to_num(kv2.float()), torch.nan_to_num(kv.float()))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page,rot", [(4, 2, 16, 4, 16), (3, 1, 64, 16, 64), (4, 1, 128, 64, 128),
+                                                (3, 3, 48, 5, 24), (2, 2, 80, 16, 40)])
+@pytest.mark.parametrize("interleaved,table", [(True, False), (False, True), (True, True)])
+def test_rotation_by_table_and_in_interleaved_pairs(ops, dtype, hq, hkv, d, page, rot, interleaved, table):
+    """The other forms of the rotation: pairs (2j, 2j + 1) instead of (j, j + rot / 2), and angles from a
+    table of cosines and sines per position instead of position * inv_freq (here: angles that no
+    inv_freq gives, a square-root law)."""
+    lens, starts = [9, 1, 23], [3, 0, 40]
+    bt, kv = paged_setup(dtype, [s + n for s, n in zip(starts, lens)], hq, hkv, d, page)
+    t = sum(lens)
+    qkv = rnd(t, (hq + 2 * hkv) * d, dtype=dtype, std=2.0)
+    pos = torch.tensor([p for s, n in zip(starts, lens) for p in range(s, s + n)], dtype=torch.int32, device=dev())
+    seq = torch.tensor([i for i, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=dev())
+    qw = 1 + 0.1 * rnd(d, dtype=torch.float32, seed=5)
+    kw = 1 + 0.1 * rnd(d, dtype=torch.float32, seed=6)
+    inv = (1.0 / (1e4 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(dev())
+    if table:
+        ang = torch.sqrt(torch.arange(70, dtype=torch.float32, device=dev()))[:, None] * inv[None, :] * 3.0
+        rotation = ops.Rotation(rot, cos_sin=torch.cat((ang.cos(), ang.sin()), dim=1).contiguous(), interleaved=interleaved)
+    else:
+        rotation = ops.Rotation(rot, inv_freq=inv, interleaved=interleaved)
+    args = dict(num_heads=hq, num_kv_heads=hkv, head_dim=d, q_norm_weight=qw, k_norm_weight=kw, eps=1e-6,
+                rotation=rotation, positions=pos, token_seq=seq, block_table=bt)
+    kv_ref = kv.clone()
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    q = ops.qk_norm_rope_append(qkv, kv_cache=kv, status=status, **args)
+    q_ref = ref.qk_norm_rope_append(qkv, kv_cache=kv_ref, **args)
+    assert int(status.item()) == 0
+    close(q, q_ref, dtype, scale=4.0)
+    written = ~torch.isnan(kv_ref.float())
+    assert torch.equal(written, ~torch.isnan(kv.float()))
+    close(kv[written], kv_ref[written], dtype, scale=4.0)
+    if table:                                   # a position the table does not reach: said, and nothing written
+        short = ops.Rotation(rot, cos_sin=rotation.cos_sin[:50].contiguous(), interleaved=interleaved)
+        kv3 = torch.full_like(kv, float("nan"))
+        ops.qk_norm_rope_append(qkv, kv_cache=kv3, status=status, **dict(args, rotation=short))
+        assert int(status.item()) == 4
+        beyond = (pos >= 50).nonzero().flatten().tolist()
+        for row in beyond:
+            pg = int(bt[int(seq[row]), int(pos[row]) // page])
+            assert torch.isnan(kv3[0, pg, :, int(pos[row]) % page].float()).all()
+
+
+def test_a_position_beyond_the_block_table_is_a_token_without_a_page(ops):
+    """A table narrower than a token's position needs: the kernels say so through the status word and
+    neither read the next request's row nor write into its pages."""
+    hq, hkv, d, page = 4, 2, 64, 16
+    for dtype in DTYPES:
+        bt = torch.tensor([[0], [1]], dtype=torch.int32, device=dev())          # one page each
+        kv = torch.full((2, 3, hkv, page, d), float("nan"), dtype=dtype, device=dev())
+        qkv = rnd(2, (hq + 2 * hkv) * d, dtype=dtype)
+        pos = torch.tensor([16, 3], dtype=torch.int32, device=dev())            # request 0 would need a second page
+        seq = torch.tensor([0, 1], dtype=torch.int32, device=dev())
+        status = torch.zeros(1, dtype=torch.int32, device=dev())
+        ops.qk_norm_rope_append(qkv, num_heads=hq, num_kv_heads=hkv, head_dim=d, q_norm_weight=None,
+                                k_norm_weight=None, eps=1e-6, positions=pos, token_seq=seq, kv_cache=kv,
+                                block_table=bt, status=status)
+        assert int(status.item()) == 1
+        assert torch.isnan(kv[:, 0].float()).all() and torch.isnan(kv[:, 2].float()).all()
+        assert not torch.isnan(kv[:, 1, :, 3].float()).any() and torch.isnan(kv[:, 1, :, 0].float()).all()
+        # the generic attention kernel: the key it cannot find counts as missing, the others still count
+        kv[:, 0] = 0.5
+        kv[:, 1] = 0.25
+        status.zero_()
+        q = rnd(2, hq, d, dtype=dtype, seed=3)
+        import tinyinfer_b200.ops as real_ops
+        out = torch.empty((2, hq * d), dtype=dtype, device=dev())
+        real_ops._run("core", "ti_attention_generic", out.data_ptr(), q.data_ptr(), kv.data_ptr(), pos.data_ptr(),
+                      seq.data_ptr(), bt.data_ptr(), 1, 2, hq, hkv, d, page, 3, d ** -0.5, 0, status.data_ptr(),
+                      real_ops._dtype_code(q), real_ops._stream())
+        assert int(status.item()) == 2
+        close(out[0], torch.full_like(out[0], 0.5), dtype)
+        close(out[1], torch.full_like(out[1], 0.25), dtype)
+
+
+def test_decode_attention_with_too_few_splits_says_so(ops):
+    """The exported decode entry point takes the number of splits from its caller. One too few: the
+    status word says so (23) and the merge reads only partials that belong to its own row."""
+    import ctypes
+    from tinyinfer_b200.ops import library
+    hq, hkv, d, page = 8, 2, 128, 64
+    lens = [700, 300]
+    dtype = torch.bfloat16
+    bt, kv = paged_setup(dtype, lens, hq, hkv, d, page, seed=2)
+    fill_cache(kv, bt, lens, hkv, d, page, dtype)
+    pos = torch.tensor([c - 1 for c in lens], dtype=torch.int32, device=dev())
+    seq = torch.arange(2, dtype=torch.int32, device=dev())
+    rows = torch.arange(2, dtype=torch.int32, device=dev())
+    q = rnd(2, hq, d, dtype=dtype, seed=8)
+    fn = ops._fn("sm100", "ti_attention_decode_bf16")
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    want = ref.paged_attention(q, kv, positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5)
+    for splits, code in ((3, 0), (2, 23)):
+        scratch = torch.full((2 * hq * splits * (d + 2),), float("nan"), dtype=torch.float32, device=dev())
+        out = torch.zeros((2, hq * d), dtype=dtype, device=dev())
+        rc = fn(out.data_ptr(), q.data_ptr(), kv.data_ptr(), scratch.data_ptr(),
+                scratch.data_ptr() + 4 * 2 * hq * splits * d, rows.data_ptr(), 2, pos.data_ptr(), seq.data_ptr(),
+                bt.data_ptr(), bt.shape[1], hq, hkv, d, page, kv.shape[1], d ** -0.5, 0, 256, splits,
+                status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, library.load("sm100").ti_last_error().decode()
+        assert int(status.item()) == code
+        assert torch.isfinite(out.float()).all()
+        close(out[1], want[1], dtype)                     # the short request is whole either way
+        if code == 0:
+            close(out[0], want[0], dtype)
+        status.zero_()
+
+
 def fill_cache(kv, bt, lens, hkv, d, page, dtype, seed=0):
     """Writes random keys and values for positions 0..len-1 of every request; returns them."""
     ks, vs = [], []

@@ -2,29 +2,55 @@
 
 ``tests/golden/ref_logits.npz`` was written by ``tests/golden/make_golden.py``, which runs
 tinyinfer/models/qwen3.py of the reference on the CPU (its three extension calls replaced by
-the PyTorch formulas the reference keeps beside them)."""
+stand-ins made of the reference's own live Python layers); ``tests/golden/ref_logits_gpu.npz`` by the
+same script on a B200 with no stand-in: there the reference's CUDA kernels (norm, rotation,
+feed-forward, FlashAttention and FlashDecoding) computed every number, in float32."""
 from pathlib import Path
 
 import numpy as np
 import torch
 
 import plain_qwen3 as plain
-from golden.make_golden import GOLDEN_CONFIG, GOLDEN_TOKENS, golden_weights
+from golden.make_golden import GOLDEN_CONFIG, GOLDEN_MODELS, GOLDEN_TOKENS, golden_weights
 
 GOLDEN = Path(__file__).parent / "golden" / "ref_logits.npz"
+GOLDEN_GPU = Path(__file__).parent / "golden" / "ref_logits_gpu.npz"
 
 
 def test_plain_matches_reference_model_code():
+    """Two models (untied with head_dim != hidden / heads; tied), each request whole and in two portions."""
     ref = np.load(GOLDEN)
-    w32 = golden_weights()
-    for dtype, tol in ((torch.float32, 2e-5), (torch.float64, 2e-5)):
-        w = {k: v.to(dtype) for k, v in w32.items()}
-        for r, tokens in enumerate(GOLDEN_TOKENS):
-            got = plain.forward(GOLDEN_CONFIG, w, tokens).to(torch.float64).numpy()
-            for tag in ("whole", "cut"):
-                want = ref[f"req{r}_{tag}"].astype(np.float64)
+    for prefix, (cfg, tokens_list, seed) in GOLDEN_MODELS.items():
+        w32 = golden_weights(cfg, seed)
+        for dtype, tol in ((torch.float32, 2e-5), (torch.float64, 2e-5)):
+            w = {k: v.to(dtype) for k, v in w32.items()}
+            for r, tokens in enumerate(tokens_list):
+                got = plain.forward(cfg, w, tokens).to(torch.float64).numpy()
+                for tag in ("whole", "cut"):
+                    want = ref[f"{prefix}req{r}_{tag}"].astype(np.float64)
+                    assert got.shape == want.shape
+                    assert np.abs(got - want).max() < tol, (prefix, dtype, r, tag)
+
+
+def test_plain_matches_the_reference_kernels():
+    """The same models through the reference's own CUDA kernels on a B200 (float32): whole prompts and
+    portions through its FlashAttention kernel, the last tokens one by one through its FlashDecoding
+    kernel. The tolerance is the one the engine's 32-bit path is held to."""
+    ref = np.load(GOLDEN_GPU)
+    checked = 0
+    for prefix, (cfg, tokens_list, seed) in GOLDEN_MODELS.items():
+        w = {k: v.double() for k, v in golden_weights(cfg, seed).items()}
+        for r, tokens in enumerate(tokens_list):
+            got = plain.forward(cfg, w, tokens).numpy()
+            for tag in ("whole", "cut", "decode"):
+                key = f"{prefix}req{r}_{tag}"
+                if key not in ref.files:
+                    continue
+                want = ref[key].astype(np.float64)
                 assert got.shape == want.shape
-                assert np.abs(got - want).max() < tol, (dtype, r, tag)
+                assert np.abs(got - want).max() <= 5e-5 * np.abs(got).max(), (key, np.abs(got - want).max())
+                checked += 1
+    assert checked >= 11
 
 
 def test_plain_window_equals_full_when_window_covers_everything():

@@ -34,7 +34,7 @@ def traces_for(requests):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("C", 16), ("D", 64)])
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("Bw", 8), ("C", 16), ("D", 64)])
 def test_every_cut_matches_plain(tmp_path, name, page, dtype):
     from tinyinfer_b200.engine.replay import TraceSession
     cfg = helpers.TINY[name]
@@ -67,7 +67,7 @@ def test_every_cut_matches_plain(tmp_path, name, page, dtype):
 def test_long_decoding_and_first_tokens(tmp_path, dtype):
     """A request decoded token by token from its very first token for several hundred steps."""
     from tinyinfer_b200.engine.replay import TraceSession
-    cfg = helpers.TINY["B"]
+    cfg = helpers.TINY["Bw"]
     folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=9, dtype=dtype)
     requests = helpers.random_requests(cfg, [400], seed=1)
     want = helpers.plain_logits(folder, requests)
@@ -117,15 +117,15 @@ def test_an_id_that_comes_back_gets_its_own_pages(tmp_path):
     folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=7, dtype="bfloat16")
     rng = np.random.default_rng(4)
     first = [int(t) for t in rng.integers(0, cfg["vocab_size"], 12)]       # one page of 16
-    again = [int(t) for t in rng.integers(0, cfg["vocab_size"], 76)]
-    other = [int(t) for t in rng.integers(0, cfg["vocab_size"], 40 + 4 + 76)]
+    again = [int(t) for t in rng.integers(0, cfg["vocab_size"], 68)]       # its fifth page is the ended request's
+    other = [int(t) for t in rng.integers(0, cfg["vocab_size"], 40 + 4 + 68)]  # 7 + 5 pages: the whole pool of 12
     steps = [{"step": 0, "entries": [{"id": "a", "tokens": first[:8], "want": [7]},
                                      {"id": "b", "tokens": other[:40], "want": [39]}], "end": []}]
     for i in range(4):                                                     # decode-only steps of "a" and "b"
         steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [first[8 + i]], "want": [0]},
                                                       {"id": "b", "tokens": [other[40 + i]], "want": [0]}],
                       "end": ["a"] if i == 3 else []})
-    for i in range(76):                                                    # the id "a" is back, one token a step
+    for i in range(68):                                                    # the id "a" is back, one token a step
         steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [again[i]], "want": [0]},
                                                       {"id": "b", "tokens": [other[44 + i]], "want": [0]}], "end": []})
     session = TraceSession(folder, "bfloat16", 192, page_size=16, poison_cache=True, cuda_graphs=True)
@@ -142,6 +142,7 @@ def test_an_id_that_comes_back_gets_its_own_pages(tmp_path):
         session.runner.manager.check_consistency()
     assert session.runner.graph_replays > 60
     assert session.runner.manager.stats()["groups"][0]["pages_taken"] > 12, "the ended request's page was not used again"
+    assert session.runner.manager.stats()["groups"][0]["free_pages"] == 0
     want = helpers.plain_logits(folder, {"a": first, "a2": again, "b": other})
     bad = helpers.first_bad(got, want, TOL["bfloat16"])
     assert bad is None, bad

@@ -1,6 +1,6 @@
 """A mixer with state of its own, a feed-forward that routes every token to one of three experts, a
-position encoding with stretched positions, a run order that names a layer twice, and an entry that
-reads another entry's cache: all defined HERE, registered, built and stepped through the
+position encoding with stretched positions and another that turns neighbouring features by angles from
+a table, a run order that names a layer twice, and an entry that reads another entry's cache: all defined HERE, registered, built and stepped through the
 framework's own model, cache and step function without touching its files. The toy is no one's model."""
 import json
 from dataclasses import dataclass
@@ -120,8 +120,42 @@ class StretchedRope(PositionEncoding):
 
 register_position("toy_stretched_rope", StretchedRope)
 
+
+@dataclass(frozen=True)
+class PairTableRopeSpec:
+    theta: float
+    rotary_dim: int                    # may be less than the head size: the rest of a head is not turned
+    max_positions: int
+    kind: str = "toy_pair_table_rope"
+
+
+def pair_table_angles(theta, rotary_dim, positions, dtype):
+    """angle[p][j] = 4 * log(1 + p) * theta ** (-2j / rotary_dim): no inverse frequencies give this law."""
+    freq = theta ** (-torch.arange(0, rotary_dim, 2, dtype=dtype) / rotary_dim)
+    return 4.0 * torch.log1p(torch.as_tensor(positions, dtype=dtype))[:, None] * freq[None, :]
+
+
+class PairTableRope(PositionEncoding):
+    """Neighbouring features (2j, 2j + 1) form a pair, and a pair's angle at a position stands in a table
+    of cosines and sines: what the part hands to its mixer is an ``ops.Rotation`` that says so. The mixer
+    and the fused kernel are the framework's own, unchanged."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        ang = pair_table_angles(spec.theta, spec.rotary_dim, range(spec.max_positions), torch.float32)
+        self.table = torch.cat((ang.cos(), ang.sin()), dim=1).contiguous().to(device)
+
+    def rotation(self):
+        from tinyinfer_b200 import ops
+        return ops.Rotation(self.spec.rotary_dim, cos_sin=self.table, interleaved=True)
+
+
+register_position("toy_pair_table_rope", PairTableRope)
+
 TOY = dict(architectures=["ToyForCausalLM"], vocab_size=97, hidden_size=48, heads=3, kv_heads=1, head_dim=16,
-           intermediate_size=80, eps=1e-5, theta=10000.0, max_positions=256, experts=3, expert_size=24, stretch=4.0)
+           intermediate_size=80, eps=1e-5, theta=10000.0, max_positions=256, experts=3, expert_size=24, stretch=4.0,
+           position="stretched")
+TOY_PAIRS = dict(TOY, position="pairs_from_table", rotary_dim=12)
 
 
 class ToyConfig:
@@ -139,8 +173,9 @@ class ToyConfig:
     def model_spec(self):
         d = self.d
         h, eps = d["hidden_size"], d["eps"]
-        attn = AttentionSpec(h, d["heads"], d["kv_heads"], d["head_dim"], d["head_dim"] ** -0.5,
-                             StretchedRopeSpec(d["theta"], d["head_dim"], d["stretch"]),
+        position = (StretchedRopeSpec(d["theta"], d["head_dim"], d["stretch"]) if d["position"] == "stretched"
+                    else PairTableRopeSpec(d["theta"], d["rotary_dim"], d["max_positions"]))
+        attn = AttentionSpec(h, d["heads"], d["kv_heads"], d["head_dim"], d["head_dim"] ** -0.5, position,
                              qk_norm=NormSpec(d["head_dim"], eps))
         ffn = GatedMLPSpec(h, d["intermediate_size"])
         routed = RoutedSpec(h, d["expert_size"], d["experts"])
@@ -157,12 +192,20 @@ register_architecture("ToyForCausalLM", ToyConfig, lambda cfg, dtype, device: De
 
 
 # ------------------------------------------------------------------ its plain statement
-def toy_plain(w, tokens):
-    d = TOY
-    cfg = dict(num_attention_heads=d["heads"], num_key_value_heads=d["kv_heads"], head_dim=d["head_dim"],
-               rms_norm_eps=d["eps"], rope_theta=d["theta"], hidden_size=d["hidden_size"])
+def toy_plain(w, tokens, d=TOY):
     pos = [i / d["stretch"] for i in range(len(tokens))]
     t = len(tokens)
+
+    def turn(a):
+        """[T, heads, head_dim] turned by the toy's position encoding."""
+        if d["position"] == "stretched":
+            return plain.rope(a, pos, d["theta"])
+        rd = d["rotary_dim"]
+        ang = pair_table_angles(d["theta"], rd, range(t), a.dtype)
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        even, odd = a[..., 0:rd:2], a[..., 1:rd:2]
+        turned = torch.stack((even * cos - odd * sin, odd * cos + even * sin), dim=-1).flatten(-2)
+        return torch.cat((turned, a[..., rd:]), dim=-1)
 
     def attn_layer(x, kv_from=None):
         p = "model.layers.0."
@@ -171,8 +214,8 @@ def toy_plain(w, tokens):
         q = (hn @ w[p + "self_attn.q_proj.weight"].T).view(t, d["heads"], d["head_dim"])
         k = (src @ w[p + "self_attn.k_proj.weight"].T).view(t, d["kv_heads"], d["head_dim"])
         v = (src @ w[p + "self_attn.v_proj.weight"].T).view(t, d["kv_heads"], d["head_dim"])
-        q = plain.rope(plain.rmsnorm(q, w[p + "self_attn.q_norm.weight"], d["eps"]), pos, d["theta"])
-        k = plain.rope(plain.rmsnorm(k, w[p + "self_attn.k_norm.weight"], d["eps"]), pos, d["theta"])
+        q = turn(plain.rmsnorm(q, w[p + "self_attn.q_norm.weight"], d["eps"]))
+        k = turn(plain.rmsnorm(k, w[p + "self_attn.k_norm.weight"], d["eps"]))
         o = plain.attention(q, k, v, d["head_dim"] ** -0.5).reshape(t, -1) @ w[p + "self_attn.o_proj.weight"].T
         x = x + o
         hn2 = plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], d["eps"])
@@ -200,11 +243,11 @@ def toy_plain(w, tokens):
     return x @ w["model.embed_tokens.weight"].T
 
 
-def run_toy(tmp_path, device, dtype_name):
+def run_toy(tmp_path, device, dtype_name, toy=TOY):
     from tinyinfer_b200.engine.replay import TraceSession
     from tinyinfer_b200.config import load_config
     from tinyinfer_b200.weights import load_weights, write_random_model
-    folder = write_random_model(tmp_path / "toy", ToyConfig(TOY), seed=11, std=0.08)
+    folder = write_random_model(tmp_path / "toy", ToyConfig(toy), seed=11, std=0.08)
     assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyForCausalLM"]
     arch, cfg = load_config(folder)
     model = arch.model_factory(cfg, torch.float32, torch.device(device))
@@ -213,7 +256,7 @@ def run_toy(tmp_path, device, dtype_name):
     assert needs[1][0] is None and needs[1][1].shape == (48,) and needs[0][0].num_kv_heads == 1
     _, w = plain.read_model_folder(folder, torch.float64)
     requests = helpers.random_requests(dict(vocab_size=97), [40, 9, 70, 33, 2, 50], seed=2)
-    want = {rid: toy_plain(w, toks).numpy() for rid, toks in requests.items()}
+    want = {rid: toy_plain(w, toks, toy).numpy() for rid, toks in requests.items()}
     for steps in (helpers.trace_whole(requests), helpers.trace_chunked(requests, seed=4),
                   helpers.trace_mixed(requests, seed=5, max_live=3)):
         # three state slots for six requests: slots are used again and must start from zero
@@ -225,12 +268,14 @@ def run_toy(tmp_path, device, dtype_name):
 
 
 @pytest.mark.gpu
-def test_toy_architecture_steps_on_the_gpu(tmp_path):
-    run_toy(tmp_path, "cuda:0", "float32")
+@pytest.mark.parametrize("toy", [TOY, TOY_PAIRS], ids=["stretched", "pairs_from_table"])
+def test_toy_architecture_steps_on_the_gpu(tmp_path, toy):
+    run_toy(tmp_path, "cuda:0", "float32", toy)
 
 
-def test_toy_architecture_steps_with_plain_ops(tmp_path, monkeypatch):
+@pytest.mark.parametrize("toy", [TOY, TOY_PAIRS], ids=["stretched", "pairs_from_table"])
+def test_toy_architecture_steps_with_plain_ops(tmp_path, monkeypatch, toy):
     from tinyinfer_b200 import ops
     for name in torch_ops.ALL:
         monkeypatch.setattr(ops, name, getattr(torch_ops, name))
-    run_toy(tmp_path, "cpu", "float32")
+    run_toy(tmp_path, "cpu", "float32", toy)

@@ -4,9 +4,11 @@ Some callers of the kernels may not allocate device memory (code inside another 
 region, an engine that has handed all free memory to its cache). For them the library exports
 ``ti_attention_decode_bf16_noalloc``, which keeps the split partials in an array built into the
 library. This test calls that symbol with ctypes, twice in a row with different inputs, and checks
-each result against the ordinary entry point (which takes a scratch buffer from the caller) within
-the tolerance the other kernel tests use; it also checks that the call allocates nothing and that
-a call beyond the built-in capacity is refused with a message. It is collected last so that a run
+each result against the ordinary entry point (which takes a scratch buffer from the caller) and
+against the plain PyTorch statement of paged attention, within the tolerance the other kernel tests
+use (contexts that end exactly on a split of 256 keys and one key past it, and a sliding window among
+them); it also checks that the call allocates nothing and that a call beyond the built-in capacity is
+refused with a message. It is collected last so that a run
 that stops at the first failure has already run every other test."""
 import ctypes
 
@@ -54,27 +56,31 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice():
     stream = torch.cuda.current_stream().cuda_stream
     status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
 
-    def call(case, out, splits=None):
+    def call(case, out, splits=None, window=0):
         return fn(out.data_ptr(), case["q"].data_ptr(), case["kv"].data_ptr(), case["rows"].data_ptr(),
                   case["rows"].shape[0], case["positions"].data_ptr(), case["token_seq"].data_ptr(),
                   case["block_table"].data_ptr(), case["block_table"].shape[1], case["hq"], case["hkv"], case["d"],
-                  case["page"], case["pages"], float(case["d"]) ** -0.5, 0, splits or case["splits"],
+                  case["page"], case["pages"], float(case["d"]) ** -0.5, window, splits or case["splits"],
                   status.data_ptr(), stream)
 
-    # two calls in a row, the second with fewer and shorter requests: what the first left in the
-    # shared array must not show in the second
-    for seed, contexts in ((1, [700, 1, 256, 257, 1030]), (2, [90, 300])):
+    import torch_ops
+    # calls in a row, each with fewer or shorter requests than the one before: what a call left in the
+    # shared array must not show in the next
+    for seed, contexts, window in ((1, [700, 1, 256, 257, 1030], 0), (2, [90, 300], 0), (3, [512, 513, 40], 300)):
         case = make_case(seed, contexts)
-        want = ops.paged_attention(case["q"], case["kv"], positions=case["positions"], token_seq=case["token_seq"],
-                                   block_table=case["block_table"], scale=float(case["d"]) ** -0.5)
+        args = dict(positions=case["positions"], token_seq=case["token_seq"], block_table=case["block_table"],
+                    scale=float(case["d"]) ** -0.5, window=window or None)
+        want = ops.paged_attention(case["q"], case["kv"], **args)
+        plain = torch_ops.paged_attention(case["q"], case["kv"], **args)
         out = torch.full_like(want, float("nan"))
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
-        assert call(case, out) == 0, lib.ti_last_error().decode()
+        assert call(case, out, window=window) == 0, lib.ti_last_error().decode()
         torch.cuda.synchronize()
         assert (torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]) == before, "the call allocated"
         assert torch.isfinite(out.float()).all()
         torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(out.float(), plain.float(), rtol=2e-2, atol=2e-2)
     assert int(status.item()) == 0
     ops.check_kernel_status()
 

@@ -39,6 +39,7 @@ def known_architectures():
 
 def known_presets() -> Dict[str, str]:
     """preset name -> the architecture that offers it (the one registered last wins a shared name)."""
+    from .. import models  # noqa: F401  (the built-in architecture registers itself on import)
     return {preset: arch.name for arch in _ARCHITECTURES.values() for preset in arch.presets}
 
 

@@ -500,8 +500,10 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
 // The array is `static __device__`: every GPU that loads this library holds TI_NOALLOC_SCRATCH_FLOATS
 // floats (8 MB) of it until the process exits. In host code the array's name is only a stand-in, not
 // a device address, so the first call on each device looks the address up with
-// cudaGetSymbolAddress while that device is current and keeps it. That first call should be made
-// before any stream capture begins. All calls on a device share the array: two calls that overlap on
+// cudaGetSymbolAddress while that device is current and keeps it; the same call may make the driver
+// load this library's code and array onto the device and raises the kernel's shared-memory limit there.
+// That first call should be made at start-up, before any stream capture begins and before allocation
+// becomes off limits. All calls on a device share the array: two calls that overlap on
 // the GPU (different streams, no ordering) race on it. Nothing in it needs clearing between calls:
 // every word the merge kernel reads was written by the split kernel of the same call.
 constexpr long long TI_NOALLOC_SCRATCH_FLOATS = 2ll * 1024 * 1024;

@@ -10,8 +10,11 @@
  * that loads it, held until exit), so
  *     num_rows * num_q_heads * max_splits * (head_dim + 2)  <=  ti_attention_decode_noalloc_capacity()
  * must hold; larger calls are refused with a message (return value != 0, text from ti_last_error()).
- * The first call on a device resolves the array's device address; make it before any stream
- * capture. Calls on one device share the array: order them on one stream, or they race.
+ * The first call on a device does set-up work that later calls do not: it resolves the array's device
+ * address, may make the driver load this library's code and its 8 MB array onto that device, and
+ * raises the kernel's shared-memory limit there. Make that call at start-up, before any stream
+ * capture and before the region in which allocation is forbidden begins. Calls on one device share
+ * the array: order them on one stream, or they race.
  */
 #ifndef TINYINFER_B200_NOALLOC_H
 #define TINYINFER_B200_NOALLOC_H
