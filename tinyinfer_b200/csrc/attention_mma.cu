@@ -15,7 +15,6 @@
 // else is in the batch. Partial results (unnormalised output, maximum, sum per split) go to float32
 // scratch and a second kernel merges them. (Prompt portions: attention_prefill_tcgen05.cu.)
 #include "sm100_ptx.cuh"
-#include <cstdlib>
 
 namespace {
 
@@ -419,10 +418,6 @@ int decode_slots(int d, int group) {
 // CTAs the larger split loses, 1 x 4,096: 9.8 and 13.1 us). Smaller splits also even out requests of
 // different lengths, hence the margin.
 TI_API int ti_attention_decode_plan(int num_rows, int hq, int hkv, int d, int max_context, int window) {
-    if (const char* e = getenv("TINYINFER_B200_DECODE_CHUNK")) {          // experiments only
-        const int c = atoi(e);
-        if (c >= CHUNK && c % CHUNK == 0) return c;
-    }
     if (num_rows <= 0 || hkv <= 0 || hq % hkv != 0 || (d != 64 && d != 128)) return CHUNK;
     const int slots = decode_slots(d, hq / hkv);
     const long long visible = window > 0 && window < max_context ? window : max_context;

@@ -26,7 +26,6 @@
 // *status, raises the CTA's abort flag, and all warps fall through to the common exit, where tensor
 // memory is freed.
 #include "sm100_ptx.cuh"
-#include <cstdlib>
 #include <type_traits>
 
 namespace {
@@ -722,10 +721,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int num_counters, bool share_sum) {
     if (tiles > num_counters) return 1;
     const int per_sm = bn <= 64 ? 2 : 1;                  // Cfg<BN>::CTAS_PER_SM
-    if (const char* forced = getenv("TINYINFER_B200_GEMM_SPLITS")) {     // experiments only
-        const int s = atoi(forced);
-        if (s >= 1 && num_kb / s >= 1 && (long long)tiles * s * bn * BM <= workspace_floats) return s;
-    }
     const int sms = ti_sm_count() * per_sm;               // CTAs that run side by side
     if (tiles * 2 >= sms) return 1;                       // every SM has a tile: cutting them only adds the merge
     if (share_sum) {
@@ -850,8 +845,7 @@ static int gemm_entry(void* out, const void* x, const void* w, const float* bias
         // last unit alone makes a trip to L2 per few tokens, one after the other; up to 8 tokens that is
         // one trip and sharing only adds the wait: measured). Needs every unit running at once, and the
         // 16-byte path of the sum.
-        static const int share_from = [] { const char* e = getenv("TINYINFER_B200_GEMM_SHARE_SUM"); return e ? atoi(e) : 16; }();
-        const bool may_share = share_from > 0 && M >= share_from && !gated && (N & 3) == 0 && ((uintptr_t)out & 15) == 0 &&
+        const bool may_share = M >= 16 && !gated && (N & 3) == 0 && ((uintptr_t)out & 15) == 0 &&
                                ((uintptr_t)residual & 7) == 0 && ((uintptr_t)bias & 15) == 0;
         if (workspace && counters)
             p.splits = choose_splits(tiles, (K + BK - 1) / BK, bn, workspace_floats, num_counters, may_share);
@@ -882,9 +876,8 @@ static int gemm_entry(void* out, const void* x, const void* w, const float* bias
         const long long tiles256 = (long long)row_tiles * ((N + cpt256 - 1) / cpt256);
         // Few tiles, many tokens (about 130 to 700 of them): the k loops are cut so that as many units as
         // there are SMs run at once, and the units of a tile add their partial sums up together.
-        static const bool spread = [] { const char* e = getenv("TINYINFER_B200_GEMM_SPREAD"); return !e || atoi(e) != 0; }();
         const int sms = ti_sm_count(), num_kb = (K + BK - 1) / BK;
-        if (spread && !gated && workspace && counters && tiles256 <= num_counters && tiles256 * 2 <= sms) {
+        if (!gated && workspace && counters && tiles256 <= num_counters && tiles256 * 2 <= sms) {
             int cut = (int)(sms / tiles256);
             cut = cut < 8 ? cut : 8;
             cut = cut < num_kb / 8 ? cut : num_kb / 8;
@@ -909,8 +902,7 @@ static int gemm_entry(void* out, const void* x, const void* w, const float* bias
         const int sms = ti_sm_count();
         const long long tall_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * col_tiles;
         const long long waves = (row_tiles * col_tiles + sms - 1) / sms, tall_waves = (tall_tiles + sms - 1) / sms;
-        static const int forced = [] { const char* e = getenv("TINYINFER_B200_GEMM_TALL"); return e ? atoi(e) : -1; }();
-        const bool tall = forced >= 0 ? (forced != 0 && M > BM) : (M >= 3072 && tall_waves * 177 < waves * 100);
+        const bool tall = M >= 3072 && tall_waves * 177 < waves * 100;
         if (tall) {
             if (!ti_get_bf16_map(x, M, K, 2 * BM, &rows_map)) return -1;
             return launch<256, 2>(rows_map, cols_map, p, (int)tall_tiles, stream);

@@ -11,7 +11,6 @@ norm weights, biases and logits are float32, indices are int32, and everything i
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
@@ -246,8 +245,7 @@ class NormLink:
 def norm_link_ok(x: torch.Tensor) -> bool:
     """True if the products around an RMSNorm of ``x`` can share it (bfloat16 on the tensor cores, at
     most 64 rows): the norm kernel between them, a hop of a decode step, is then left out."""
-    return (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= NORM_LINK_MAX_TOKENS
-            and os.environ.get("TINYINFER_B200_NORM_LINK", "1") != "0")
+    return x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= NORM_LINK_MAX_TOKENS
 
 
 def _gemm_linked(out, x, w, bias, residual, m, n, k, gated, scale, emit_weight):
