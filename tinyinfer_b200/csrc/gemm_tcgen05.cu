@@ -137,32 +137,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            // The copies of one k block: `rows_side` / `cols_side` pick the operand(s) to load.
-            auto issue = [&](int unit, int kb, int s, bool rows_side, bool cols_side) {
-                const int tile = unit / p.splits;
-                const int rt = tile % row_tiles, ct = tile / row_tiles;
-                const int r0 = rt * rows_per_tile, c0 = ct * cols_per_tile;
+            // The copies of one k block of the tile whose first row and column are r0 and c0: `rows_side` /
+            // `cols_side` pick the operand(s) to load. (This thread's work per k block is on the critical
+            // path of a decode step: what depends on the unit alone is worked out once per unit.)
+            auto issue = [&](int r0, int c0, int kb, int s, bool rows_side, bool cols_side) {
                 const uint32_t a_dst = smem_u32(stages + s * C::STAGE_BYTES);
                 const uint32_t b_dst = a_dst + TM * BM * BK * 2;      // tall tiles: one copy of 256 rows
                 if (rows_side) {
-                    if (p.gated && p.swap) {          // 64 gate rows, then 64 up rows
-                        tma_load_2d(a_dst, &map_rows, full_bar(s), kb * BK, r0);
+                    tma_load_2d(a_dst, &map_rows, full_bar(s), kb * BK, r0);
+                    if (p.gated && p.swap)            // 64 gate rows, then 64 up rows
                         tma_load_2d(a_dst + (BM / 2) * BK * 2, &map_rows, full_bar(s), kb * BK, p.N + r0);
-                    } else {
-                        tma_load_2d(a_dst, &map_rows, full_bar(s), kb * BK, r0);
-                    }
                 }
                 if (cols_side) {
-                    if (p.gated && !p.swap) {         // BN/2 gate rows, then BN/2 up rows
-                        tma_load_2d(b_dst, &map_cols, full_bar(s), kb * BK, c0);
+                    tma_load_2d(b_dst, &map_cols, full_bar(s), kb * BK, c0);
+                    if (p.gated && !p.swap)           // BN/2 gate rows, then BN/2 up rows
                         tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_cols, full_bar(s), kb * BK, p.N + c0);
-                    } else {
-                        tma_load_2d(b_dst, &map_cols, full_bar(s), kb * BK, c0);
-                    }
                 }
             };
-            auto kb_range = [&](int unit, int& kb0, int& kb1) {
-                const int split = unit % p.splits;
+            auto unit_range = [&](int unit, int& r0, int& c0, int& kb0, int& kb1) {
+                const int tile = unit / p.splits, split = unit % p.splits;
+                r0 = (tile % row_tiles) * rows_per_tile;
+                c0 = (tile / row_tiles) * cols_per_tile;
                 kb0 = (int)((long long)split * num_kb / p.splits);
                 kb1 = (int)((long long)(split + 1) * num_kb / p.splits);
             };
@@ -172,29 +167,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             const bool weights_are_rows = p.swap != 0;
             uint32_t pre = 0;
             for (int unit = blockIdx.x; unit < num_units && pre < (uint32_t)C::STAGES; unit += gridDim.x) {
-                int kb0, kb1;
-                kb_range(unit, kb0, kb1);
+                int r0, c0, kb0, kb1;
+                unit_range(unit, r0, c0, kb0, kb1);
                 for (int kb = kb0; kb < kb1 && pre < (uint32_t)C::STAGES; ++kb, ++pre) {
                     mbar_expect_tx(full_bar(pre), C::STAGE_BYTES);
-                    issue(unit, kb, pre, weights_are_rows, !weights_are_rows);
+                    issue(r0, c0, kb, pre, weights_are_rows, !weights_are_rows);
                 }
             }
             ti_grid_wait();
             uint32_t it = 0;
             bool ok = true;
             for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
-                int kb0, kb1;
-                kb_range(unit, kb0, kb1);
+                int r0, c0, kb0, kb1;
+                unit_range(unit, r0, c0, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % C::STAGES;
                     if (it < pre) {                   // its weights are already on their way
-                        issue(unit, kb, s, !weights_are_rows, weights_are_rows);
+                        issue(r0, c0, kb, s, !weights_are_rows, weights_are_rows);
                         continue;
                     }
                     const uint32_t ph = (it / C::STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-                    issue(unit, kb, s, true, true);
+                    issue(r0, c0, kb, s, true, true);
                 }
             }
             // After an abort, give the copies this CTA still has in flight time to land (they take
