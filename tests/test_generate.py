@@ -231,21 +231,71 @@ def test_prefix_cache_is_off_where_a_window_gives_pages_back(tmp_path):
 
 def test_a_kernel_status_that_is_set_stops_generation(tmp_path, monkeypatch):
     """The kernels' status words come home with the sampled tokens; a step during which one was set
-    (here by hand: nothing on a CPU sets it) raises instead of handing its tokens on."""
+    (here by hand: nothing on a CPU sets it) raises when its tokens are read back, instead of handing
+    them on: in the same call without overlap, in the next call with it."""
     from tinyinfer_b200 import ops
     import tinyinfer_b200.engine.llm as llm_mod
     for name in torch_ops.ALL:
         monkeypatch.setattr(ops, name, getattr(torch_ops, name))
     monkeypatch.setattr(llm_mod, "require_cuda", lambda d: torch.device("cpu"))
     folder = helpers.make_model_folder(tmp_path / "m", helpers.TINY_A, seed=3)
-    llm = llm_mod.LLM(folder, dtype="float32", device="cpu", max_num_batched_tokens=24, max_num_seqs=3,
-                      kvcache_block_size=4, num_kvcache_blocks=30, max_model_len=128)
-    llm.add_request([5, 6, 7], SamplingParams(greedy=True, max_tokens=4))
-    llm.step()
     words = ops.status_words(torch.device("cpu"))
-    for word, code, text in ((0, 15, "gave up waiting"), (1, 1, "without a page")):
-        words[word] = code
-        with pytest.raises(ops.KernelError, match=text):
+    for overlap in (False, True):
+        for word, code, text in ((0, 15, "gave up waiting"), (1, 1, "without a page")):
+            llm = llm_mod.LLM(folder, dtype="float32", device="cpu", max_num_batched_tokens=24, max_num_seqs=3,
+                              kvcache_block_size=4, num_kvcache_blocks=30, max_model_len=128, overlap_steps=overlap)
+            llm.add_request([5, 6, 7], SamplingParams(greedy=True, max_tokens=6))
             llm.step()
-        assert words.tolist() == [0, 0]                      # reported once, then cleared
+            words[word] = code
+            with pytest.raises(ops.KernelError, match=text):
+                llm.step()                                   # the step that runs while the word is set
+                assert overlap
+                llm.step()                                   # with overlap its tokens are read back one call later
+            assert words.tolist() == [0, 0]                  # reported once, then cleared
     words.zero_()
+
+
+def test_overlapped_steps_give_the_tokens_of_steps_one_by_one(tmp_path, monkeypatch):
+    """Launching a step before the tokens of the one before are read back changes nothing that a request
+    sees: the same tokens, greedy and sampled, the same reasons to end (token limit, end-of-sequence token,
+    which is found one step late and whose extra step is dropped), the same prefix-cache hits, every page
+    given back."""
+    from tinyinfer_b200 import ops
+    import tinyinfer_b200.engine.llm as llm_mod
+    for name in torch_ops.ALL:
+        monkeypatch.setattr(ops, name, getattr(torch_ops, name))
+    monkeypatch.setattr(llm_mod, "require_cuda", lambda d: torch.device("cpu"))
+    cfg = helpers.TINY_A
+    folder = helpers.make_model_folder(tmp_path / "m", cfg, seed=3)
+    requests = helpers.random_requests(cfg, [1, 7, 16, 33, 50, 21, 9], seed=6)
+    prompts = list(requests.values())
+    prompts.append(prompts[3][:20] + [3, 1, 4])              # shares a head with another prompt
+    params = [SamplingParams(greedy=i % 2 == 0, temperature=0.9, topk=40, max_tokens=3 + 2 * i, seed=11)
+              for i in range(len(prompts))]
+
+    def run(overlap, eos):
+        llm = llm_mod.LLM(folder, dtype="float32", device="cpu", max_num_batched_tokens=24, max_num_seqs=3,
+                          kvcache_block_size=4, num_kvcache_blocks=40, prefill_chunk=8, max_model_len=128,
+                          overlap_steps=overlap, eos_token_id=eos, track_nll=True)
+        outs = llm.generate(prompts, params)
+        assert not llm.runner.manager.live_requests and llm.is_finished()
+        llm.runner.manager.check_consistency()
+        return outs, llm.runner.steps_run
+
+    plain_outs, plain_steps = run(False, -1)
+    # an end-of-sequence token that some request really draws part-way
+    eos = plain_outs[5]["token_ids"][4]
+    for end in (-1, eos):
+        a, steps_a = run(False, end)
+        b, steps_b = run(True, end)
+        assert [o["token_ids"] for o in a] == [o["token_ids"] for o in b]
+        assert [o["finish_reason"] for o in a] == [o["finish_reason"] for o in b]
+        assert [o["num_cached_tokens"] for o in a] == [o["num_cached_tokens"] for o in b]
+        for x, y in zip(a, b):
+            # the same tokens under the same model; the extra step of a request that ended on a token puts one
+            # more row into that step's batch, which moves the others' float32 sums by rounding
+            assert abs(x["statistics"]["perplexity"] - y["statistics"]["perplexity"]) <= (
+                0.0 if end < 0 else 1e-4 * x["statistics"]["perplexity"])
+        if end >= 0:
+            assert "eos" in [o["finish_reason"] for o in a]
+        assert steps_b >= steps_a                            # a request that ended on a token ran one step more

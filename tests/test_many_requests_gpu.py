@@ -39,8 +39,8 @@ def test_many_requests(tmp_path, name, dtype, tol, graphs, pages):
               enable_prefix_caching=None if graphs else False)
     ids = [llm.add_request(p, sp) for p, sp in zip(prompts, params)]
     steps = 0
-    while not llm.scheduler.is_finished():
-        assert llm.step(), "the scheduler made no progress"
+    while not llm.is_finished():
+        assert llm.step() or llm.is_finished(), "the scheduler made no progress"   # the last call only reads tokens back
         steps += 1
         assert steps < 40 * 200, "the requests do not come to an end"
     llm.runner.check_status()

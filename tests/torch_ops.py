@@ -145,9 +145,15 @@ def token_nll(logits, tokens):
     return (torch.logsumexp(x, dim=-1) - x.gather(1, tokens.long()[:, None])[:, 0]).float()
 
 
+def feed_tokens(token_ids, dst_rows, src_rows, src):
+    for d, r in zip(dst_rows.tolist(), src_rows.tolist()):
+        if d >= 0:
+            token_ids[d] = src[r]
+
+
 def launch_count():
     return 0
 
 
 ALL = ["embedding", "rmsnorm", "add", "linear", "gated_linear", "qk_norm_rope_append",
-       "paged_attention", "argmax", "sample", "token_nll", "launch_count"]
+       "paged_attention", "argmax", "sample", "token_nll", "launch_count", "feed_tokens"]

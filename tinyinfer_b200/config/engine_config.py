@@ -20,6 +20,7 @@ class EngineConfig:
     seed: int = 0                           # base of the sampling streams
     eos_token_id: int = -1                  # -1: taken from the model's configuration, if any
     cuda_graphs: bool = True                # replay captured decode steps
+    overlap_steps: bool = True              # launch a step before the tokens of the one before are read back
     track_nll: bool = False                 # sum each request's token NLL (the perplexity statistic)
     enable_prefix_caching: Optional[bool] = None   # keep full pages for later prompts with the same
                                                    # start; None: on where the model allows it

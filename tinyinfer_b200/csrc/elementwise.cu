@@ -39,6 +39,28 @@ TI_API int ti_embedding(void* out, const void* table, const int* ids, int num_to
     return 0;
 }
 
+// ------------------------------------------------------------------ token ids that never visit the host
+// ids[dst_rows[i]] = src[src_rows[i]] for every i with dst_rows[i] >= 0: the tokens a step sampled become the
+// next step's inputs on the device, so the next step can be launched before the host has seen them.
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ dst_rows,
+                                   const int* __restrict__ src_rows, const int* __restrict__ src, int n) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const int d = dst_rows[i];
+        if (d >= 0) ids[d] = src[src_rows[i]];
+    }
+}
+
+TI_API int ti_feed_tokens(int* ids, const int* dst_rows, const int* src_rows, const int* src, int n, cudaStream_t stream) {
+    TI_REQUIRE(n >= 0, "feed_tokens: bad size");
+    if (n == 0) return 0;
+    ti_launch(feed_tokens_kernel, (n + 127) / 128, 128, 0, stream, ids, dst_rows, src_rows, src, n);
+    TI_CHECK_LAUNCH("feed_tokens");
+    return 0;
+}
+
 // ------------------------------------------------------------------ rmsnorm
 // One block per output row. rows == nullptr: output row r is input row r; else input row rows[r].
 // General form: two passes over the row.

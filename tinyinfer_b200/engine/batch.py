@@ -21,6 +21,8 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    feed_row: int = -1       # >= 0: the entry's LAST token is not known on the host yet: it is row feed_row of
+                             # the device tensor of sampled tokens handed to the step (its value here is ignored)
 
 
 @dataclass
@@ -60,6 +62,11 @@ class StepContext:
     num_decode: int = 0
     prefill_tiles: Optional[torch.Tensor] = None
     num_prefill_tiles: int = 0
+    # tokens that come from the device: per entry the flat row of its last token (-1: none) and the row of
+    # the sampled-token tensor that holds it
+    feed_dst: Optional[torch.Tensor] = None
+    feed_src: Optional[torch.Tensor] = None
+    num_feeds: int = 0
     # filled by the runner: entry of the run order -> CacheView
     views: Dict[int, CacheView] = field(default_factory=dict)
 
@@ -77,8 +84,8 @@ class BatchBuffers:
         self.device = torch.device(device)
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
         self.max_blocks, self.num_groups = max_blocks, num_groups
-        words = (3 * max_tokens + 4 * max_seqs + 1 + max_tokens + num_groups * max_seqs * max_blocks
-                 + max_seqs + 4 * (max_tokens // 64 + max_seqs) + 128)   # tiles: at most one per 64 tokens plus one per request
+        words = (3 * max_tokens + 6 * max_seqs + 1 + max_tokens + num_groups * max_seqs * max_blocks
+                 + max_seqs + 4 * (max_tokens // 64 + max_seqs) + 160)   # tiles: at most one per 64 tokens plus one per request
         self.host = torch.empty(words, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self.dev = torch.empty(words, dtype=torch.int32, device=self.device)
         if self.device.type == "cuda":
@@ -130,7 +137,7 @@ class BatchBuffers:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request_id!r}: wanted place {w} is not among its {n} tokens")
                 rows.append(cu[-1] + w)
-            ids.extend(int(x) for x in e.tokens)
+            ids.extend(max(0, int(x)) for x in e.tokens)    # a token yet to come from the device is staged as 0
             pos.extend(range(starts[i], starts[i] + n))
             seq.extend([i] * n)
             cu.append(cu[-1] + n)
@@ -152,6 +159,9 @@ class BatchBuffers:
         from ..ops import plan_attention
         decode_rows, tiles = plan_attention(q_lens, starts)
         put("dec", decode_rows); put("tiles", tiles)
+        feed_dst = [cu[i + 1] - 1 if e.feed_row >= 0 else -1 for i, e in enumerate(entries)]
+        feed_src = [max(0, e.feed_row) for e in entries]
+        put("fdst", feed_dst); put("fsrc", feed_src)
         for g in range(self.num_groups):
             w = widths[g]
             padded: List[int] = []
@@ -181,7 +191,8 @@ class BatchBuffers:
             block_tables=[view(f"bt{g}").view(s, widths[g]) for g in range(self.num_groups)],
             status=self.status, q_lens=q_lens, starts=list(starts), max_q_len=max(q_lens, default=0),
             max_context=max(ctx_lens, default=0), decode_rows=view("dec"), num_decode=len(decode_rows),
-            prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4, num_real_seqs=num_real)
+            prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4, num_real_seqs=num_real,
+            feed_dst=view("fdst"), feed_src=view("fsrc"), num_feeds=sum(1 for d in feed_dst if d >= 0))
         self._last = None
         if fixed_layout and admissions is not None and all(n == 1 for n in q_lens):
             self._last = dict(key=(tuple(admissions), s), ctx=ctx, words=n,
@@ -190,7 +201,8 @@ class BatchBuffers:
         return ctx
 
     def advance_decode(self, admissions: Sequence[int], pad_to: int, tokens: Sequence[int], starts: Sequence[int],
-                       tables: Sequence[Sequence[Sequence[int]]]) -> Optional[StepContext]:
+                       tables: Sequence[Sequence[Sequence[int]]],
+                       feed_rows: Optional[Sequence[int]] = None) -> Optional[StepContext]:
         """The step after a step of single decoded tokens, for the same requests (the same admissions,
         not merely the same ids: a request that ended and whose id came back holds other pages and
         another state slot) in the same order, each with its next token: only the token ids, the positions and the pages that were added
@@ -207,6 +219,13 @@ class BatchBuffers:
         host[off["starts"][0]:off["starts"][0] + n_real] = starts
         ctx_lens = [st + 1 for st in starts]
         host[off["ctx"][0]:off["ctx"][0] + n_real] = ctx_lens
+        if feed_rows is None:
+            host[off["fdst"][0]:off["fdst"][0] + n_real] = -1
+            num_feeds = 0
+        else:                                   # entry i is flat row i of a step of single tokens
+            host[off["fdst"][0]:off["fdst"][0] + n_real] = [i if r >= 0 else -1 for i, r in enumerate(feed_rows)]
+            host[off["fsrc"][0]:off["fsrc"][0] + n_real] = [max(0, r) for r in feed_rows]
+            num_feeds = sum(1 for r in feed_rows if r >= 0)
         for g in range(self.num_groups):
             base, w, lens = off[f"bt{g}"][0], last["widths"][g], last["table_lens"][g]
             for i, tb in enumerate(tables[g]):
@@ -223,6 +242,7 @@ class BatchBuffers:
             self._copied.record()
             self._copy_pending = True
         ctx = last["ctx"]
+        ctx.num_feeds = num_feeds
         ctx.starts = list(starts)
         ctx.max_context = max(ctx_lens)          # padding rows have context 1
         return ctx

@@ -18,7 +18,14 @@ from .batch import StepEntry
 from .loading import build_random_model, load_model, require_cuda
 from .runner import ModelRunner, pages_that_fit
 from .scheduler import Scheduler
-from .sequence import ScheduledItem, Sequence
+from .sequence import PENDING, ScheduledItem, Sequence
+
+
+class _InFlight:
+    """A launched step whose sampled tokens are still on the device."""
+
+    def __init__(self, items, sampling, drawn, row_of):
+        self.items, self.sampling, self.drawn, self.row_of = items, sampling, drawn, row_of
 
 
 class LLM:
@@ -81,6 +88,7 @@ class LLM:
         self.sampler = Sampler(device, self.config.seed)
         self._ids = count()
         self.sequences: Dict[int, Sequence] = {}
+        self._in_flight: Optional[_InFlight] = None      # the step whose tokens have not been read back yet
 
     def close(self) -> None:
         """Gives the device memory back (weights, cache, graphs); the engine cannot be used afterwards."""
@@ -100,26 +108,68 @@ class LLM:
     def step(self) -> List[ScheduledItem]:
         """schedule -> run -> sample -> postprocess; returns what was scheduled. The kernels' status
         words come home with the sampled tokens: a step whose kernels gave up on a wait or met a token
-        without a page raises KernelError instead of handing on tokens drawn from its logits."""
-        items = self.scheduler.schedule()
-        if not items:
-            return items
-        entries = [StepEntry(it.seq.seq_id,
-                             it.seq.token_ids[it.start_pos:it.start_pos + it.num_tokens],
-                             [it.num_tokens - 1] if it.sample_after else [])
-                   for it in items]
-        logits = self.runner.step(entries)
+        without a page raises KernelError instead of handing on tokens drawn from its logits.
+
+        With ``overlap_steps`` (the default) a call launches a step and only then reads back the tokens of
+        the step the call before launched: the host schedules and stages step n + 1 while the device runs
+        step n, and the tokens that step n + 1 needs from step n reach it on the device. What depends on
+        counts alone (how far a request is, whether it has reached its token limit) is settled when a step
+        is launched; what depends on the token (end of sequence, the prefix cache's page hashes, timing
+        marks) when it has been read back, one call later. A request that ends on an end-of-sequence token
+        has then already run in the next step; that step's token for it is dropped. Call ``step`` until
+        ``is_finished()``: the last call launches nothing and reads the last tokens back."""
+        before = self._in_flight
+        if before is None:
+            items = self.scheduler.schedule()
+        else:
+            items = self.scheduler.schedule_ahead()
+            if not items:
+                # nothing fits as things stand: read the step in flight back first, then schedule with
+                # everything known (making room, if need be, changes requests; none may be waiting for a token)
+                self._in_flight = None
+                self._retire(before)
+                before = None
+                items = self.scheduler.schedule()
+        launched = self._launch(items, before) if items else None
+        if launched is not None and not self.config.overlap_steps:
+            self._retire(launched)
+            launched = None
+        self._in_flight = launched
+        if before is not None:
+            self._retire(before)
+        return items
+
+    def is_finished(self) -> bool:
+        """No request waits, runs, or has a token on its way back."""
+        return self._in_flight is None and self.scheduler.is_finished()
+
+    def _launch(self, items: List[ScheduledItem], before) -> "_InFlight":
+        entries = []
+        for it in items:
+            tokens = it.seq.token_ids[it.start_pos:it.start_pos + it.num_tokens]
+            feed_row = -1
+            if tokens[-1] == PENDING:          # sampled by the step in flight: it stays on the device
+                feed_row = before.row_of[it.seq.seq_id]
+                tokens = tokens[:-1] + [0]
+            entries.append(StepEntry(it.seq.seq_id, tokens, [it.num_tokens - 1] if it.sample_after else [], feed_row))
+        fed = before.drawn.tokens if before is not None else None
+        logits = self.runner.step(entries, fed_tokens=fed)
         sampling = [it for it in items if it.sample_after]
-        tokens = self.sampler.sample(
+        drawn = self.sampler.sample_async(
             logits, [it.seq.sampling_params for it in sampling],
             [it.seq.seq_id for it in sampling], [it.seq.num_completion_tokens for it in sampling],
             with_nll=self.config.track_nll, status=self.runner.status_words())
+        self.scheduler.advance(items)
+        return _InFlight(items, sampling, drawn, {it.seq.seq_id: row for row, it in enumerate(sampling)})
+
+    def _retire(self, flight: "_InFlight") -> None:
+        tokens = flight.drawn.result()
         if self.config.track_nll:
             tokens, nlls = tokens
-            for it, nll in zip(sampling, nlls):
-                it.seq.sum_nll += nll
-        self.scheduler.postprocess(items, {it.seq.seq_id: tok for it, tok in zip(sampling, tokens)})
-        return items
+            for it, nll in zip(flight.sampling, nlls):
+                if not it.seq.is_finished:
+                    it.seq.sum_nll += nll
+        self.scheduler.retire(flight.items, {it.seq.seq_id: tok for it, tok in zip(flight.sampling, tokens)})
 
     # ------------------------------------------------------------------ generation
     def generate_token_ids(self, prompts: Seq[Seq[int]],
@@ -131,8 +181,8 @@ class LLM:
         if len(params) != len(prompts):
             raise ValueError("prompts and sampling params length mismatch")
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
-        while not self.scheduler.is_finished():
-            if not self.step() and not self.scheduler.is_finished():
+        while not self.is_finished():
+            if not self.step() and not self.is_finished():
                 raise RuntimeError("scheduler made no progress while requests remain")
         out = []
         for i in ids:

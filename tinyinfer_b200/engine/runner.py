@@ -57,11 +57,13 @@ class ModelRunner:
         return self.manager.get(request_id).length
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], fed_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the entries' tokens and returns float32 logits [N, V] on the device, N being the
         number of wanted places, in the order of the entries and of each ``want``.
         A request id not seen before is admitted. Raises CacheExhausted before anything runs
-        if the pages do not suffice for ALL entries; the cache is then as it was before the call."""
+        if the pages do not suffice for ALL entries; the cache is then as it was before the call.
+        ``fed_tokens``: int32 device tensor of tokens sampled by the step before; an entry with
+        ``feed_row >= 0`` takes its last token from there, on the device (the host need not have seen it)."""
         entries = [e for e in entries if len(e.tokens) > 0]
         ids = [e.request_id for e in entries]
         if len(set(ids)) != len(ids):
@@ -75,9 +77,12 @@ class ModelRunner:
             if start + len(e.tokens) > self.max_model_len:
                 raise ValueError(f"request {e.request_id!r} would reach {start + len(e.tokens)} tokens, "
                                  f"the limit is {self.max_model_len}")
-            for tok in e.tokens:
+            known = e.tokens if e.feed_row < 0 else e.tokens[:-1]
+            for tok in known:
                 if not 0 <= int(tok) < vocab:
                     raise ValueError(f"token id {tok} is outside the vocabulary of {vocab}")
+            if e.feed_row >= 0 and fed_tokens is None:
+                raise ValueError(f"request {e.request_id!r} takes a token from the device, but none were handed over")
             starts.append(start)
         admitted_here = [rid for rid in ids if rid not in self.manager]
         try:
@@ -104,12 +109,16 @@ class ModelRunner:
         ctx = None
         if decode_only and self._tables_only_grow:
             # the same requests as in the step before, one more token each: patch the staged arrays
-            ctx = self.buffers.advance_decode(serials, pad_to, [int(e.tokens[0]) for e in entries], starts, tables)
+            ctx = self.buffers.advance_decode(serials, pad_to, [max(0, int(e.tokens[0])) for e in entries], starts, tables,
+                                              [e.feed_row for e in entries] if fed_tokens is not None else None)
         if ctx is None:
             ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables,
                                      fixed_layout=decode_only, pad_to=pad_to, admissions=serials,
                                      pad_pages=[CacheStorage.dump_page(self.manager, g) for g in range(num_groups)])
             self._bind_views(ctx)
+        if ctx.num_feeds:
+            from .. import ops
+            ops.feed_tokens(ctx.token_ids, ctx.feed_dst, ctx.feed_src, fed_tokens)
         logits = self._graph_forward(ctx) if decode_only else self.model.forward(ctx)
         for e, start in zip(entries, starts):
             self.manager.commit(e.request_id, start + len(e.tokens))

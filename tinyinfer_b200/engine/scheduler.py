@@ -38,6 +38,7 @@ class Scheduler:
         self.manager = manager
         self.waiting: Deque[Sequence] = deque()
         self.running: Deque[Sequence] = deque()
+        self.retiring: List[Sequence] = []         # their last token is still on its way to the host
         self.num_preemptions = 0
         self.finished_early: List[Sequence] = []   # ended by the scheduler, not by a token
 
@@ -54,7 +55,7 @@ class Scheduler:
         self.waiting.append(seq)
 
     def is_finished(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and not self.retiring
 
     # ------------------------------------------------------------------ schedule
     def schedule(self) -> List[ScheduledItem]:
@@ -165,7 +166,70 @@ class Scheduler:
             self.manager.release(seq.seq_id)
             seq.admitted = False
 
+    def schedule_ahead(self) -> List[ScheduledItem]:
+        """The next step's items while a step is still in flight: what can be scheduled as things stand,
+        without making room (preemption changes requests whose last token is not known yet)."""
+        return self._schedule_once()
+
     # ------------------------------------------------------------------ after the step
+    def advance(self, items: List[ScheduledItem]) -> None:
+        """The first half of ``postprocess``, at the moment a step is LAUNCHED: everything that follows
+        from counts alone. Every scheduled request moves on by its tokens; one that gets a token from this
+        step gets a place for it (``PENDING``); a request that reaches its token or length limit with that
+        token leaves the queues now (it is not scheduled again) and waits in ``retiring`` for ``retire``."""
+        for item in items:
+            seq = item.seq
+            seq.num_computed_tokens = item.start_pos + item.num_tokens
+            if not item.sample_after:
+                continue
+            last = seq.append_pending()
+            reason = seq.length_stop(self.max_model_len)
+            if reason is not None:
+                seq.stopping = (last, reason)               # it ends when the token of this place is known
+                if seq in self.running:
+                    self.running.remove(seq)
+                if seq in self.waiting:
+                    self.waiting.remove(seq)
+                self.retiring.append(seq)
+            elif item.is_prefill:
+                self.waiting.remove(seq)
+                seq.status = SequenceStatus.RUNNING
+                self.running.append(seq)
+
+    def retire(self, items: List[ScheduledItem], sampled: Dict[int, int]) -> List[Sequence]:
+        """The second half, when the step's tokens have been read back: they take their places, the
+        end-of-sequence token is looked for, full pages join the prefix cache, finished requests give
+        their pages back. A request that ended while a later step with it was already in flight is
+        skipped here when that step retires. Returns the requests that finished."""
+        finished: List[Sequence] = []
+        for item in items:
+            seq = item.seq
+            if seq.is_finished:
+                continue                                    # ended by an earlier step's token
+            if item.sample_after:
+                position = item.start_pos + item.num_tokens
+                token = sampled[seq.seq_id]
+                seq.resolve(position, token)
+                reason = seq.token_stop(self.eos_token_id, token)
+                if seq.stopping is not None and seq.stopping[0] == position:
+                    reason = seq.stopping[1]
+                if reason is not None:
+                    del seq.token_ids[position + 1:]        # a place made for a token of a later step in flight
+                    seq.num_computed_tokens = min(seq.num_computed_tokens, position)
+                    seq.mark_finished(reason)
+                    finished.append(seq)
+            if seq.seq_id in self.manager:
+                # full pages join the prefix cache, once every token whose key is stored is known (only
+                # the newest two places can still be waiting)
+                stored = self.manager.get(seq.seq_id).length
+                if all(t >= 0 for t in seq.token_ids[max(0, stored - 2):stored]):
+                    self.manager.note_tokens(seq.seq_id, seq.token_ids)
+        for seq in finished:
+            if seq in self.retiring:
+                self.retiring.remove(seq)
+            self._drop(seq)
+        return finished
+
     def postprocess(self, items: List[ScheduledItem], sampled: Dict[int, int]) -> List[Sequence]:
         """Advances every scheduled request, appends sampled tokens, moves finished prompts to
         the running queue, finishes and frees. Returns the requests that finished."""

@@ -18,6 +18,9 @@ class SequenceStatus(Enum):
     FINISHED = auto()
 
 
+PENDING = -1      # stands in token_ids for a token that has been sampled on the device but not read back yet
+
+
 class Sequence:
     def __init__(self, seq_id: int, token_ids: List[int], sampling_params: SamplingParams):
         if not token_ids:
@@ -32,6 +35,7 @@ class Sequence:
         self.num_cached_tokens = 0                          # prompt tokens found in a prefix cache
         self.num_preemptions = 0
         self.finish_reason: Optional[str] = None
+        self.stopping = None           # (position, reason): it ends once the token of that place has been read back
         self.admitted = False
         self.sum_nll = 0.0
         self.arrival_time = time.perf_counter()
@@ -71,6 +75,21 @@ class Sequence:
 
     def append_token(self, token: int) -> None:
         self.token_ids.append(int(token))
+        self._stamp_token()
+
+    def append_pending(self) -> int:
+        """Makes room for a token that a step in flight is sampling; returns its position."""
+        self.token_ids.append(PENDING)
+        return len(self.token_ids) - 1
+
+    def resolve(self, position: int, token: int) -> None:
+        """The token that was pending at ``position`` has been read back."""
+        if self.token_ids[position] != PENDING:
+            raise RuntimeError(f"request {self.seq_id}: position {position} was not waiting for a token")
+        self.token_ids[position] = int(token)
+        self._stamp_token()
+
+    def _stamp_token(self) -> None:
         now = time.perf_counter()
         if self.first_token_time is None:
             self.first_token_time = now
@@ -84,12 +103,19 @@ class Sequence:
     def stop_reason(self, eos_token_id: int, max_model_len: int) -> Optional[str]:
         """Why generation ends now, or None (tinyinfer/engine/sequence.py:152-170; the end-of-
         sequence token stays in the output)."""
+        return self.length_stop(max_model_len) or self.token_stop(eos_token_id, self.last_token)
+
+    def length_stop(self, max_model_len: int) -> Optional[str]:
+        """The reasons to end that depend on counts alone: known before the last token is."""
         if self.num_completion_tokens >= self.sampling_params.max_tokens:
             return "max_tokens"
         if self.num_tokens >= max_model_len:
             return "max_model_len"
+        return None
+
+    def token_stop(self, eos_token_id: int, token: int) -> Optional[str]:
         if (not self.sampling_params.ignore_eos and eos_token_id >= 0
-                and self.num_completion_tokens > 0 and self.last_token == eos_token_id):
+                and self.num_completion_tokens > 0 and token == eos_token_id):
             return "eos"
         return None
 

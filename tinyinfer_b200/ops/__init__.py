@@ -27,6 +27,7 @@ class KernelError(RuntimeError):
 _SIGNATURES = {
     "core": {
         "ti_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "ti_feed_tokens": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "ti_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
         "ti_add": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p],
         "ti_qk_norm_rope_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
@@ -196,6 +197,19 @@ def embedding(token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     _run("core", "ti_embedding", out.data_ptr(), table.data_ptr(), token_ids.data_ptr(),
          token_ids.shape[0], table.shape[1], table.shape[0], _dtype_code(table), _stream())
     return out
+
+
+def feed_tokens(token_ids: torch.Tensor, dst_rows: torch.Tensor, src_rows: torch.Tensor, src: torch.Tensor) -> None:
+    """token_ids[dst_rows[i]] = src[src_rows[i]] wherever dst_rows[i] >= 0 (all int32, on the device): tokens
+    that a step sampled become inputs of the next step without a trip to the host."""
+    _check(token_ids, "token_ids", torch.int32, 1)
+    _check(dst_rows, "dst_rows", torch.int32, 1)
+    _check(src_rows, "src_rows", torch.int32, 1)
+    _check(src, "src", torch.int32, 1)
+    if src_rows.shape[0] != dst_rows.shape[0]:
+        raise KernelError("feed_tokens: one source row per destination row")
+    _run("core", "ti_feed_tokens", token_ids.data_ptr(), dst_rows.data_ptr(), src_rows.data_ptr(), src.data_ptr(),
+         dst_rows.shape[0], _stream())
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
