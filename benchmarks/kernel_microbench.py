@@ -121,13 +121,14 @@ def main():
         pos = torch.tensor([p for n, ql in zip(lens, q_lens) for p in range(n - ql, n)], dtype=torch.int32, device=dev)
         seq = torch.tensor([s for s, ql in enumerate(q_lens) for _ in range(ql)], dtype=torch.int32, device=dev)
         q = torch.randn(pos.shape[0], hq, d, device=dev).bfloat16()
-        rows_l, tiles_l = ops.plan_attention(q_lens, [n - ql for n, ql in zip(lens, q_lens)])
+        rows_l, tiles_l, pair_tiles = ops.plan_attention(q_lens, [n - ql for n, ql in zip(lens, q_lens)])
 
         class Step:
             decode_rows = torch.tensor(rows_l or [0], dtype=torch.int32, device=dev)
             num_decode = len(rows_l)
             prefill_tiles = torch.tensor(tiles_l or [0, 0, 0, 0], dtype=torch.int32, device=dev)
             num_prefill_tiles = len(tiles_l) // 4
+            num_pair_tiles = pair_tiles
             max_context = max(lens)
         i = [0]
 

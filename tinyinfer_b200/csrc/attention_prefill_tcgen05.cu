@@ -103,9 +103,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const uint32_t tmem_base = tmem_base_sh;
     ti_grid_wait();                                     // q, the pages and the tables come from earlier kernels
 
-    const int4 td = reinterpret_cast<const int4*>(p.tiles)[blockIdx.x];
+    // heads along x, tiles (longest key range first) along y: CTAs are handed out x first, so every head of
+    // the longest tile starts before any shorter tile does
+    const int4 td = reinterpret_cast<const int4*>(p.tiles)[blockIdx.y];
     const int seq = td.x, row0 = td.y, nrows = td.z, pos0 = td.w;
-    const int head = blockIdx.y;
+    const int head = blockIdx.x;
     const int kvh = head / (p.hq / p.hkv);
     const int hi = pos0 + nrows;                                   // one past the last key any query sees
     const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0; // first key the first query sees
@@ -361,7 +363,8 @@ TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv
                                         int page_size, int num_pages, float scale, int window, int* status,
                                         cudaStream_t stream) {
     TI_REQUIRE(d == 64 || d == 128, "attention_prefill_tc: head_dim %d is not 64 or 128", d);
-    TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0 && hq <= 65535, "attention_prefill_tc: bad head counts");
+    TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_tc: bad head counts");
+    TI_REQUIRE(num_tiles <= 65535, "attention_prefill_tc: more than 65535 tiles in one step");
     TI_REQUIRE(page_size == 16 || page_size == 32 || page_size % 64 == 0, "attention_prefill_tc: page size %d", page_size);
     TI_REQUIRE(num_tiles >= 0 && num_tokens > 0, "attention_prefill_tc: bad sizes");
     if (num_tiles == 0) return 0;
@@ -372,7 +375,7 @@ TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
     p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    dim3 grid(num_tiles, hq);
+    dim3 grid(hq, num_tiles);
     if (d == 128) {
         static bool once = false;
         if (!once) {

@@ -62,6 +62,7 @@ class StepContext:
     num_decode: int = 0
     prefill_tiles: Optional[torch.Tensor] = None
     num_prefill_tiles: int = 0
+    num_pair_tiles: int = 0        # the first so many tiles have more than 128 rows (two query tiles a CTA)
     # tokens that come from the device: per entry the flat row of its last token (-1: none) and the row of
     # the sampled-token tensor that holds it
     feed_dst: Optional[torch.Tensor] = None
@@ -157,7 +158,7 @@ class BatchBuffers:
         put("ids", ids); put("pos", pos); put("seq", seq); put("cu", cu)
         put("starts", list(starts)); put("ctx", ctx_lens); put("slots", list(slots)); put("rows", rows)
         from ..ops import plan_attention
-        decode_rows, tiles = plan_attention(q_lens, starts)
+        decode_rows, tiles, num_pairs = plan_attention(q_lens, starts)
         put("dec", decode_rows); put("tiles", tiles)
         feed_dst = [cu[i + 1] - 1 if e.feed_row >= 0 else -1 for i, e in enumerate(entries)]
         feed_src = [max(0, e.feed_row) for e in entries]
@@ -191,7 +192,8 @@ class BatchBuffers:
             block_tables=[view(f"bt{g}").view(s, widths[g]) for g in range(self.num_groups)],
             status=self.status, q_lens=q_lens, starts=list(starts), max_q_len=max(q_lens, default=0),
             max_context=max(ctx_lens, default=0), decode_rows=view("dec"), num_decode=len(decode_rows),
-            prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4, num_real_seqs=num_real,
+            prefill_tiles=view("tiles"), num_prefill_tiles=len(tiles) // 4, num_pair_tiles=num_pairs,
+            num_real_seqs=num_real,
             feed_dst=view("fdst"), feed_src=view("fsrc"), num_feeds=sum(1 for d in feed_dst if d >= 0))
         self._last = None
         if fixed_layout and admissions is not None and all(n == 1 for n in q_lens):

@@ -59,8 +59,9 @@ _SIGNATURES["sm100"]["ti_attention_decode_plan"] = [c_int, c_int, c_int, c_int, 
 _SIGNATURES["sm100"]["ti_attention_prefill_tc_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
     c_float, c_int, c_void_p, c_void_p]
+_SIGNATURES["sm100"]["ti_attention_prefill_pair_bf16"] = _SIGNATURES["sm100"]["ti_attention_prefill_tc_bf16"]
 DECODE_CHUNK = 256        # fewest keys per split of the decode attention kernel (see decode_chunk)
-PREFILL_TILE = 128        # query rows per CTA of the prefill attention kernel
+PREFILL_TILE = 256        # most query rows per CTA of the prefill attention kernels (two tiles of 128)
 _bound = {}
 _status = {}
 
@@ -426,20 +427,28 @@ def qk_norm_rope_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int,
 
 def plan_attention(q_lens, starts):
     """Splits a step's entries into single decoded tokens and portions of prompts.
-    Returns (decode_rows, tiles): flat rows of entries that bring one token, and for the others
-    tiles [entry, first flat row, rows, first position] of at most PREFILL_TILE query rows,
-    longest key range first."""
-    decode_rows, tiles = [], []
+    Returns (decode_rows, tiles, num_pair_tiles): flat rows of entries that bring one token, and for the
+    others tiles [entry, first flat row, rows, first position]. A portion is cut into tiles of
+    PREFILL_TILE = 256 query rows for the kernel that runs two query tiles a CTA; what is left at its end,
+    if it is at most 128 rows, is a tile for the kernel with one. The first ``num_pair_tiles`` tiles are
+    the former, the rest the latter; each kind longest key range first."""
+    decode_rows, pairs, singles = [], [], []
     row = 0
     for i, (n, start) in enumerate(zip(q_lens, starts)):
         if n == 1:
             decode_rows.append(row)
         else:
-            for off in range(0, n, PREFILL_TILE):
-                tiles.append((i, row + off, min(PREFILL_TILE, n - off), start + off))
+            off = 0
+            while n - off > PREFILL_TILE // 2:
+                rows = min(PREFILL_TILE, n - off)
+                pairs.append((i, row + off, rows, start + off))
+                off += rows
+            if off < n:
+                singles.append((i, row + off, n - off, start + off))
         row += n
-    tiles.sort(key=lambda t: -(t[3] + t[2]))
-    return decode_rows, [x for t in tiles for x in t]
+    pairs.sort(key=lambda t: -(t[3] + t[2]))
+    singles.sort(key=lambda t: -(t[3] + t[2]))
+    return decode_rows, [x for t in pairs + singles for x in t], len(pairs)
 
 
 def attention_tensor_cores_ok(q: torch.Tensor, kv_cache: torch.Tensor) -> bool:
@@ -543,6 +552,7 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
     if step is not None:
         decode_rows, num_decode = step.decode_rows, step.num_decode
         tiles, num_tiles, max_context = step.prefill_tiles, step.num_prefill_tiles, step.max_context
+        num_pairs = step.num_pair_tiles
     else:
         pos_h, seq_h = positions.tolist(), token_seq.tolist()
         q_lens, starts = [], []
@@ -553,7 +563,7 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
                 q_lens.append(1)
                 starts.append(p_)
         # entries here are runs of consecutive positions; their request index comes from token_seq
-        rows_l, tiles_l = plan_attention(q_lens, starts)
+        rows_l, tiles_l, num_pairs = plan_attention(q_lens, starts)
         firsts, r = [], 0
         for n in q_lens:
             firsts.append(seq_h[r])
@@ -573,10 +583,14 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
              scratch.data_ptr(), part_ml, decode_rows.data_ptr(), num_decode, positions.data_ptr(),
              token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), chunk, splits, kstatus, _stream())
-    if num_tiles:
-        _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
-             tiles.data_ptr(), num_tiles, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
+    if num_pairs:                                   # two query tiles a CTA
+        _run("sm100", "ti_attention_prefill_pair_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+             tiles.data_ptr(), num_pairs, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), kstatus, _stream())
+    if num_tiles > num_pairs:                       # ends of portions of at most 128 rows: one query tile a CTA
+        _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+             tiles.data_ptr() + 16 * num_pairs, num_tiles - num_pairs, t, block_table.data_ptr(), block_table.shape[1],
+             hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), kstatus, _stream())
     return out
 
 
