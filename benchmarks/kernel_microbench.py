@@ -77,8 +77,12 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--pair-min-ctas", type=int, default=None,
+                    help="attention_prefill: fewest CTAs for which the two-tile kernel runs (default: the product's)")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
+    if a.pair_min_ctas is not None:
+        ops.PAIR_MIN_CTAS = a.pair_min_ctas
     hbm, tflops, source = peaks()
     torch.manual_seed(0)
     out = {"kernel": a.kernel, "peaks": source}

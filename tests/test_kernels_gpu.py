@@ -360,12 +360,21 @@ ATTN_SHAPES = [
     (8, 2, 128, 128, 300, [(1000, 1), (900, 130), (299, 1), (300, 1), (301, 1)]),
     (4, 4, 64, 64, 70, [(500, 200), (129, 2), (64, 64), (1, 1)]),
     (12, 3, 128, 64, None, [(450, 61), (63, 63), (2, 2), (1100, 17)]),
+    # portions of several tiles of 256 rows behind a prefix, their ends of 129 and 128 rows and less
+    (8, 2, 128, 64, None, [(1300, 897), (700, 513), (640, 384), (1, 1)]),
+    (4, 2, 64, 32, 200, [(1500, 1000), (420, 385)]),
 ]
 
 
+@pytest.mark.parametrize("pair_min_ctas", [0, 1 << 30])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hkv,d,page,window,work", ATTN_SHAPES)
-def test_paged_attention(ops, dtype, hq, hkv, d, page, window, work):
+def test_paged_attention(ops, monkeypatch, dtype, hq, hkv, d, page, window, work, pair_min_ctas):
+    """pair_min_ctas: 0 sends every tile of more than 128 rows to the kernel with two query tiles a CTA,
+    the large value sends its halves to the kernel with one (what the product does with few tiles)."""
+    if pair_min_ctas and (dtype != torch.bfloat16 or d not in (64, 128)):
+        pytest.skip("one path only")
+    monkeypatch.setattr(ops, "PAIR_MIN_CTAS", pair_min_ctas)
     lens = [c for c, _ in work]
     bt, kv = paged_setup(dtype, lens, hq, hkv, d, page, seed=1)
     fill_cache(kv, bt, lens, hkv, d, page, dtype)

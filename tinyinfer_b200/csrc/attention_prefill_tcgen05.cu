@@ -31,6 +31,7 @@ struct PrefillParams {
     const int* tiles;                // int4 {request index, first flat row, rows (<= 128), first position}
     const int* block_table;
     int max_blocks, hq, hkv, page_size, num_pages, window;
+    int halves;                      // 1: a tile entry has up to 256 rows and two CTAs take 128 each
     float scale_log2;
     int* status;
 };
@@ -105,8 +106,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 
     // heads along x, tiles (longest key range first) along y: CTAs are handed out x first, so every head of
     // the longest tile starts before any shorter tile does
-    const int4 td = reinterpret_cast<const int4*>(p.tiles)[blockIdx.y];
-    const int seq = td.x, row0 = td.y, nrows = td.z, pos0 = td.w;
+    const int4 td = reinterpret_cast<const int4*>(p.tiles)[p.halves ? blockIdx.y >> 1 : blockIdx.y];
+    const int half_off = p.halves ? (blockIdx.y & 1) * QM : 0;
+    const int seq = td.x, row0 = td.y + half_off, pos0 = td.w + half_off;
+    const int nrows = min(td.z - half_off, QM);
     const int head = blockIdx.x;
     const int kvh = head / (p.hq / p.hkv);
     const int hi = pos0 + nrows;                                   // one past the last key any query sees
@@ -115,7 +118,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int num_tiles = tile1 - tile0;
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
 
-    if (warp == 0) {
+    if (nrows <= 0) {
+        // the second half of an entry of at most 128 rows: nothing to do but the common exit
+    } else if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         // A tile is KT / piece_rows pieces (a piece lies in one page) x head halves x (keys, values): up to
         // 32 copies. Each lane issues one of them, so that a tile is on its way in one round instead of
@@ -358,13 +363,15 @@ TI_API int ti_attention_prefill_tile_rows() { return QM; }
 // Prefill attention on tcgen05. `tiles`: num_tiles int4 {request index in the step, first flat row,
 // rows (<= 128), position of the first row}, every tile inside one request's portion. q [T, Hq, D],
 // out [T, Hq * D], kv_cache [2, num_pages, Hkv, page_size, D]; page_size 16, 32 or a multiple of 64.
+// With `halves` a tile entry has up to 256 rows (the form the two-tile kernel takes) and two CTAs take
+// 128 rows each: for steps whose entries are too few to fill the machine with one CTA each.
 TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
                                         int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
-                                        int page_size, int num_pages, float scale, int window, int* status,
+                                        int page_size, int num_pages, float scale, int window, int halves, int* status,
                                         cudaStream_t stream) {
     TI_REQUIRE(d == 64 || d == 128, "attention_prefill_tc: head_dim %d is not 64 or 128", d);
     TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_tc: bad head counts");
-    TI_REQUIRE(num_tiles <= 65535, "attention_prefill_tc: more than 65535 tiles in one step");
+    TI_REQUIRE(num_tiles <= 32767, "attention_prefill_tc: more than 32767 tiles in one step");
     TI_REQUIRE(page_size == 16 || page_size == 32 || page_size % 64 == 0, "attention_prefill_tc: page size %d", page_size);
     TI_REQUIRE(num_tiles >= 0 && num_tokens > 0, "attention_prefill_tc: bad sizes");
     if (num_tiles == 0) return 0;
@@ -374,8 +381,8 @@ TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv
     PrefillParams p;
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
     p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
-    p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    dim3 grid(hq, num_tiles);
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.halves = halves ? 1 : 0;
+    dim3 grid(hq, halves ? 2 * num_tiles : num_tiles);
     if (d == 128) {
         static bool once = false;
         if (!once) {

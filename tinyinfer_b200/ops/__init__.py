@@ -56,12 +56,15 @@ _SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_decode_plan"] = [c_int, c_int, c_int, c_int, c_int, c_int]
-_SIGNATURES["sm100"]["ti_attention_prefill_tc_bf16"] = [
+_SIGNATURES["sm100"]["ti_attention_prefill_pair_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
     c_float, c_int, c_void_p, c_void_p]
-_SIGNATURES["sm100"]["ti_attention_prefill_pair_bf16"] = _SIGNATURES["sm100"]["ti_attention_prefill_tc_bf16"]
+_SIGNATURES["sm100"]["ti_attention_prefill_tc_bf16"] = [
+    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+    c_float, c_int, c_int, c_void_p, c_void_p]
 DECODE_CHUNK = 256        # fewest keys per split of the decode attention kernel (see decode_chunk)
 PREFILL_TILE = 256        # most query rows per CTA of the prefill attention kernels (two tiles of 128)
+PAIR_MIN_CTAS = 148       # fewer CTAs than this of the two-tile kernel: its tiles run as halves, one a CTA
 _bound = {}
 _status = {}
 
@@ -583,14 +586,18 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
              scratch.data_ptr(), part_ml, decode_rows.data_ptr(), num_decode, positions.data_ptr(),
              token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), chunk, splits, kstatus, _stream())
-    if num_pairs:                                   # two query tiles a CTA
+    if num_pairs * hq >= PAIR_MIN_CTAS:             # two query tiles a CTA
         _run("sm100", "ti_attention_prefill_pair_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              tiles.data_ptr(), num_pairs, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), kstatus, _stream())
-    if num_tiles > num_pairs:                       # ends of portions of at most 128 rows: one query tile a CTA
+    elif num_pairs:                                 # too few of them to fill the machine: one query tile a CTA
+        _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+             tiles.data_ptr(), num_pairs, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
+             num_pages, float(scale), int(window or 0), 1, kstatus, _stream())
+    if num_tiles > num_pairs:                       # ends of portions of at most 128 rows
         _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              tiles.data_ptr() + 16 * num_pairs, num_tiles - num_pairs, t, block_table.data_ptr(), block_table.shape[1],
-             hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), kstatus, _stream())
+             hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), 0, kstatus, _stream())
     return out
 
 
