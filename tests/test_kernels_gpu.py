@@ -297,10 +297,10 @@ def test_a_position_beyond_the_block_table_is_a_token_without_a_page(ops):
         close(out[1], torch.full_like(out[1], 0.25), dtype)
 
 
-def test_decode_attention_with_too_few_splits_says_so(ops):
-    """The exported decode entry point takes the number of splits from its caller. One too few: the
-    status word says so (23) and the merge reads only partials that belong to its own row."""
-    import ctypes
+def test_decode_attention_scratch_is_checked_and_fully_written(ops):
+    """The exported decode entry point takes its scratch from the caller: with as many floats as the library
+    asks for, every word the merge reads has been written (the scratch starts as NaN); with one float less
+    the call is refused with a message and nothing runs."""
     from tinyinfer_b200.ops import library
     hq, hkv, d, page = 8, 2, 128, 64
     lens = [700, 300]
@@ -314,20 +314,23 @@ def test_decode_attention_with_too_few_splits_says_so(ops):
     fn = ops._fn("sm100", "ti_attention_decode_bf16")
     status = torch.zeros(1, dtype=torch.int32, device=dev())
     want = ref.paged_attention(q, kv, positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5)
-    for splits, code in ((3, 0), (2, 23)):
-        scratch = torch.full((2 * hq * splits * (d + 2),), float("nan"), dtype=torch.float32, device=dev())
+    need = ops.decode_scratch_floats(2, hq, hkv, d, max(lens), 0)
+    assert 0 < need < 1 << 20
+    for given, fine in ((need, True), (need - 1, False)):
+        scratch = torch.full((need,), float("nan"), dtype=torch.float32, device=dev())
         out = torch.zeros((2, hq * d), dtype=dtype, device=dev())
-        rc = fn(out.data_ptr(), q.data_ptr(), kv.data_ptr(), scratch.data_ptr(),
-                scratch.data_ptr() + 4 * 2 * hq * splits * d, rows.data_ptr(), 2, pos.data_ptr(), seq.data_ptr(),
-                bt.data_ptr(), bt.shape[1], hq, hkv, d, page, kv.shape[1], d ** -0.5, 0, 256, splits,
-                status.data_ptr(), torch.cuda.current_stream().cuda_stream)
-        assert rc == 0, library.load("sm100").ti_last_error().decode()
-        assert int(status.item()) == code
-        assert torch.isfinite(out.float()).all()
-        close(out[1], want[1], dtype)                     # the short request is whole either way
-        if code == 0:
-            close(out[0], want[0], dtype)
-        status.zero_()
+        rc = fn(out.data_ptr(), q.data_ptr(), kv.data_ptr(), scratch.data_ptr(), given, rows.data_ptr(), 2,
+                pos.data_ptr(), seq.data_ptr(), bt.data_ptr(), bt.shape[1], hq, hkv, d, page, kv.shape[1], d ** -0.5,
+                0, max(lens), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        message = library.load("sm100").ti_last_error().decode()
+        assert int(status.item()) == 0
+        if fine:
+            assert rc == 0, message
+            assert torch.isfinite(out.float()).all()
+            close(out, want, dtype)
+        else:
+            assert rc != 0 and "floats of scratch" in message
+            assert not out.any()
 
 
 def fill_cache(kv, bt, lens, hkv, d, page, dtype, seed=0):
@@ -390,21 +393,18 @@ def test_paged_attention(ops, monkeypatch, dtype, hq, hkv, d, page, window, work
     close(out, want, dtype)
 
 
-@pytest.mark.parametrize("hq,hkv,d,page,window,lens,chunk", [
-    (32, 8, 128, 64, None, [4096, 3000, 1, 257, 513, 4000, 2048, 1025], 512),
-    (8, 8, 64, 16, None, [9000, 8193, 700, 8192], None),
-    (8, 4, 128, 128, 2500, [6000, 2501, 2500, 5121, 40, 4608, 3000, 5632, 5633, 6000, 2600, 4097, 777, 5120], -1024)])
-def test_decode_attention_with_larger_splits(ops, monkeypatch, hq, hkv, d, page, window, lens, chunk):
-    """Many long contexts are cut into splits of 512 keys and more: the same results, at the edges of the
-    larger splits too (a context that ends on one, one key past it, a window that starts inside one).
-    chunk: what the plan is expected to say; None: anything above 256; negative: forced here (a window
-    keeps the visible keys few, so the plan would not choose it)."""
+@pytest.mark.parametrize("hq,hkv,d,page,window,lens", [
+    (32, 8, 128, 64, None, [4096, 3000, 1, 257, 513, 4000, 2048, 1025]),
+    (8, 8, 64, 16, None, [9000, 8193, 700, 8192]),
+    (8, 4, 128, 128, 2500, [6000, 2501, 2500, 5121, 40, 4608, 3000, 5632, 5633, 6000, 2600, 4097, 777, 5120]),
+    # many short requests: a CTA's run of four key tiles crosses kv heads and requests
+    (6, 3, 128, 32, None, [1, 64, 65, 130, 7, 200, 63, 129, 2, 300, 64, 64, 1, 191, 192, 193] * 3),
+    (4, 1, 64, 16, 100, [1, 99, 100, 101, 164, 165, 230, 700, 3, 64] * 7)])
+def test_decode_attention_shares_the_keys_out_evenly(ops, hq, hkv, d, page, window, lens):
+    """Long contexts are cut where a CTA's run ends, not at fixed positions, and short ones share a CTA: the
+    same results wherever the cuts fall (inside a request, at its last key, across kv heads and requests, a
+    window that starts inside a run)."""
     dtype = torch.bfloat16
-    key = (len(lens), hq, hkv, d, max(lens), window or 0)
-    if chunk is not None and chunk < 0:
-        monkeypatch.setitem(ops._decode_chunks, key, -chunk)
-    planned = ops.decode_chunk(*key)
-    assert planned > 256 and planned % 256 == 0 and (chunk is None or planned == abs(chunk))
     bt, kv = paged_setup(dtype, lens, hq, hkv, d, page, seed=5)
     fill_cache(kv, bt, lens, hkv, d, page, dtype)
     pos = torch.tensor([c - 1 for c in lens], dtype=torch.int32, device=dev())
@@ -415,6 +415,11 @@ def test_decode_attention_with_larger_splits(ops, monkeypatch, hq, hkv, d, page,
     out = ops.paged_attention(q, kv, status=status, **args)
     assert int(status.item()) == 0
     close(out, ref.paged_attention(q, kv, **args), dtype)
+    # rows in another order and fewer of them: other cuts, the same results
+    keep = list(range(len(lens) - 1, -1, -2))
+    sub = ops.paged_attention(q[keep].contiguous(), kv, positions=pos[keep].contiguous(),
+                              token_seq=seq[keep].contiguous(), block_table=bt, scale=d ** -0.5, window=window)
+    close(sub, out[keep], dtype)
     ops.check_kernel_status()
 
 

@@ -39,7 +39,7 @@ def make_case(seed, contexts, hq=8, hkv=2, d=128, page=64):
         positions=torch.tensor([c - 1 for c in contexts], dtype=torch.int32, device=dev),
         token_seq=torch.arange(n, dtype=torch.int32, device=dev),
         rows=torch.arange(n, dtype=torch.int32, device=dev), hq=hq, hkv=hkv, d=d, page=page, pages=total,
-        splits=(max(contexts) + 255) // 256)
+        max_context=max(contexts))
 
 
 def test_noalloc_entry_point_matches_the_ordinary_one_twice():
@@ -56,11 +56,11 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice():
     stream = torch.cuda.current_stream().cuda_stream
     status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
 
-    def call(case, out, splits=None, window=0):
+    def call(case, out, num_rows=None, window=0):
         return fn(out.data_ptr(), case["q"].data_ptr(), case["kv"].data_ptr(), case["rows"].data_ptr(),
-                  case["rows"].shape[0], case["positions"].data_ptr(), case["token_seq"].data_ptr(),
+                  num_rows or case["rows"].shape[0], case["positions"].data_ptr(), case["token_seq"].data_ptr(),
                   case["block_table"].data_ptr(), case["block_table"].shape[1], case["hq"], case["hkv"], case["d"],
-                  case["page"], case["pages"], float(case["d"]) ** -0.5, window, splits or case["splits"],
+                  case["page"], case["pages"], float(case["d"]) ** -0.5, window, case["max_context"],
                   status.data_ptr(), stream)
 
     import torch_ops
@@ -84,9 +84,11 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice():
     assert int(status.item()) == 0
     ops.check_kernel_status()
 
-    # beyond the built-in scratch: refused, with a message that says why
+    # beyond the built-in scratch: refused before anything is read or launched, with a message that says why
+    # (the call claims more rows than the scratch has slots for; it never looks at them)
     case = make_case(3, [40])
     out = torch.zeros(1, case["hq"] * case["d"], dtype=torch.bfloat16, device="cuda:0")
     too_many = capacity // (case["hq"] * (case["d"] + 2)) + 1
-    assert call(case, out, splits=too_many) != 0
-    assert b"exceed" in lib.ti_last_error()
+    assert call(case, out, num_rows=too_many) != 0
+    assert b"built-in scratch" in lib.ti_last_error()
+    assert not out.any()

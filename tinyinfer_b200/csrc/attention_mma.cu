@@ -11,15 +11,21 @@
 // (never added), and value rows that no query of the CTA may see are zeroed in shared memory, so
 // stale or unwritten pages cannot leak NaNs.
 //
-// The split is by position only (256 keys per split), so a request's result does not depend on what
-// else is in the batch. Partial results (unnormalised output, maximum, sum per split) go to float32
-// scratch and a second kernel merges them. (Prompt portions: attention_prefill_tcgen05.cu.)
+// The work is shared out evenly: all key tiles of the step, in the order (request, kv head, tile), are
+// cut into as many equal runs as there are CTAs (at least four tiles, 256 keys, a run), so that every
+// CTA streams the same number of bytes whatever the mix of context lengths; a run that crosses from one
+// (request, kv head) into the next makes a part of each. A pair that lies inside one run is finished
+// there. Of a pair that several CTAs share, each writes its partial result (unnormalised output, maximum,
+// sum) to float32 scratch and a second kernel merges the pair's parts, in key order. Where the cuts fall
+// depends on the batch, so a request's result depends on what else is in the batch by float32 rounding
+// of the merge, and by nothing else.
+// (Prompt portions: attention_prefill_tcgen05.cu.)
 #include "sm100_ptx.cuh"
 
 namespace {
 
 constexpr int TK = 64;            // keys per tile
-constexpr int CHUNK = 256;        // keys per decode split
+constexpr int MIN_RUN_TILES = 4;  // fewest key tiles of a CTA's run: a part pays about 52 keys' worth of time beyond its keys
 constexpr int STAGES = 3;
 constexpr int CONSUMER_THREADS = 128;
 constexpr int THREADS = CONSUMER_THREADS + 32;
@@ -27,13 +33,14 @@ constexpr int THREADS = CONSUMER_THREADS + 32;
 struct AttnParams {
     __nv_bfloat16* out;            // [T, Hq * D]
     const __nv_bfloat16* q;        // [T, Hq, D]
-    float* part_o;                 // decode: [rows][Hq][max_splits][D]
-    float* part_ml;                // decode: [rows][Hq][max_splits][2]
-    const int* rows;               // decode: flat token rows; prefill: tiles as int4 {seq, row0, nrows, pos0}
+    float* part_o;                 // [part slots][query heads of a kv head][D]
+    float* part_ml;                // [part slots][query heads of a kv head][2]
+    const int* rows;               // flat token rows of the decoded tokens
     const int* positions;
     const int* token_seq;
     const int* block_table;
-    int max_blocks, hq, hkv, page_size, num_pages, window, max_splits, num_rows, chunk;
+    int max_blocks, hq, hkv, page_size, num_pages, window, num_rows;
+    int num_ctas;                  // CTAs of the split kernel: the runs are cut for this many
     float scale_log2;              // softmax scale times log2(e)
     int* status;
 };
@@ -119,9 +126,76 @@ __device__ __forceinline__ void zero_value_rows(uint8_t* v_tile, int keep_lo, in
 }
 
 // ------------------------------------------------------------------------------------ decode
-// Persistent: a CTA walks over work items (decode row, kv head, split of 256 keys), item = cta,
-// cta + grid, ...; the loading warp runs ahead into the next item while the consumers merge and
-// write the current one, so HBM does not idle at item boundaries.
+// Key tiles a decoded row has to read: those from the one its window (if any) begins in to its last.
+struct RowTiles { int n, lo_tile, lo, ctx, row; };
+__device__ __forceinline__ RowTiles row_tiles(const AttnParams& p, int r) {
+    RowTiles t;
+    t.row = p.rows[r];
+    t.ctx = p.positions[t.row] + 1;
+    t.lo = p.window > 0 ? max(0, t.ctx - p.window) : 0;
+    t.lo_tile = t.lo / TK;
+    t.n = (t.ctx + TK - 1) / TK - t.lo_tile;
+    return t;
+}
+// Tiles per run for `total` tiles (all kv heads) on `ctas` CTAs.
+__device__ __forceinline__ int run_tiles(long long total, int ctas) {
+    const long long per = (total + ctas - 1) / ctas;
+    return (int)(per < MIN_RUN_TILES ? MIN_RUN_TILES : per);
+}
+// Sum over the block of `mine` (all of it) and over the threads before this one. NT threads, all call it.
+template <int NT>
+__device__ __forceinline__ void block_scan(int mine, int* warp_sums /* [NT / 32] shared */, int& before, int& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += v;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    before = incl - mine;
+    total = 0;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) {
+        if (w < warp) before += warp_sums[w];
+        total += warp_sums[w];
+    }
+}
+
+// A CTA's walk over the parts of its run: the loading warp and the consumers step through the same parts.
+struct Part { int r, row, kvh, tile0, tile1, k_begin, k_end, slot, pair, cta0, cta1; };   // cta0..cta1: the CTAs whose runs hold the pair's tiles
+struct RunWalk {
+    long long cur, end, base;      // global tile indices; base: that of (row r, kv head 0, its first tile)
+    int r, per;
+    RowTiles rt;
+    __device__ __forceinline__ bool next(const AttnParams& p, Part& part) {
+        if (cur >= end) return false;
+        while (cur - base >= (long long)p.hkv * rt.n) {        // on to the next decoded row
+            base += (long long)p.hkv * rt.n;
+            rt = row_tiles(p, ++r);
+        }
+        const int off = (int)(cur - base);
+        const int kvh = off / rt.n, tl = off % rt.n;
+        const int cnt = (int)min((long long)(rt.n - tl), end - cur);
+        part.r = r; part.row = rt.row; part.kvh = kvh;
+        part.tile0 = rt.lo_tile + tl; part.tile1 = part.tile0 + cnt;
+        part.k_begin = max(rt.lo, part.tile0 * TK);
+        part.k_end = min(rt.ctx, part.tile1 * TK);
+        part.pair = r * p.hkv + kvh;
+        part.slot = (int)blockIdx.x + part.pair;               // CTA and pair both only grow along the walk: no two parts share a slot
+        const long long first = base + (long long)kvh * rt.n;  // the pair's first tile
+        part.cta0 = (int)(first / per);
+        part.cta1 = (int)((first + rt.n - 1) / per);
+        cur += cnt;
+        return true;
+    }
+};
+
+// Persistent: every CTA takes one run of key tiles (see the head of the file) and walks over its parts;
+// the loading warp runs ahead into the next part while the consumers merge and write the current one,
+// so HBM does not idle at part boundaries. `rows` and `positions` are read BEFORE the wait for the
+// kernels ahead in the stream (they are inputs of the step, never written by the kernel just before).
 template <int D>
 __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                    const AttnParams p) {
@@ -133,44 +207,53 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
     float* mbuf = reinterpret_cast<float*>(smem + STAGES * S::STAGE_BYTES + 128);   // [4 warps][group][LD]
     const uint32_t bar0 = smem_u32(bars);
     __shared__ int abort_sh;
+    __shared__ int warp_sums[THREADS / 32];
+    __shared__ int start_sh[2];                            // first row of this CTA's run, tiles (per kv head) before it
     volatile int* abort_flag = &abort_sh;
 
     ti_grid_launch_dependents();
     const int group = p.hq / p.hkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_items = p.num_rows * p.hkv * p.max_splits;
     if (threadIdx.x == 0) {
         abort_sh = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(bar0 + 8u * s, 1); mbar_init(bar0 + 8u * (STAGES + s), 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // ---- this CTA's run: every thread adds up the tiles of a stretch of rows, a scan gives the total and
+    // what lies before each stretch, and the thread whose stretch holds the run's first tile says where
+    const int stretch = (p.num_rows + THREADS - 1) / THREADS;
+    const int my_r0 = min(p.num_rows, (int)threadIdx.x * stretch), my_r1 = min(p.num_rows, my_r0 + stretch);
+    int mine = 0;
+    for (int r = my_r0; r < my_r1; ++r) mine += row_tiles(p, r).n;
+    int before, total;
+    block_scan<THREADS>(mine, warp_sums, before, total);
+    const long long all_tiles = (long long)total * p.hkv;
+    const int per = run_tiles(all_tiles, p.num_ctas);
+    const long long run_begin = (long long)blockIdx.x * per, run_end = min(all_tiles, run_begin + per);
+    if (run_begin < all_tiles && run_begin >= (long long)before * p.hkv && run_begin < (long long)(before + mine) * p.hkv) {
+        int acc = before;
+        for (int r = my_r0; r < my_r1; ++r) {
+            const int n = row_tiles(p, r).n;
+            if (run_begin < (long long)(acc + n) * p.hkv) { start_sh[0] = r; start_sh[1] = acc; break; }
+            acc += n;
+        }
+    }
     __syncthreads();
+    if (run_begin >= all_tiles) return;                    // more CTAs than runs
+    RunWalk walk;
+    walk.cur = run_begin; walk.end = run_end; walk.r = start_sh[0]; walk.per = per;
+    walk.base = (long long)start_sh[1] * p.hkv;
+    walk.rt = row_tiles(p, walk.r);
     ti_grid_wait();
-
-    // item -> its row, kv head and key range; false if the split holds no visible key
-    struct Item { int r, row, kvh, split, k_begin, k_end; };
-    auto get_item = [&](int w, Item& it) {
-        it.split = w % p.max_splits;
-        const int rest = w / p.max_splits;
-        it.kvh = rest % p.hkv;
-        it.r = rest / p.hkv;
-        it.row = p.rows[it.r];
-        const int ctx = p.positions[it.row] + 1;
-        const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
-        it.k_begin = max(it.split * p.chunk, lo);
-        it.k_end = min(ctx, (it.split + 1) * p.chunk);
-        return it.k_begin < it.k_end;
-    };
 
     if (warp == 4) {
         if (lane == 0) {
             uint32_t n = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
-                Item it;
-                if (!get_item(w, it)) continue;
+            Part it;
+            while (ok && walk.next(p, it)) {
                 const int* table = p.block_table + (size_t)p.token_seq[it.row] * p.max_blocks;
-                for (int t = it.k_begin / TK; t < (it.k_end + TK - 1) / TK; ++t, ++n) {
+                for (int t = it.tile0; t < it.tile1; ++t, ++n) {
                     const int s = n % STAGES;
                     if (!mbar_wait(bar0 + 8u * (STAGES + s), ((n / STAGES) & 1u) ^ 1u, abort_flag, p.status, 21)) { ok = false; break; }
                     load_tile<D>(&kv_map, p, table, it.kvh, t, smem_u32(smem + s * S::STAGE_BYTES), bar0 + 8u * s);
@@ -184,9 +267,8 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
     const int g = lane >> 2, c = (lane & 3) * 2;
     const int id = lane >> 3, rr = lane & 7;
     uint32_t n = 0;
-    for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
-        Item item;
-        if (!get_item(w, item)) continue;
+    Part item;
+    while (walk.next(p, item)) {
         uint32_t qa[D / 16][4];
         {
             const __nv_bfloat16* q0 = p.q + ((size_t)item.row * p.hq + (size_t)item.kvh * group) * D;
@@ -204,7 +286,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
         float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
         const int k_begin = item.k_begin, k_end = item.k_end;
 
-        for (int t = k_begin / TK; t < (k_end + TK - 1) / TK; ++t, ++n) {
+        for (int t = item.tile0; t < item.tile1; ++t, ++n) {
             const int s = n % STAGES;
             if (!mbar_wait(bar0 + 8u * s, (n / STAGES) & 1u, abort_flag, p.status, 22)) return;
             uint8_t* k_tile = smem + s * S::STAGE_BYTES;
@@ -275,7 +357,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
             if (lane == 0) mbar_arrive(bar0 + 8u * (STAGES + s));
         }
 
-        // ---- merge the four warps (each saw a quarter of the keys) and write the split's partial.
+        // ---- merge the four warps (each saw a quarter of the keys) and write the part's partial.
         // Only the rows that are real query heads travel through shared memory.
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -313,41 +395,59 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
                 acc += f * mbuf[((size_t)w4 * group + hrow) * LD + d];
                 l_all += f * mbuf[((size_t)w4 * group + hrow) * LD + D + 1];
             }
-            const size_t slot = ((size_t)item.r * p.hq + (size_t)item.kvh * group + hrow) * p.max_splits + item.split;
-            p.part_o[slot * D + d] = acc;
-            if (d == 0) { p.part_ml[slot * 2] = m_all; p.part_ml[slot * 2 + 1] = l_all; }
+            if (item.cta0 == item.cta1) {                      // the pair lies inside this run: this is its result
+                p.out[((size_t)item.row * p.hq + (size_t)item.kvh * group + hrow) * D + d] =
+                    __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+            } else {
+                const size_t slot = (size_t)item.slot * group + hrow;
+                __stcg(p.part_o + slot * D + d, acc);
+                if (d == 0) __stcg(reinterpret_cast<float2*>(p.part_ml + slot * 2), make_float2(m_all, l_all));
+            }
         }
     }
 }
 
-// One block per (decode row, query head), one thread per feature: merges the splits that hold visible
-// keys. The partials of sixteen splits are requested together (one trip to L2 for a context of 4096)
-// and folded into a running maximum, sum and output, in split order.
+// The pairs that several CTAs share: one block per (decode row, query head), one thread per feature, merges
+// the pair's parts in key order (a pair that lay inside one run was finished there: its blocks leave at
+// once). The block works out which CTAs' runs hold the pair the way the split kernel does, before it waits
+// for that kernel. The partials of sixteen parts are requested together and folded into a running maximum,
+// sum and output. (Merging inside the split kernel, by the CTA that counts itself in last, was slower by
+// 3 to 5 us at 1 to 8 long requests: while the kernel streams, the release that publishes a CTA's
+// partials waits microseconds for its stores.)
 template <int D>
 __global__ void decode_merge_kernel(const AttnParams p) {
+    __shared__ int warp_sums[D / 32];
     ti_grid_launch_dependents();
-    ti_grid_wait();
     const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-    const int row = p.rows[r];
-    const int ctx = p.positions[row] + 1;
-    const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
-    const int s0 = lo / p.chunk;
-    int s1 = (ctx - 1) / p.chunk;
-    if (s1 >= p.max_splits) {                              // the caller gave fewer splits than the context needs:
-        if (d == 0 && p.status) atomicExch(p.status, 23);  // say so, and read nothing that is not this row's
-        s1 = p.max_splits - 1;
+    int mine = 0, mine_before = 0;
+    for (int r2 = d; r2 < p.num_rows; r2 += D) {
+        const int n = row_tiles(p, r2).n;
+        mine += n;
+        if (r2 < r) mine_before += n;
     }
-    const size_t base = ((size_t)r * p.hq + h) * p.max_splits;
+    int skip, total, tiles_before;
+    block_scan<D>(mine, warp_sums, skip, total);
+    __syncthreads();
+    block_scan<D>(mine_before, warp_sums, skip, tiles_before);
+    const RowTiles rt = row_tiles(p, r);
+    const int group = p.hq / p.hkv, kvh = h / group, hrow = h % group;
+    const int per = run_tiles((long long)total * p.hkv, p.num_ctas);
+    const long long first = (long long)tiles_before * p.hkv + (long long)kvh * rt.n;      // the pair's tiles, globally
+    const int c0 = (int)(first / per), c1 = (int)((first + rt.n - 1) / per);
+    if (c0 == c1) return;
+    const int pair = r * p.hkv + kvh;
+    ti_grid_wait();
     float m_run = -INFINITY, acc = 0.f, l_all = 0.f;
-    for (int sb = s0; sb <= s1; sb += 16) {
+    for (int cb = c0; cb <= c1; cb += 16) {
         float ms[16], ls[16], os[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const bool in = sb + j <= s1;
-            const float2 ml = in ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + (base + sb + j) * 2)) : make_float2(-INFINITY, 0.f);
+            const bool in = cb + j <= c1;
+            const size_t slot = (size_t)(cb + j + pair) * group + hrow;
+            const float2 ml = in ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + slot * 2)) : make_float2(-INFINITY, 0.f);
             ms[j] = ml.x;
             ls[j] = ml.y;
-            os[j] = in ? __ldcg(p.part_o + (base + sb + j) * D + d) : 0.f;
+            os[j] = in ? __ldcg(p.part_o + slot * D + d) : 0.f;
         }
         float m_new = m_run;
 #pragma unroll
@@ -358,13 +458,13 @@ __global__ void decode_merge_kernel(const AttnParams p) {
         l_all *= keep;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const float f = exp2f(ms[j] - m_use);          // 0 for a split that is not there
+            const float f = exp2f(ms[j] - m_use);          // 0 for a part that is not there
             acc += f * os[j];
             l_all += f * ls[j];
         }
         m_run = m_new;
     }
-    p.out[((size_t)row * p.hq + h) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+    p.out[((size_t)rt.row * p.hq + h) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
 }
 
 template <typename K>
@@ -389,8 +489,6 @@ TI_API int ti_attention_bf16_supported(int hq, int hkv, int d, int page_size) {
     return (d == 64 || d == 128) && hq > 0 && hkv > 0 && hq % hkv == 0 && hq / hkv <= 16 && page_size >= 16 &&
            ((page_size < TK && TK % page_size == 0) || page_size % TK == 0) ? 1 : 0;
 }
-TI_API int ti_attention_decode_chunk() { return CHUNK; }
-
 namespace {
 // Shared memory that decode_attention_kernel<128> (which 0) or <64> (which 1) was last allowed on the
 // current device: the attribute is kept per device, so the record is too. nullptr: no current device.
@@ -410,62 +508,59 @@ int decode_slots(int d, int group) {
 }
 }  // namespace
 
-// Keys per split for a decode step of num_rows requests whose longest context is max_context: 256, or a
-// larger power-of-two multiple of it where that is expected to be at least 5 % faster. A work item (row,
-// kv head, split) costs about 52 keys' worth of time beyond its keys, the items run in rounds over the
-// resident CTAs, and the merge makes one trip to L2 per 16 splits (measured on a B200 at 8 x 4,096 keys:
-// 32.1 us with splits of 256, 29.3 with 512; 1 x 32,768: 43.1 and 29.7 with 1,024; with fewer items than
-// CTAs the larger split loses, 1 x 4,096: 9.8 and 13.1 us). Smaller splits also even out requests of
-// different lengths, hence the margin.
-TI_API int ti_attention_decode_plan(int num_rows, int hq, int hkv, int d, int max_context, int window) {
-    if (num_rows <= 0 || hkv <= 0 || hq % hkv != 0 || (d != 64 && d != 128)) return CHUNK;
+// CTAs the decode kernel is launched with for num_rows requests of at most max_context keys each: those
+// that run side by side, or fewer when there are not four key tiles for each. A function of its arguments
+// alone, so a captured launch and the scratch sized for it agree.
+TI_API int ti_attention_decode_ctas(int num_rows, int hq, int hkv, int d, int max_context, int window) {
+    if (num_rows <= 0 || hkv <= 0 || hq % hkv != 0 || (d != 64 && d != 128) || max_context <= 0) return 1;
+    const long long visible = window > 0 && window + TK < max_context ? window + TK : max_context;
+    const long long runs = ((long long)num_rows * hkv * ((visible + TK - 1) / TK) + MIN_RUN_TILES - 1) / MIN_RUN_TILES;
     const int slots = decode_slots(d, hq / hkv);
-    const long long visible = window > 0 && window < max_context ? window : max_context;
-    int best = CHUNK;
-    double best_cost = 0.0;
-    for (int c = CHUNK; c <= 8 * CHUNK; c *= 2) {
-        const long long splits = (visible + c - 1) / c;
-        const long long items = (long long)num_rows * hkv * splits;
-        const double cost = (double)((items + slots - 1) / slots) * (c + 52) + (double)((splits + 15) / 16) * 60.0;
-        if (c == CHUNK || cost < 0.95 * best_cost) { best = c; best_cost = cost; }
-    }
-    return best;
+    return (int)(runs < slots ? (runs < 1 ? 1 : runs) : slots);
+}
+// Floats of scratch that ti_attention_decode_bf16 needs for these arguments: a part slot per CTA and per
+// (request, kv head), each the query heads of a kv head times head_dim + 2.
+TI_API long long ti_attention_decode_scratch_floats(int num_rows, int hq, int hkv, int d, int max_context, int window) {
+    if (hkv <= 0) return 0;
+    const long long slots = (long long)ti_attention_decode_ctas(num_rows, hq, hkv, d, max_context, window) + (long long)num_rows * hkv;
+    return slots * (hq / hkv) * (d + 2);
 }
 
-// Decode: `rows` lists the flat rows of the step whose request brings exactly one token.
-// Scratch: part_o float32 [num_rows * hq * max_splits * d], part_ml float32 [num_rows * hq * max_splits * 2];
-// chunk: keys per split, a multiple of 256 (ti_attention_decode_plan suggests one); max_splits >=
-// ceil(longest context / chunk): a row whose context needs more sets *status to 23 and is computed from
-// the keys the splits cover, reading nothing outside its own partials. Calls that share the scratch must
-// not overlap.
-TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cache, float* part_o, float* part_ml,
+// Decode: `rows` lists the flat rows of the step whose request brings exactly one token. `scratch`: float32,
+// scratch_floats >= ti_attention_decode_scratch_floats(same arguments), else the call is refused. max_context:
+// an upper bound of the rows' contexts (it only sizes the launch: a longer context is computed all the same,
+// on the CTAs there are). `rows` and `positions` are read before the kernels wait for the work ahead of them
+// in the stream: they must not be results of the kernel launched just before. Calls that share the scratch
+// must not overlap.
+TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cache, float* scratch, long long scratch_floats,
                                     const int* rows, int num_rows, const int* positions, const int* token_seq,
                                     const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,
-                                    int num_pages, float scale, int window, int chunk, int max_splits, int* status,
+                                    int num_pages, float scale, int window, int max_context, int* status,
                                     cudaStream_t stream) {
     if (check_shape(hq, hkv, d, page_size, "attention_decode")) return -1;
-    TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && max_splits > 0 && max_splits <= 65535, "attention_decode: bad sizes");
-    TI_REQUIRE(chunk >= CHUNK && chunk % CHUNK == 0, "attention_decode: splits of %d keys are not a multiple of %d", chunk, CHUNK);
+    TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && max_context > 0, "attention_decode: bad sizes");
     if (num_rows == 0) return 0;
+    const int group = hq / hkv;
+    const int ctas = ti_attention_decode_ctas(num_rows, hq, hkv, d, max_context, window);
+    const long long slots = (long long)ctas + (long long)num_rows * hkv;
+    TI_REQUIRE(slots * group * (d + 2) <= scratch_floats,
+               "attention_decode: %d rows x %d kv heads on %d CTAs need %lld floats of scratch, %lld given",
+               num_rows, hkv, ctas, slots * group * (d + 2), scratch_floats);
     CUtensorMap map;
     if (!ti_get_bf16_map(kv_cache, 2ll * num_pages * hkv * page_size, d, page_size < TK ? page_size : TK, &map)) return -1;
     AttnParams p;
-    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q; p.part_o = part_o; p.part_ml = part_ml;
+    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q;
+    p.part_o = scratch; p.part_ml = scratch + slots * group * d;
     p.rows = rows; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
     p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
-    p.chunk = chunk;
-    p.window = window; p.max_splits = max_splits; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    p.num_rows = num_rows;
-    const int group = hq / hkv;
-    const long long items = (long long)num_rows * hkv * max_splits;
-    TI_REQUIRE(items < (1ll << 31), "attention_decode: too many work items");
+    p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    p.num_rows = num_rows; p.num_ctas = ctas;
     if (d == 128) {
         const int bytes = Smem<128>::decode_bytes(group);
         int* configured = configured_bytes(0);
         TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
         if (*configured < bytes) { if (set_smem(decode_attention_kernel<128>, bytes, "attention_decode")) return -1; *configured = bytes; }
-        const int slots = ti_sm_count() * (bytes <= 113 * 1024 ? 2 : 1);
-        ti_launch(decode_attention_kernel<128>, (int)(items < slots ? items : slots), THREADS, bytes, stream, map, p);
+        ti_launch(decode_attention_kernel<128>, ctas, THREADS, bytes, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
         ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
     } else {
@@ -473,8 +568,7 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
         int* configured = configured_bytes(1);
         TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
         if (*configured < bytes) { if (set_smem(decode_attention_kernel<64>, bytes, "attention_decode")) return -1; *configured = bytes; }
-        const int slots = ti_sm_count() * (bytes <= 56 * 1024 ? 4 : (bytes <= 75 * 1024 ? 3 : 2));
-        ti_launch(decode_attention_kernel<64>, (int)(items < slots ? items : slots), THREADS, bytes, stream, map, p);
+        ti_launch(decode_attention_kernel<64>, ctas, THREADS, bytes, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
         ti_launch(decode_merge_kernel<64>, dim3(num_rows, hq), 64, 0, stream, p);
     }
@@ -509,16 +603,16 @@ TI_API long long ti_attention_decode_noalloc_capacity() { return TI_NOALLOC_SCRA
 TI_API int ti_attention_decode_bf16_noalloc(void* out, const void* q, const void* kv_cache, const int* rows,
                                             int num_rows, const int* positions, const int* token_seq,
                                             const int* block_table, int max_blocks, int hq, int hkv, int d,
-                                            int page_size, int num_pages, float scale, int window, int max_splits,
+                                            int page_size, int num_pages, float scale, int window, int max_context,
                                             int* status, cudaStream_t stream) {
     constexpr int MAX_DEVICES = 64;
     static float* scratch_of_device[MAX_DEVICES] = {};
-    TI_REQUIRE(num_rows >= 0 && max_splits > 0 && hq > 0 && d > 0, "attention_decode_noalloc: bad sizes");
-    const long long need = (long long)num_rows * hq * max_splits * (d + 2);
+    TI_REQUIRE(num_rows >= 0 && max_context > 0 && hq > 0 && hkv > 0 && d > 0, "attention_decode_noalloc: bad sizes");
+    const long long need = ti_attention_decode_scratch_floats(num_rows, hq, hkv, d, max_context, window);
     TI_REQUIRE(need <= TI_NOALLOC_SCRATCH_FLOATS,
-               "attention_decode_noalloc: %d rows x %d heads x %d splits x (%d + 2) = %lld floats exceed the built-in "
-               "scratch of %lld floats; use ti_attention_decode_bf16 with a buffer of your own",
-               num_rows, hq, max_splits, d, need, TI_NOALLOC_SCRATCH_FLOATS);
+               "attention_decode_noalloc: %d rows x %d kv heads x %d query heads each x (%d + 2) need %lld floats, the "
+               "built-in scratch has %lld; use ti_attention_decode_bf16 with a buffer of your own",
+               num_rows, hkv, hq / hkv, d, need, TI_NOALLOC_SCRATCH_FLOATS);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     TI_REQUIRE(e == cudaSuccess && dev >= 0 && dev < MAX_DEVICES, "attention_decode_noalloc: no current device (%s)",
@@ -530,9 +624,7 @@ TI_API int ti_attention_decode_bf16_noalloc(void* out, const void* q, const void
                    cudaGetErrorString(e));
         scratch_of_device[dev] = ptr;
     }
-    float* part_o = scratch_of_device[dev];
-    float* part_ml = part_o + (long long)num_rows * hq * max_splits * d;
-    return ti_attention_decode_bf16(out, q, kv_cache, part_o, part_ml, rows, num_rows, positions, token_seq,
-                                    block_table, max_blocks, hq, hkv, d, page_size, num_pages, scale, window,
-                                    CHUNK, max_splits, status, stream);
+    return ti_attention_decode_bf16(out, q, kv_cache, scratch_of_device[dev], TI_NOALLOC_SCRATCH_FLOATS, rows, num_rows,
+                                    positions, token_seq, block_table, max_blocks, hq, hkv, d, page_size, num_pages,
+                                    scale, window, max_context, status, stream);
 }

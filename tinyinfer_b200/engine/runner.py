@@ -42,7 +42,7 @@ class ModelRunner:
         self.cuda_graphs = (cuda_graphs and self.device.type == "cuda"
                             and all(b.mixer.graph_safe for b in model.blocks))
         self._tables_only_grow = all(g.need.window is None for g in self.manager.groups)
-        self._graphs = {}          # (requests, split bucket) -> (graph, static logits)
+        self._graphs = {}          # requests in the step -> (graph, static logits, kernels)
         self._graph_pool = None
         self.graph_replays = 0
 
@@ -129,16 +129,12 @@ class ModelRunner:
         """A step of single decoded tokens: replayed from a CUDA graph captured for this number
         of requests (batches are padded up to a few sizes, so a handful of graphs serve every batch
         size). The graph reads the step's arrays from the fixed device buffer that
-        ``build`` has just filled; the attention grid is sized for the context rounded up to a
-        power of two of 256-key splits, so a handful of graphs cover every context length.
+        ``build`` has just filled; the attention launch is sized for the longest context a request
+        may have, so one graph covers every context length (the kernel shares out the keys there are).
         The returned logits live in the graph's own memory until the next replay."""
-        from .. import ops
         from ..ops import library
-        splits = 1
-        while splits * ops.DECODE_CHUNK < ctx.max_context:
-            splits *= 2
-        ctx.max_context = splits * ops.DECODE_CHUNK
-        key = (ctx.num_seqs, splits)
+        ctx.max_context = self.max_model_len
+        key = ctx.num_seqs
         hit = self._graphs.get(key)
         real = ctx.num_real_seqs
         if hit is not None:

@@ -53,16 +53,15 @@ _SIGNATURES["sm100"] = {
 }
 NORM_LINK_MAX_TOKENS = 64   # up to here two products can share an RMSNorm between them (see linear)
 _SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
-    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p]
-_SIGNATURES["sm100"]["ti_attention_decode_plan"] = [c_int, c_int, c_int, c_int, c_int, c_int]
+    c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
+_SIGNATURES["sm100"]["ti_attention_decode_scratch_floats"] = [c_int, c_int, c_int, c_int, c_int, c_int]
 _SIGNATURES["sm100"]["ti_attention_prefill_pair_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
     c_float, c_int, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_prefill_tc_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
     c_float, c_int, c_int, c_void_p, c_void_p]
-DECODE_CHUNK = 256        # fewest keys per split of the decode attention kernel (see decode_chunk)
 PREFILL_TILE = 256        # most query rows per CTA of the prefill attention kernels (two tiles of 128)
 PAIR_MIN_CTAS = 148       # fewer CTAs than this of the two-tile kernel: its tiles run as halves, one a CTA
 _bound = {}
@@ -494,18 +493,19 @@ def _decode_scratch(device, floats: int) -> torch.Tensor:
     return t
 
 
-_decode_chunks = {}
+_scratch_floats = {}
 
 
-def decode_chunk(num_rows: int, hq: int, hkv: int, head_dim: int, max_context: int, window: int = 0) -> int:
-    """Keys per split that the decode attention kernel is run with for this batch: DECODE_CHUNK or a
-    power-of-two multiple of it (many long contexts), as the library's plan says. A function of its
-    arguments alone, so a captured graph and the step that replays it agree."""
+def decode_scratch_floats(num_rows: int, hq: int, hkv: int, head_dim: int, max_context: int, window: int = 0) -> int:
+    """Floats of scratch the decode attention kernel needs for this batch (a slot for every CTA's and every
+    (request, kv head)'s partial result), as the library says. A function of its arguments alone."""
     key = (num_rows, hq, hkv, head_dim, max_context, window)
-    c = _decode_chunks.get(key)
-    if c is None:
-        c = _decode_chunks[key] = int(_fn("sm100", "ti_attention_decode_plan")(*key))
-    return c
+    n = _scratch_floats.get(key)
+    if n is None:
+        fn = _fn("sm100", "ti_attention_decode_scratch_floats")
+        fn.restype = ctypes.c_longlong
+        n = _scratch_floats[key] = int(fn(*key))
+    return n
 
 
 def release_scratch(device) -> None:
@@ -516,12 +516,6 @@ def release_scratch(device) -> None:
     _attn_scratch_outgrown.clear()
     _workspace.pop(key, None)
     _argmax_scratch.pop(key, None)
-
-
-def reserve_decode_scratch(device, num_rows: int, num_heads: int, head_dim: int, max_context: int) -> None:
-    """Sizes the decode attention scratch up front (before a CUDA graph is captured)."""
-    splits = (max_context + DECODE_CHUNK - 1) // DECODE_CHUNK
-    _decode_scratch(device, num_rows * num_heads * splits * (head_dim + 2))
 
 
 def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch.Tensor,
@@ -578,14 +572,11 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
         num_decode, num_tiles, max_context = len(rows_l), len(tiles_l) // 4, max(pos_h) + 1
     kstatus = kernel_status(q.device).data_ptr()
     if num_decode:
-        chunk = decode_chunk(num_decode, hq, hkv, d, max_context, int(window or 0))
-        splits = (max_context + chunk - 1) // chunk
-        scratch = _decode_scratch(q.device, num_decode * hq * splits * (d + 2))
-        part_ml = scratch.data_ptr() + 4 * num_decode * hq * splits * d
+        scratch = _decode_scratch(q.device, decode_scratch_floats(num_decode, hq, hkv, d, max_context, int(window or 0)))
         _run("sm100", "ti_attention_decode_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
-             scratch.data_ptr(), part_ml, decode_rows.data_ptr(), num_decode, positions.data_ptr(),
+             scratch.data_ptr(), scratch.numel(), decode_rows.data_ptr(), num_decode, positions.data_ptr(),
              token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
-             num_pages, float(scale), int(window or 0), chunk, splits, kstatus, _stream())
+             num_pages, float(scale), int(window or 0), int(max_context), kstatus, _stream())
     if num_pairs * hq >= PAIR_MIN_CTAS:             # two query tiles a CTA
         _run("sm100", "ti_attention_prefill_pair_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              tiles.data_ptr(), num_pairs, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,

@@ -143,6 +143,12 @@ def build(name: str, verbose: bool = True) -> Path:
             if res.returncode != 0:
                 raise BuildError(f"link of {name} failed:\n{res.stdout}\n{res.stderr}")
             os.replace(tmp, out)
+            for old in folder.glob(f"libti_{name}-*.so"):     # builds of earlier states of the sources
+                if old != out:
+                    try:
+                        old.unlink()       # a process that has one loaded keeps its mapping
+                    except OSError:
+                        pass
         finally:
             stop.set()
             shutil.rmtree(work, ignore_errors=True)
