@@ -164,7 +164,7 @@ __device__ __forceinline__ void block_scan(int mine, int* warp_sums /* [NT / 32]
 }
 
 // A CTA's walk over the parts of its run: the loading warp and the consumers step through the same parts.
-struct Part { int r, row, kvh, tile0, tile1, k_begin, k_end, slot, pair, cta0, cta1; };   // cta0..cta1: the CTAs whose runs hold the pair's tiles
+struct Part { int r, row, kvh, tile0, tile1, tile_new, k_begin, k_end, slot, pair, cta0, cta1; };   // tile_new: the tile of the row's own token; cta0..cta1: the CTAs whose runs hold the pair's tiles
 struct RunWalk {
     long long cur, end, base;      // global tile indices; base: that of (row r, kv head 0, its first tile)
     int r, per;
@@ -180,6 +180,7 @@ struct RunWalk {
         const int cnt = (int)min((long long)(rt.n - tl), end - cur);
         part.r = r; part.row = rt.row; part.kvh = kvh;
         part.tile0 = rt.lo_tile + tl; part.tile1 = part.tile0 + cnt;
+        part.tile_new = (rt.ctx - 1) / TK;
         part.k_begin = max(rt.lo, part.tile0 * TK);
         part.k_end = min(rt.ctx, part.tile1 * TK);
         part.pair = r * p.hkv + kvh;
@@ -194,8 +195,9 @@ struct RunWalk {
 
 // Persistent: every CTA takes one run of key tiles (see the head of the file) and walks over its parts;
 // the loading warp runs ahead into the next part while the consumers merge and write the current one,
-// so HBM does not idle at part boundaries. `rows` and `positions` are read BEFORE the wait for the
-// kernels ahead in the stream (they are inputs of the step, never written by the kernel just before).
+// so HBM does not idle at part boundaries. `rows`, `positions`, `token_seq`, the block tables and every key
+// tile but a row's last are read BEFORE the wait for the kernels ahead in the stream: they are inputs of the
+// step or older than it, never written by the kernels that lead up to this one.
 template <int D>
 __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                    const AttnParams p) {
@@ -244,16 +246,20 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
     walk.cur = run_begin; walk.end = run_end; walk.r = start_sh[0]; walk.per = per;
     walk.base = (long long)start_sh[1] * p.hkv;
     walk.rt = row_tiles(p, walk.r);
-    ti_grid_wait();
 
     if (warp == 4) {
+        // The kernel just before wrote this step's keys and values: for a decoded row that is its own token, in
+        // the row's last tile. Every other tile is older than the step, so the ring is filled with such tiles
+        // BEFORE the wait for that kernel (block tables and token_seq are inputs of the step, like positions),
+        // and HBM is busy while the kernels ahead drain.
         if (lane == 0) {
             uint32_t n = 0;
-            bool ok = true;
+            bool ok = true, waited = false;
             Part it;
             while (ok && walk.next(p, it)) {
                 const int* table = p.block_table + (size_t)p.token_seq[it.row] * p.max_blocks;
                 for (int t = it.tile0; t < it.tile1; ++t, ++n) {
+                    if (!waited && (n >= STAGES || t == it.tile_new)) { ti_grid_wait(); waited = true; }
                     const int s = n % STAGES;
                     if (!mbar_wait(bar0 + 8u * (STAGES + s), ((n / STAGES) & 1u) ^ 1u, abort_flag, p.status, 21)) { ok = false; break; }
                     load_tile<D>(&kv_map, p, table, it.kvh, t, smem_u32(smem + s * S::STAGE_BYTES), bar0 + 8u * s);
@@ -264,6 +270,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
     }
 
     // ---- consumers: the 16 rows of the MMA are the query heads of one kv head (rows >= group are zero)
+    ti_grid_wait();                                        // q comes from the kernel before
     const int g = lane >> 2, c = (lane & 3) * 2;
     const int id = lane >> 3, rr = lane & 7;
     uint32_t n = 0;
@@ -529,9 +536,10 @@ TI_API long long ti_attention_decode_scratch_floats(int num_rows, int hq, int hk
 // Decode: `rows` lists the flat rows of the step whose request brings exactly one token. `scratch`: float32,
 // scratch_floats >= ti_attention_decode_scratch_floats(same arguments), else the call is refused. max_context:
 // an upper bound of the rows' contexts (it only sizes the launch: a longer context is computed all the same,
-// on the CTAs there are). `rows` and `positions` are read before the kernels wait for the work ahead of them
-// in the stream: they must not be results of the kernel launched just before. Calls that share the scratch
-// must not overlap.
+// on the CTAs there are). `rows`, `positions`, `token_seq`, `block_table` and the keys and values of all
+// positions before each row's own are read before the kernels wait for the work ahead of them in the stream:
+// they must be complete when the call is made, not results of the kernels launched just before (those may
+// write q and the keys and values at the rows' own positions). Calls that share the scratch must not overlap.
 TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cache, float* scratch, long long scratch_floats,
                                     const int* rows, int num_rows, const int* positions, const int* token_seq,
                                     const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,

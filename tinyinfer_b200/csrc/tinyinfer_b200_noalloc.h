@@ -38,10 +38,12 @@ long long ti_attention_decode_scratch_floats(int num_rows, int hq, int hkv, int 
  * `rows` (num_rows of them, each the one new token of its request) are read and written.
  * kv_cache [2, num_pages, Hkv, page_size, D]; block_table int32 [requests, max_blocks] (-1: no page);
  * positions / token_seq int32 [T]: position of each row in its request, and its request's row in
- * block_table. max_context: an upper bound of the rows' contexts (it sizes the launch only). rows and
- * positions are read before the kernels wait for the work ahead of them in the stream: they must not be
- * results of the kernel launched just before. status: optional device int set on a bounded wait that
- * ran out. Same results as ti_attention_decode_bf16. */
+ * block_table. max_context: an upper bound of the rows' contexts (it sizes the launch only). rows,
+ * positions, token_seq, block_table and the keys and values of all positions before each row's own are
+ * read before the kernels wait for the work ahead of them in the stream: they must be complete when the
+ * call is made (the kernels launched just before may write q and the keys and values at the rows' own
+ * positions). status: optional device int set on a bounded wait that ran out. Same results as
+ * ti_attention_decode_bf16. */
 int ti_attention_decode_bf16_noalloc(void* out, const void* q, const void* kv_cache, const int* rows,
                                      int num_rows, const int* positions, const int* token_seq,
                                      const int* block_table, int max_blocks, int hq, int hkv, int d,
