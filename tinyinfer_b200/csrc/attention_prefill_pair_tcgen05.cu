@@ -9,15 +9,26 @@
 //                 (through the block table) into a ring of four buffers;
 //   warp 1        one thread issues the MMAs, whichever is ready next: S_X = Q_X K_j^T (128 x 128, fp32 in
 //                 tensor memory) and O_X += P_X V_j, X = A, B. P is read from TENSOR MEMORY (it is written
-//                 over the first half of S_X, two bfloat16 a column), V straight from the page layout as
-//                 an MN-major operand. O_X accumulates in tensor memory over all key tiles;
-//   warps 2..9    softmax of tile A, warps 10..17 of tile B: two threads share a query row (its
-//                 tensor-memory lane), each half of the keys and of the output features. They read the
-//                 scores once (tcgen05.ld), mask by assignment, keep a reference maximum m (from -inf) and
-//                 the sum in float32 and write P = 2^(s - m) as bfloat16 (tcgen05.st). The reference moves
-//                 only when the row maximum has grown by more than 8 (a factor 256: bfloat16 and float32
-//                 hold that with ease); then, and only then, the rows of O_X in tensor memory are
-//                 multiplied by 2^(m_old - m_new). At the end O_X / sum is stored.
+//                 over the first 64 columns of S_X, two bfloat16 a column), V straight from the page layout
+//                 as an MN-major operand. O_X accumulates in tensor memory over all key tiles;
+//   warps 2..5    softmax of tile A, warps 6..9 of tile B: a thread owns a query row (its tensor-memory
+//                 lane). The row's 128 scores come to registers in one trip (tcgen05.ld), are masked by
+//                 assignment, and with a reference maximum m (from -inf) and the sum in float32 go back
+//                 as P = 2^(s - m) in bfloat16 (tcgen05.st); nothing is exchanged between threads. The
+//                 reference moves only when the row maximum has grown by more than 8 (a factor 256:
+//                 bfloat16 and float32 hold that with ease); then, and only then, the rows of O_X in
+//                 tensor memory are multiplied by 2^(m_old - m_new). At the end O_X / sum is stored.
+//
+// Clock stamps taken inside the kernel (8,192 tokens, a tile of 128 keys for both query tiles every 4,200
+// cycles): a tile's softmax takes 2,200 cycles (scores in 90, maxima 280, exponentials 1,300 against 1,024
+// at the rate of the XU pipe, P out and fenced 300), its two products 1,100 (1,024 at the tensor rate), and
+// 400 go by before the issuing thread notices that P is there (a look at an mbarrier whose phase is not
+// complete costs it that much). The two tiles run out of step by themselves. Tried on this form, none
+// faster: the issuing thread watching plain counters instead of mbarriers (the tiles then fall into step:
+// both in their exponentials, then both waiting for products), P handed over in two halves, turns of the
+// two tiles at the exponentials, an issuing warp per tile (polling or sleeping), sleeping between polls.
+// What the stamps point to instead: tiles of 64 keys with two score buffers a query tile, so that the next
+// scores are ready before a tile's softmax ends and the softmax warps never wait for a product.
 //
 // Masked scores never reach an exponential (P is assigned 0 there), rows of V that no query of the CTA
 // may see are zeroed in shared memory before the second product (pages never written or given back cannot
@@ -32,7 +43,7 @@ namespace {
 constexpr int QM = 128;              // query rows per tile = accumulator lanes
 constexpr int KT = 128;              // keys per tile
 constexpr int NBUF = 4;              // ring of key OR value tiles
-constexpr int PP_THREADS = 576;      // TMA warp, MMA warp, eight softmax warps per query tile
+constexpr int PP_THREADS = 320;      // TMA warp, MMA warp, four softmax warps per query tile (a thread a row)
 constexpr float RESCALE_STEP = 8.f;  // the reference maximum follows the row maximum in steps of at least this (log2)
 
 struct PairParams {
@@ -58,6 +69,11 @@ __device__ __forceinline__ float ex2(float x) {          // 2^x, flushing; input
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -111,8 +127,6 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
     auto p_full = [&](int x) { return bar0 + 8u * (3 + 2 * NBUF + x); };
     auto o_full = [&](int x) { return bar0 + 8u * (5 + 2 * NBUF + x); };
     __shared__ uint32_t tmem_base_sh;
-    __shared__ float max_xch[2][2][2][QM];   // [query tile][step parity][column half][row]
-    __shared__ float sum_xch[2][2][QM];      // [query tile][column half][row]
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
 
@@ -122,7 +136,7 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
         abort_sh = 0;
         mbar_init(q_full, 1);
         for (int b = 0; b < NBUF; ++b) { mbar_init(kv_full(b), 1); mbar_init(kv_empty(b), 1); }
-        for (int x = 0; x < 2; ++x) { mbar_init(s_full(x), 1); mbar_init(p_full(x), 8); mbar_init(o_full(x), 1); }
+        for (int x = 0; x < 2; ++x) { mbar_init(s_full(x), 1); mbar_init(p_full(x), 4); mbar_init(o_full(x), 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(&tmem_base_sh, S::TMEM_COLS);
@@ -217,10 +231,10 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
                             const uint32_t v_addr = smem_u32(kv_ring + b * S::KV_TILE);
 #pragma unroll
                             for (int ks = 0; ks < KT / 16; ++ks) {
-                                // A: 16 keys = 8 columns of packed bfloat16 pairs (the keys of a column half lie over the
-                                // first 32 of that half's 64 score columns); B: 16 key rows of V = 2048 bytes
+                                // A: 16 keys = 8 columns of packed bfloat16 pairs (P lies over the first 64 of the
+                                // tile's 128 score columns); B: 16 key rows of V = 2048 bytes
                                 const uint64_t bdesc = make_sw128_desc_mn(v_addr + ks * 16 * 128, KT * 128, 1024);
-                                umma_bf16_tmem_a(o_tmem, s_tmem + (ks >> 2) * 64 + (ks & 3) * 8, bdesc, idesc_o,
+                                umma_bf16_tmem_a(o_tmem, s_tmem + ks * 8, bdesc, idesc_o,
                                                  (j > t0x[x] || ks > 0) ? 1u : 0u);
                             }
                             umma_commit(o_full(x));
@@ -259,19 +273,18 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
             }
         }
     } else {
-        // ------------------------------------------------------------ softmax and output (warps 2..17)
-        const int x = (warp - 2) >> 3;                                  // query tile of this warp
+        // ------------------------------------------------------------ softmax and output (warps 2..9)
+        // A thread owns a query row (its tensor-memory lane): the whole row of 128 scores comes to registers in
+        // one trip, nothing is exchanged with other threads, and P goes back in one.
+        const int x = (warp - 2) >> 2;                                  // query tile of this warp
         const int lane_group = warp & 3;                                // tensor-memory lanes this warp may touch
-        const int half = ((warp - 2) & 7) >> 2;                         // keys 64*half.., output features (D/2)*half..
         const int r = lane_group * 32 + lane;                           // query row of the tile = tensor-memory lane
         const int num_x = t1x[x] - t0x[x];
         const int first_pos = pos0 + x * QM;
         const int qpos = first_pos + r;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
         const uint32_t s_tmem = lane_addr + x * KT, o_tmem = lane_addr + 2 * KT + x * D;
-        const int bar_id = 1 + x * 4 + lane_group;                      // the two warps that share these rows
-        const int gtid = threadIdx.x - 64 - x * 256;                    // 0..255 among this tile's softmax threads
-        constexpr int KH = KT / 2, DH = D / 2;
+        const int gtid = threadIdx.x - 64 - x * 128;                    // 0..127 among this tile's softmax threads
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int i = 0; i < num_x && ok; ++i) {
@@ -282,85 +295,76 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
             // columns of this tile the row may see: kmin < column <= kmax (tile-local)
             const int kmax = qpos - tk0;
             const int kmin = p.window > 0 ? qpos - p.window - tk0 : -1;
-            const int c0 = half * KH;
-            const bool all_seen = c0 + KH - 1 <= kmax && c0 > kmin;
-            // pass 1: the maximum of this thread's 64 scores of the row (the visible ones)
-            float mx = -INFINITY;
+            const bool all_seen = KT - 1 <= kmax && kmin < 0;
+            uint32_t sr[KT];
 #pragma unroll
-            for (int cc = 0; cc < KH; cc += 32) {
-                uint32_t sr[32];
-                tmem_ld32_nowait(s_tmem + c0 + cc, sr);
-                tmem_wait_ld();
-                if (all_seen) {
+            for (int cc = 0; cc < KT; cc += 32) tmem_ld32_nowait(s_tmem + cc, sr + cc);
+            tmem_wait_ld();
+            // the row's maximum (of the visible scores), four chains side by side
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (all_seen) {
 #pragma unroll
-                    for (int k = 0; k < 32; ++k) mx = fmaxf(mx, __uint_as_float(sr[k]));
-                } else {
+                for (int k = 0; k < KT; k += 8)
 #pragma unroll
-                    for (int k = 0; k < 32; ++k)
-                        mx = fmaxf(mx, (c0 + cc + k <= kmax && c0 + cc + k > kmin) ? __uint_as_float(sr[k]) : -INFINITY);
+                    for (int u = 0; u < 4; ++u)
+                        m4[u] = fmax3(m4[u], __uint_as_float(sr[k + 2 * u]), __uint_as_float(sr[k + 2 * u + 1]));
+            } else {
+#pragma unroll
+                for (int k = 0; k < KT; ++k) {
+                    if (!(k <= kmax && k > kmin)) sr[k] = 0xff800000u;             // -inf: masked by assignment
+                    m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(sr[k]));
                 }
             }
-            max_xch[x][i & 1][half][r] = mx;
-            asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-            mx = fmaxf(mx, max_xch[x][i & 1][half ^ 1][r]) * p.scale_log2;      // the scale is positive
-            // The reference maximum moves only when the row's maximum has outgrown it by RESCALE_STEP; both
-            // threads of a row see the same numbers and decide alike, and so do the two warps (same rows).
+            const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;   // the scale is positive
+            // The reference maximum moves only when the row's maximum has outgrown it by RESCALE_STEP.
             const bool move = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
             const float m_new = move ? mx : m_ref;
+            const float m_old = m_ref;
+            m_ref = m_new;
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            // P = 2^(s * scale - m) (a masked score is -inf: exactly 0), its sum, and P as packed bfloat16 over the
+            // first 64 score columns of the tile
+            // Sixteen exponentials are issued before the first of them is used: a warp is alone on its scheduler
+            // while the other tile is in its products, and an ex2 takes tens of cycles to come back.
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k0 = 0; k0 < KT; k0 += 16) {
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    sr[k0 + u] = __float_as_uint(ex2(fmaf(__uint_as_float(sr[k0 + u]), p.scale_log2, -m_use)));
+#pragma unroll
+                for (int u = 0; u < 16; u += 2) {
+                    const float a = __uint_as_float(sr[k0 + u]), b = __uint_as_float(sr[k0 + u + 1]);
+                    l4[(u >> 1) & 3] += a + b;
+                    sr[(k0 + u) >> 1] = pack2(a, b);
+                }
+            }
+            l_run = l_run * (move ? ex2(m_old - m_new) : 1.f) + ((l4[0] + l4[1]) + (l4[2] + l4[3]));   // m_old = -inf: l_run is 0
+            tmem_st32(s_tmem, sr);
+            tmem_st32(s_tmem + 32, sr + 32);
+            // (after P is on its way, so that the row of scores and the row of O never share the registers)
             if (i > 0 && __any_sync(0xffffffffu, move)) {
                 // the rows of O so far carry the old reference: O *= 2^(m_ref - m_new), once P V of the tile before is in
                 if (!mbar_wait(o_full(x), (i - 1) & 1u, abort_flag, p.status, 45)) { ok = false; break; }
                 tmem_fence_after();
-                const float f = move ? ex2(m_ref - m_new) : 1.f;               // m_ref = -inf: O and l are 0, f = 0 is right
+                const float f = move ? ex2(m_old - m_new) : 1.f;               // m_ref = -inf: O and l are 0, f = 0 is right
                 uint32_t orow[32];
 #pragma unroll
-                for (int c = 0; c < DH; c += 32) {
-                    tmem_ld32_nowait(o_tmem + half * DH + c, orow);
+                for (int c = 0; c < D; c += 32) {
+                    tmem_ld32_nowait(o_tmem + c, orow);
                     tmem_wait_ld();
 #pragma unroll
                     for (int k = 0; k < 32; ++k) orow[k] = __float_as_uint(__uint_as_float(orow[k]) * f);
-                    tmem_st32(o_tmem + half * DH + c, orow);
-                }
-                tmem_wait_st();
-                l_run *= f;
-            }
-            m_ref = m_new;
-            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            // pass 2: P = 2^(s * scale - m), its sum, and P as packed bfloat16 over the first half of this
-            // thread's own scores (columns c0 .. c0 + 31: the scores they held are behind us by then)
-            uint32_t pr[KH / 2];
-#pragma unroll
-            for (int cc = 0; cc < KH; cc += 32) {
-                uint32_t sr[32];
-                tmem_ld32_nowait(s_tmem + c0 + cc, sr);
-                tmem_wait_ld();
-                if (all_seen) {
-#pragma unroll
-                    for (int k = 0; k < 32; k += 2) {
-                        const float a = ex2(fmaf(__uint_as_float(sr[k]), p.scale_log2, -m_use));
-                        const float b = ex2(fmaf(__uint_as_float(sr[k + 1]), p.scale_log2, -m_use));
-                        l_run += a + b;
-                        pr[(cc + k) >> 1] = pack2(a, b);
-                    }
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 32; k += 2) {
-                        const int col = c0 + cc + k;
-                        const float a = (col <= kmax && col > kmin) ? ex2(fmaf(__uint_as_float(sr[k]), p.scale_log2, -m_use)) : 0.f;
-                        const float b = (col + 1 <= kmax && col + 1 > kmin) ? ex2(fmaf(__uint_as_float(sr[k + 1]), p.scale_log2, -m_use)) : 0.f;
-                        l_run += a + b;
-                        pr[(cc + k) >> 1] = pack2(a, b);
-                    }
+                    tmem_st32(o_tmem + c, orow);
                 }
             }
-            tmem_st32(s_tmem + c0, pr);
             tmem_wait_st();
             // value rows no query of the CTA may see: zero them once the tile has landed (first and last tiles only)
             if (tk0 < lo || tk0 + KT > hi) {
                 const int li = 2 * (j - tmin) + 1, b = li % NBUF;
                 if (!mbar_wait(kv_full(b), (li / NBUF) & 1u, abort_flag, p.status, 46)) { ok = false; break; }
                 uint8_t* v_tile = kv_ring + b * S::KV_TILE;
-                for (int idx = gtid; idx < KT * (D / 8); idx += 256) {
+                for (int idx = gtid; idx < KT * (D / 8); idx += 128) {
                     const int row = idx / (D / 8), chunk = idx % (D / 8);
                     if (row >= lo - tk0 && row < hi - tk0) continue;
                     *reinterpret_cast<uint4*>(v_tile + (chunk >> 3) * (KT * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) =
@@ -375,16 +379,13 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
         if (ok && num_x > 0) {
             if (mbar_wait(o_full(x), (num_x - 1) & 1u, abort_flag, p.status, 47)) {
                 tmem_fence_after();
-                sum_xch[x][half][r] = l_run;
-                asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-                const float l_all = l_run + sum_xch[x][half ^ 1][r];
-                const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
                 const int rows_x = min(QM, nrows - x * QM);
-                __nv_bfloat16* dst = p.out + ((size_t)(row0 + x * QM + r) * p.hq + head) * D + half * DH;
+                __nv_bfloat16* dst = p.out + ((size_t)(row0 + x * QM + r) * p.hq + head) * D;
                 uint32_t orow[32];
 #pragma unroll
-                for (int c = 0; c < DH; c += 32) {
-                    tmem_ld32_nowait(o_tmem + half * DH + c, orow);
+                for (int c = 0; c < D; c += 32) {
+                    tmem_ld32_nowait(o_tmem + c, orow);
                     tmem_wait_ld();
                     if (r < rows_x) {
 #pragma unroll
