@@ -479,6 +479,29 @@ def test_sampling_matches_plain(ops):
     assert again.item() == got[5]
 
 
+@pytest.mark.parametrize("v", [151936, 50001])
+def test_sampling_of_long_rows_matches_plain(ops, v):
+    """A row is shared out over several blocks: top-k through the slices' own candidates (k up to 256), through
+    a scan of the whole row (larger k; hundreds of equal logits at the top), no top-k, greedy: the token is the
+    one the plain sampler draws from the whole row."""
+    ks = [0, 1, 100, 256, 257, 5000, 0, 50, 50, 7, 300, 3]
+    n = len(ks)
+    logits = rnd(n, v, dtype=torch.float32, std=2.5)
+    logits[7, 1000:3500] = 9.0            # 2,500 equal logits above all others: more candidates than a slice may leave
+    logits[8, ::977] = 9.0                # equal logits at the top spread over the slices: ties at the threshold are kept
+    logits[9, 6] = float("-inf")
+    temp = torch.tensor([1.0, 0.7, 1.3, 0.9] * 3, device=dev())
+    topk = torch.tensor(ks, dtype=torch.int32, device=dev())
+    greedy = torch.tensor([0, 0, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1], dtype=torch.int32, device=dev())
+    seed = torch.tensor([7, 2 ** 33 + 1, 99] * 4, dtype=torch.int64, device=dev())
+    stream = torch.arange(n, dtype=torch.int32, device=dev())
+    for first_step in (0, 40):
+        step = torch.arange(first_step, first_step + n, dtype=torch.int32, device=dev())
+        got = ops.sample(logits, temp, topk, greedy, seed, stream, step).tolist()
+        want = ref.sample(logits.cpu(), temp.cpu(), topk.cpu(), greedy.cpu(), seed.cpu(), stream.cpu(), step.cpu()).tolist()
+        assert got == want
+
+
 def test_sampling_distribution_and_topk(ops):
     v, n = 64, 4000
     row = rnd(1, v, dtype=torch.float32, std=1.5)

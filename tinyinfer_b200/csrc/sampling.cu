@@ -8,7 +8,6 @@
 #include "common.cuh"
 
 constexpr int SP_THREADS = 256;      // argmax parts, nll
-constexpr int SK_THREADS = 1024;     // the one-block-per-row sampling kernel: a row is 150 thousand logits
 
 __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
 #pragma unroll
@@ -90,95 +89,80 @@ __device__ __forceinline__ Best block_best_n(Best x, Best* sh) {
     return sh[0];
 }
 
-// Calls f(value, index) for every logit of the row, four at a time where the row allows it.
-template <typename F>
-__device__ __forceinline__ void for_each_logit(const float* x, int vocab, F f) {
+// Calls f(value, index) for the logits [begin, end) of the row (begin a multiple of 4), four at a time where
+// the row allows it. NT threads.
+template <int NT, typename F>
+__device__ __forceinline__ void for_each_logit(const float* x, int vocab, int begin, int end, F f) {
     if ((((uintptr_t)x) & 15) == 0 && (vocab & 3) == 0) {
-        for (int i = threadIdx.x * 4; i < vocab; i += SK_THREADS * 4) {
+        for (int i = begin + threadIdx.x * 4; i < end; i += NT * 4) {
             const float4 v = *reinterpret_cast<const float4*>(x + i);
             f(v.x, i); f(v.y, i + 1); f(v.z, i + 2); f(v.w, i + 3);
         }
     } else {
-        for (int i = threadIdx.x; i < vocab; i += SK_THREADS) f(x[i], i);
+        for (int i = begin + threadIdx.x; i < end; i += NT) f(x[i], i);
     }
 }
 
-__global__ void __launch_bounds__(SK_THREADS) sample_kernel(
-    int* __restrict__ out, const float* __restrict__ logits, int vocab,
-    const float* __restrict__ temperature, const int* __restrict__ topk, const int* __restrict__ greedy,
-    const long long* __restrict__ seed, const int* __restrict__ stream_id, const int* __restrict__ step,
-    const int* __restrict__ extra, int num_extra) {
-    __shared__ Best sh_best[SK_THREADS / 32];
-    __shared__ unsigned hist[256];
-    __shared__ unsigned sel_prefix, sel_remaining;
-    ti_grid_launch_dependents();
-    ti_grid_wait();
-    const int row = blockIdx.x, tid = threadIdx.x;
-    if (row == 0 && tid < num_extra) out[gridDim.x + tid] = extra[tid];   // words that ride home with the tokens
-    const float* x = logits + (size_t)row * vocab;
-
-    if (greedy == nullptr || greedy[row]) {
-        Best b{0.f, -1};
-        for_each_logit(x, vocab, [&](float v, int i) { if (v == v) b = better(b, Best{v, i}); });
-        b = block_best_n<SK_THREADS>(b, sh_best);
-        if (tid == 0) out[row] = b.i < 0 ? 0 : b.i;
-        return;
-    }
-
-    const float temp = temperature[row];
-    const int k = topk[row];
-    unsigned threshold = 0u;                              // keys below it are masked
-    if (k > 0 && k < vocab) {
-        // radix select of the k-th largest key, one byte per pass from the top
-        if (tid == 0) { sel_prefix = 0u; sel_remaining = (unsigned)k; }
-        for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            if (tid < 256) hist[tid] = 0u;
-            __syncthreads();
-            const unsigned prefix = sel_prefix;
-            const unsigned mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-            for_each_logit(x, vocab, [&](float raw, int) {
-                const float v = raw / temp;
-                if (v == v) {
-                    const unsigned key = order_key(v);
-                    if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u);
-                }
-            });
-            __syncthreads();
-            if (tid == 0) {
-                unsigned remaining = sel_remaining;
-                int b = 255;
-                for (; b > 0; --b) {
-                    if (hist[b] >= remaining) break;
-                    remaining -= hist[b];
-                }
-                sel_prefix = prefix | ((unsigned)b << shift);
-                sel_remaining = remaining;
+// Radix select, one byte per pass from the top: the k-th largest of the keys that `each` hands out (it calls
+// its argument once per key; every thread of the block calls select_kth with the same k). 0 if k <= 0.
+// hist: 256 shared words; sel: 2 shared words.
+template <typename Each>
+__device__ __forceinline__ unsigned select_kth(int k, unsigned* hist, unsigned* sel, Each each) {
+    if (k <= 0) return 0u;
+    if (threadIdx.x == 0) { sel[0] = 0u; sel[1] = (unsigned)k; }
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
+        __syncthreads();
+        const unsigned prefix = sel[0];
+        const unsigned mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+        each([&](unsigned key) { if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u); });
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned remaining = sel[1];
+            int b = 255;
+            for (; b > 0; --b) {
+                if (hist[b] >= remaining) break;
+                remaining -= hist[b];
             }
-            __syncthreads();
+            sel[0] = prefix | ((unsigned)b << shift);
+            sel[1] = remaining;
         }
-        threshold = sel_prefix;
+        __syncthreads();
     }
+    return sel[0];
+}
 
-    const uint2 key2 = make_uint2((unsigned)(seed[row] & 0xFFFFFFFFll), (unsigned)((unsigned long long)seed[row] >> 32));
-    const unsigned c1 = (unsigned)step[row], c2 = (unsigned)stream_id[row];
+__device__ __forceinline__ float key_value(unsigned key) {          // the inverse of order_key
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key);
+}
+__device__ __forceinline__ float gumbel(int index, unsigned c1, unsigned c2, uint2 key2) {
+    const uint4 r = philox4x32_10(make_uint4((unsigned)(index >> 2), c1, c2, 0u), key2);
+    const unsigned words[4] = {r.x, r.y, r.z, r.w};
+    return -logf(-logf(philox_uniform(words[index & 3])));
+}
+
+// Gumbel-max over the logits [begin, end) of a row whose scaled value's key is at least `threshold`.
+template <int NT>
+__device__ __forceinline__ Best gumbel_best(const float* x, int vocab, int begin, int end, float temp, unsigned threshold,
+                                            unsigned c1, unsigned c2, uint2 key2) {
     Best b{0.f, -1};
     const bool vec = (((uintptr_t)x) & 15) == 0 && (vocab & 3) == 0;
-    for (int blk = tid; blk * 4 < vocab; blk += SK_THREADS) {
+    for (int blk = (begin >> 2) + threadIdx.x; blk * 4 < end; blk += NT) {
         float vals[4];
         if (vec) {
             const float4 q = *reinterpret_cast<const float4*>(x + blk * 4);
             vals[0] = q.x; vals[1] = q.y; vals[2] = q.z; vals[3] = q.w;
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) vals[j] = blk * 4 + j < vocab ? x[blk * 4 + j] : -INFINITY;
+            for (int j = 0; j < 4; ++j) vals[j] = blk * 4 + j < end ? x[blk * 4 + j] : -INFINITY;
         }
         bool any = false;
         float sc[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             sc[j] = vals[j] / temp;
-            const bool keep = blk * 4 + j < vocab && sc[j] == sc[j] && sc[j] != -INFINITY && order_key(sc[j]) >= threshold;
+            const bool keep = blk * 4 + j < end && sc[j] == sc[j] && sc[j] != -INFINITY && order_key(sc[j]) >= threshold;
             if (!keep) sc[j] = -INFINITY;
             any |= keep;
         }
@@ -192,21 +176,154 @@ __global__ void __launch_bounds__(SK_THREADS) sample_kernel(
             b = better(b, Best{sc[j] + g, blk * 4 + j});
         }
     }
-    b = block_best_n<SK_THREADS>(b, sh_best);
-    if (tid == 0) out[row] = b.i < 0 ? 0 : b.i;
+    return b;
 }
 
+// A row of 150 thousand logits is too long for one block, and a Gumbel draw costs a Philox block and two
+// logarithms: SMP_PARTS blocks each take a slice of the row and the block that arrives last (a counter per
+// row, left at zero again) finishes it.
+//   greedy, or temperature without top-k: a part leaves its best (scaled logit + Gumbel noise for the
+//       latter) and the last block picks among the parts: the argmax of a row is the best of its slices' best.
+//   top-k with k <= SMP_CAP: a part finds the k-th largest scaled logit OF ITS SLICE and leaves every logit of
+//       the slice that is at least that (its key and index). Every logit among the row's k largest, ties with
+//       the k-th included, is among those; the last block selects the k-th largest of the at most SMP_PARTS *
+//       SMP_CAP candidates, which is the row's, and draws among the candidates that reach it. The noise
+//       of a logit depends on its index alone, so the token is the one a scan of the whole row would give.
+//   larger k, or more than SMP_CAP candidates in a slice (hundreds of equal logits): the last block scans the
+//       whole row itself.
+constexpr int SMP_PARTS = 16;
+constexpr int SMP_THREADS = 256;
+constexpr int SMP_CAP = 256;
+
+__global__ void __launch_bounds__(SMP_THREADS) sample_parts_kernel(
+    int* __restrict__ out, const float* __restrict__ logits, int vocab,
+    const float* __restrict__ temperature, const int* __restrict__ topk, const int* __restrict__ greedy,
+    const long long* __restrict__ seed, const int* __restrict__ stream_id, const int* __restrict__ step,
+    float* __restrict__ part_val, int* __restrict__ part_idx, unsigned* __restrict__ cand_key,
+    int* __restrict__ cand_idx, int* __restrict__ cand_cnt, int* __restrict__ counters,
+    const int* __restrict__ extra, int num_extra) {
+    __shared__ Best sh_best[SMP_THREADS / 32];
+    __shared__ unsigned hist[256];
+    __shared__ unsigned sel[2];
+    __shared__ int count_sh, last_sh;
+    __shared__ unsigned keys_sh[SMP_PARTS * SMP_CAP];
+    __shared__ int idx_sh[SMP_PARTS * SMP_CAP];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int part = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+    if (part == 0 && row == 0 && tid < num_extra) out[gridDim.y + tid] = extra[tid];   // words that ride home with the tokens
+    const float* x = logits + (size_t)row * vocab;
+    const int chunk = ((vocab + SMP_PARTS - 1) / SMP_PARTS + 3) & ~3;
+    const int begin = min(vocab, part * chunk), end = min(vocab, begin + chunk);
+    const bool is_greedy = greedy == nullptr || greedy[row];
+    const float temp = is_greedy ? 1.f : temperature[row];
+    const int k = is_greedy ? 0 : topk[row];
+    const bool top = k > 0 && k < vocab;
+    const uint2 key2 = is_greedy ? make_uint2(0u, 0u)
+                                 : make_uint2((unsigned)(seed[row] & 0xFFFFFFFFll), (unsigned)((unsigned long long)seed[row] >> 32));
+    const unsigned c1 = is_greedy ? 0u : (unsigned)step[row], c2 = is_greedy ? 0u : (unsigned)stream_id[row];
+
+    Best b{0.f, -1};
+    if (is_greedy) {
+        for_each_logit<SMP_THREADS>(x, vocab, begin, end, [&](float v, int i) { if (v == v) b = better(b, Best{v, i}); });
+    } else if (!top) {
+        b = gumbel_best<SMP_THREADS>(x, vocab, begin, end, temp, 0u, c1, c2, key2);
+    } else if (k <= SMP_CAP) {
+        const unsigned local = select_kth(k, hist, sel, [&](auto count) {
+            for_each_logit<SMP_THREADS>(x, vocab, begin, end, [&](float raw, int) {
+                const float v = raw / temp;
+                if (v == v) count(order_key(v));
+            });
+        });
+        if (tid == 0) count_sh = 0;
+        __syncthreads();
+        unsigned* ck = cand_key + ((size_t)row * SMP_PARTS + part) * SMP_CAP;
+        int* ci = cand_idx + ((size_t)row * SMP_PARTS + part) * SMP_CAP;
+        for_each_logit<SMP_THREADS>(x, vocab, begin, end, [&](float raw, int i) {
+            const float v = raw / temp;
+            if (v == v && order_key(v) >= local) {
+                const int at = atomicAdd(&count_sh, 1);
+                if (at < SMP_CAP) { ck[at] = order_key(v); ci[at] = i; }
+            }
+        });
+        __syncthreads();
+        if (tid == 0) cand_cnt[row * SMP_PARTS + part] = count_sh <= SMP_CAP ? count_sh : -1;
+    }
+    if (is_greedy || !top) {
+        b = block_best_n<SMP_THREADS>(b, sh_best);
+        if (tid == 0) { part_val[row * SMP_PARTS + part] = b.v; part_idx[row * SMP_PARTS + part] = b.i; }
+    }
+    __syncthreads();                                      // every thread's candidates are written
+    if (tid == 0) {
+        __threadfence();
+        const int arrived = atomicAdd(counters + row, 1);
+        last_sh = arrived == SMP_PARTS - 1;
+        if (last_sh) counters[row] = 0;
+    }
+    __syncthreads();
+    if (!last_sh) return;
+    __threadfence();
+
+    Best m{0.f, -1};
+    if (is_greedy || !top) {
+        if (tid < SMP_PARTS) m = Best{__ldcg(part_val + row * SMP_PARTS + tid), __ldcg(part_idx + row * SMP_PARTS + tid)};
+    } else {
+        bool whole = k > SMP_CAP;
+        int total = 0;
+        if (!whole) {
+            for (int pp = 0; pp < SMP_PARTS; ++pp) {
+                const int n = __ldcg(cand_cnt + row * SMP_PARTS + pp);
+                if (n < 0) { whole = true; break; }
+                for (int i = tid; i < n; i += SMP_THREADS) {
+                    keys_sh[total + i] = __ldcg(cand_key + ((size_t)row * SMP_PARTS + pp) * SMP_CAP + i);
+                    idx_sh[total + i] = __ldcg(cand_idx + ((size_t)row * SMP_PARTS + pp) * SMP_CAP + i);
+                }
+                total += n;
+            }
+        }
+        __syncthreads();
+        if (whole) {
+            // the plain way: select over the whole row, then draw over the whole row
+            const unsigned threshold = select_kth(k, hist, sel, [&](auto count) {
+                for_each_logit<SMP_THREADS>(x, vocab, 0, vocab, [&](float raw, int) {
+                    const float v = raw / temp;
+                    if (v == v) count(order_key(v));
+                });
+            });
+            m = gumbel_best<SMP_THREADS>(x, vocab, 0, vocab, temp, threshold, c1, c2, key2);
+        } else {
+            const unsigned threshold = select_kth(k, hist, sel, [&](auto count) {
+                for (int i = tid; i < total; i += SMP_THREADS) count(keys_sh[i]);
+            });
+            for (int i = tid; i < total; i += SMP_THREADS) {
+                const float sc = key_value(keys_sh[i]);
+                if (keys_sh[i] >= threshold && sc != -INFINITY)
+                    m = better(m, Best{sc + gumbel(idx_sh[i], c1, c2, key2), idx_sh[i]});
+            }
+        }
+    }
+    m = block_best_n<SMP_THREADS>(m, sh_best);
+    if (tid == 0) out[row] = m.i < 0 ? 0 : m.i;
+}
+
+TI_API int ti_sample_parts() { return SMP_PARTS; }
+TI_API int ti_sample_candidates() { return SMP_CAP; }
+
 // greedy == nullptr: every row is an argmax and the other per-row arrays are not read.
+// Scratch: part_val / part_idx of num_rows * ti_sample_parts() entries, cand_key / cand_idx of num_rows *
+// ti_sample_parts() * ti_sample_candidates(), cand_cnt of num_rows * ti_sample_parts(), counters: num_rows
+// zeroed ints (left zeroed). Calls that share them must be ordered on one stream.
 // extra / num_extra: device words (the kernels' status words, say) copied to out[num_rows ...] so that
 // one device-to-host copy brings them home with the tokens; out then has num_rows + num_extra entries.
 TI_API int ti_sample(int* out, const float* logits, int num_rows, int vocab, const float* temperature,
                      const int* topk, const int* greedy, const long long* seed, const int* stream_id,
-                     const int* step, const int* extra, int num_extra, cudaStream_t stream) {
-    TI_REQUIRE(num_rows >= 0 && vocab > 0, "sample: bad sizes");
+                     const int* step, float* part_val, int* part_idx, unsigned* cand_key, int* cand_idx, int* cand_cnt,
+                     int* counters, const int* extra, int num_extra, cudaStream_t stream) {
+    TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && vocab > 0, "sample: bad sizes");
     TI_REQUIRE(num_extra >= 0 && num_extra <= 32 && (num_extra == 0 || extra != nullptr), "sample: bad extra words");
     if (num_rows == 0) return 0;
-    ti_launch(sample_kernel, num_rows, SK_THREADS, 0, stream, out, logits, vocab, temperature, topk, greedy, seed, stream_id, step,
-              extra, num_extra);
+    ti_launch(sample_parts_kernel, dim3(SMP_PARTS, num_rows), SMP_THREADS, 0, stream, out, logits, vocab, temperature, topk,
+              greedy, seed, stream_id, step, part_val, part_idx, cand_key, cand_idx, cand_cnt, counters, extra, num_extra);
     TI_CHECK_LAUNCH("sample");
     return 0;
 }

@@ -39,9 +39,12 @@ _SIGNATURES = {
         "ti_gemm_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                          c_int, c_int, c_int, c_void_p],
         "ti_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                      c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_void_p, c_int, c_void_p],
         "ti_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "ti_token_nll": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "ti_sample_parts": [],
+        "ti_sample_candidates": [],
     },
 }
 _SIGNATURES["sm100"] = {
@@ -516,6 +519,7 @@ def release_scratch(device) -> None:
     _attn_scratch_outgrown.clear()
     _workspace.pop(key, None)
     _argmax_scratch.pop(key, None)
+    _sample_scratch.pop(key, None)
 
 
 def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch.Tensor,
@@ -595,6 +599,7 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
 # ---------------------------------------------------------------------- sampling
 _ARGMAX_PARTS = 32
 _argmax_scratch = {}
+_sample_scratch = {}
 
 
 def argmax(logits: torch.Tensor, extra: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -643,9 +648,23 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, topk: torch.Tensor, 
             raise KernelError(f"{name} must have one entry per row")
     num_extra = _check_extra(extra)
     out = torch.empty((n + num_extra,), dtype=torch.int32, device=logits.device)
+    key = torch.device(logits.device)
+    scratch = _sample_scratch.get(key)
+    if scratch is None or scratch[5].numel() < n:
+        # a row is shared out over several blocks: their best, and for top-k their candidates, meet here
+        rows = max(64, n)
+        parts = int(_fn("core", "ti_sample_parts")())
+        cap = int(_fn("core", "ti_sample_candidates")())
+        scratch = _sample_scratch[key] = (
+            torch.empty(rows * parts, dtype=torch.float32, device=key),
+            torch.empty(rows * parts, dtype=torch.int32, device=key),
+            torch.empty(rows * parts * cap, dtype=torch.int32, device=key),
+            torch.empty(rows * parts * cap, dtype=torch.int32, device=key),
+            torch.empty(rows * parts, dtype=torch.int32, device=key),
+            torch.zeros(rows, dtype=torch.int32, device=key))
     _run("core", "ti_sample", out.data_ptr(), logits.data_ptr(), n, logits.shape[1],
          temperature.data_ptr(), topk.data_ptr(), greedy.data_ptr(), seed.data_ptr(),
-         stream_id.data_ptr(), step.data_ptr(), _ptr(extra), num_extra, _stream())
+         stream_id.data_ptr(), step.data_ptr(), *(t.data_ptr() for t in scratch), _ptr(extra), num_extra, _stream())
     return out
 
 
