@@ -75,14 +75,22 @@ def main():
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--preset", default="8b", help="decode_step / prefill_step: whose layer sizes (8b, 1.7b, 32b)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--pair-form", choices=["auto", "never", "always"], default="auto",
+                    help="gemm, gated_gemm, steps: products of many tokens in the pair form where the library chooses it, "
+                         "never, or always")
     ap.add_argument("--pair-min-ctas", type=int, default=None,
                     help="attention_prefill: fewest CTAs for which the two-tile kernel runs (default: the product's)")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     if a.pair_min_ctas is not None:
         ops.PAIR_MIN_CTAS = a.pair_min_ctas
+    if a.pair_form == "never":
+        ops.set_pair_form(False)
+    elif a.pair_form == "always":
+        ops.PAIR_MIN_TOKENS = 1
     hbm, tflops, source = peaks()
     torch.manual_seed(0)
     out = {"kernel": a.kernel, "peaks": source}
@@ -153,7 +161,7 @@ def main():
         from tinyinfer_b200.cli import preset_config
         from tinyinfer_b200.engine.batch import StepEntry
         from tinyinfer_b200.engine.llm import LLM
-        cfg = preset_config("8b", num_hidden_layers=a.layers)
+        cfg = preset_config(a.preset, num_hidden_layers=a.layers)
         eng = EngineConfig(max_num_batched_tokens=max(2048, a.tokens), max_num_seqs=a.batch, max_model_len=a.context,
                            kvcache_block_size=a.page_size, dtype="bfloat16", cuda_graphs=not a.no_graph,
                            num_kvcache_blocks=(a.context // a.page_size) * a.batch + 8 + a.tokens // a.page_size)

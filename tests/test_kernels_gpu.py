@@ -117,8 +117,16 @@ TC_SHAPES = [(1, 4096, 4096), (8, 6144, 4096), (16, 1000, 512), (17, 520, 264), 
              (16, 4096, 4096), (48, 2048, 12288), (64, 4096, 4096)]
 
 
+@pytest.fixture
+def one_cta_form(ops):
+    """The products of many tokens stay with the one-CTA kernel (the library would hand some to the pair form)."""
+    ops.set_pair_form(False)
+    yield
+    ops.set_pair_form(True)
+
+
 @pytest.mark.parametrize("m,n,k", TC_SHAPES)
-def test_linear_tensor_cores(ops, m, n, k):
+def test_linear_tensor_cores(ops, one_cta_form, m, n, k):
     dtype = torch.bfloat16
     x, w = rnd(m, k, dtype=dtype), rnd(n, k, dtype=dtype, seed=1, std=k ** -0.5)
     bias = rnd(n, dtype=torch.float32, seed=2)
@@ -126,6 +134,48 @@ def test_linear_tensor_cores(ops, m, n, k):
     close(ops.linear(x, w), ref.linear(x, w), dtype)
     close(ops.linear(x, w, bias=bias, residual=res), ref.linear(x, w, bias=bias, residual=res), dtype)
     close(ops.linear(x, w, out_float32=True), ref.linear(x, w, out_float32=True), torch.float32, scale=100.0)
+    ops.check_kernel_status()
+
+
+# the pair form (two CTAs a 256 x 256 tile): one tile, many tiles per cluster, ragged edges in every direction,
+# k loops shorter and longer than the ring of stages, fewer tiles than clusters
+PAIR_SHAPES = [(256, 256, 64), (2048, 4096, 512), (777, 1032, 1096), (1500, 5000, 136), (3100, 2600, 72), (130, 300, 4096),
+               (4096, 6144, 4096), (1, 256, 128), (513, 12288, 256)]
+
+
+@pytest.mark.parametrize("m,n,k", PAIR_SHAPES)
+def test_linear_pair_form(ops, monkeypatch, m, n, k):
+    monkeypatch.setattr(ops, "PAIR_MIN_TOKENS", 1)
+    dtype = torch.bfloat16
+    x, w = rnd(m, k, dtype=dtype), rnd(n, k, dtype=dtype, seed=1, std=k ** -0.5)
+    bias = rnd(n, dtype=torch.float32, seed=2)
+    res = rnd(m, n, dtype=dtype, seed=3)
+    close(ops.linear(x, w), ref.linear(x, w), dtype)
+    close(ops.linear(x, w, bias=bias, residual=res), ref.linear(x, w, bias=bias, residual=res), dtype)
+    close(ops.linear(x, w, out_float32=True), ref.linear(x, w, out_float32=True), torch.float32, scale=100.0)
+    ops.check_kernel_status()
+
+
+def test_products_of_many_tokens_choose_their_form(ops):
+    """Left alone, the library sends a product of 2,048 tokens to the pair form and one of 300 to the one-CTA
+    form; both give what the plain product gives."""
+    dtype = torch.bfloat16
+    for m in (2048, 300):
+        x, w = rnd(m, 512, dtype=dtype), rnd(4096, 512, dtype=dtype, seed=1, std=512 ** -0.5)
+        res = rnd(m, 4096, dtype=dtype, seed=3)
+        close(ops.linear(x, w, residual=res), ref.linear(x, w, residual=res), dtype)
+        wg = rnd(2 * 1536, 512, dtype=dtype, seed=4, std=512 ** -0.5)
+        close(ops.gated_linear(x, wg), ref.gated_linear(x, wg), dtype)
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("m,inter,k", [(256, 128, 64), (300, 448, 320), (2048, 1024, 256), (130, 136, 40), (1500, 2500, 136),
+                                       (3100, 1300, 72), (2048, 12288, 512)])
+def test_gated_linear_pair_form(ops, monkeypatch, m, inter, k):
+    monkeypatch.setattr(ops, "PAIR_MIN_TOKENS", 1)
+    dtype = torch.bfloat16
+    x, w = rnd(m, k, dtype=dtype), rnd(2 * inter, k, dtype=dtype, seed=1, std=k ** -0.5)
+    close(ops.gated_linear(x, w), ref.gated_linear(x, w), dtype)
     ops.check_kernel_status()
 
 
@@ -164,7 +214,7 @@ def test_rmsnorm_shared_between_two_products(ops, m, k0, h, inter, eps):
 
 @pytest.mark.parametrize("m,inter,k", [(1, 12288, 4096), (8, 1000, 512), (20, 448, 320), (64, 100, 96), (65, 176, 96),
                                        (300, 448, 320), (2048, 1024, 256), (130, 72, 40), (1500, 2500, 136), (3100, 1300, 72)])
-def test_gated_linear_tensor_cores(ops, m, inter, k):
+def test_gated_linear_tensor_cores(ops, one_cta_form, m, inter, k):
     dtype = torch.bfloat16
     x, w = rnd(m, k, dtype=dtype), rnd(2 * inter, k, dtype=dtype, seed=1, std=k ** -0.5)
     close(ops.gated_linear(x, w), ref.gated_linear(x, w), dtype)

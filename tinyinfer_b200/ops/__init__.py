@@ -54,7 +54,17 @@ _SIGNATURES["sm100"] = {
                             c_void_p, c_ll, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
                             c_void_p, c_void_p, c_void_p, c_void_p],
 }
+_SIGNATURES["sm100"]["ti_gemm_set_pair_form"] = [c_int]
+_SIGNATURES["sm100"]["ti_gemm_pair_bf16"] = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                             c_int, c_void_p, c_void_p]
 NORM_LINK_MAX_TOKENS = 64   # up to here two products can share an RMSNorm between them (see linear)
+PAIR_MIN_TOKENS = 1 << 30   # tests and measurements: from this many tokens on a product is sent to the pair form (two
+                            # CTAs a 256 x 256 tile) whatever the library would choose; it chooses by itself from 512 on
+
+
+def set_pair_form(allowed: bool) -> None:
+    """Measurements: whether the library may run products of many tokens in the pair form (default: yes)."""
+    _fn("sm100", "ti_gemm_set_pair_form")(1 if allowed else 0)
 _SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
@@ -320,6 +330,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             made = _gemm_linked(out, x, w, bias, residual, m, n, k, 0, (link, link_eps) if link else None,
                                 next_norm_weight)
             return (out, made) if wants_link else out
+    if _tensor_core_ok(x, w) and m >= PAIR_MIN_TOKENS and n >= 256:
+        _run("sm100", "ti_gemm_pair_bf16", out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual),
+             m, n, k, 0, int(out_float32), kernel_status(x.device).data_ptr(), _stream())
+        return (out, None) if wants_link else out
     if _tensor_core_ok(x, w):
         ws, counters = _gemm_scratch(x.device)
         _run("sm100", "ti_gemm_bf16", out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual),
@@ -347,6 +361,10 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, *, link: Optional[Nor
         if not (_tensor_core_ok(x, w_gate_up) and norm_link_ok(x)):
             raise KernelError("gated_linear: a norm link needs the tensor-core product of at most 64 rows")
         _gemm_linked(out, x, w_gate_up, None, None, m, inter, k, 1, (link, link_eps), None)
+        return out
+    if _tensor_core_ok(x, w_gate_up) and m >= PAIR_MIN_TOKENS and inter >= 128:
+        _run("sm100", "ti_gemm_pair_bf16", out.data_ptr(), x.data_ptr(), w_gate_up.data_ptr(), None, None,
+             m, inter, k, 1, 0, kernel_status(x.device).data_ptr(), _stream())
         return out
     if _tensor_core_ok(x, w_gate_up):
         ws, counters = _gemm_scratch(x.device)

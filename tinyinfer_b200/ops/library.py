@@ -37,7 +37,7 @@ LIBRARIES: Dict[str, dict] = {
                  headers=["common.cuh"], link=[]),
     # bfloat16 tensor-core kernels (tcgen05 + TMA); only a bfloat16 model loads it
     "sm100": dict(sources=["runtime.cu", "sm100_host.cu", "gemm_tcgen05.cu", "attention_mma.cu",
-                           "attention_prefill_tcgen05.cu", "attention_prefill_pair_tcgen05.cu"],
+                           "attention_prefill_tcgen05.cu", "attention_prefill_pair_tcgen05.cu", "gemm_pair_tcgen05.cu"],
                   headers=["common.cuh", "sm100_ptx.cuh"], link=[]),
 }
 
