@@ -473,6 +473,32 @@ def test_decode_attention_shares_the_keys_out_evenly(ops, hq, hkv, d, page, wind
     ops.check_kernel_status()
 
 
+@pytest.mark.parametrize("hq,hkv,d,page,window,work", [
+    (4, 2, 128, 64, None, [(5000, 200), (2300, 129)]),          # halves of a 200-row tile and a 129-row tile, shares of 1,024+ keys
+    (2, 1, 64, 16, None, [(9000, 100)]),                         # one tile of 100 rows on 2 CTAs: many shares
+    (4, 4, 128, 128, 3000, [(8000, 256), (4100, 60), (2049, 128)]),   # a window: the first shares hold no visible key
+    (8, 2, 128, 64, None, [(4096, 128), (2048, 2048)])])
+def test_prompt_portions_behind_long_prefixes_share_the_keys_out(ops, monkeypatch, hq, hkv, d, page, window, work):
+    """Few query tiles behind thousands of keys: the keys are split over CTAs and merged. The same results as the
+    plain attention, and as the kernel without the split."""
+    dtype = torch.bfloat16
+    lens = [c for c, _ in work]
+    bt, kv = paged_setup(dtype, lens, hq, hkv, d, page, seed=3)
+    fill_cache(kv, bt, lens, hkv, d, page, dtype)
+    pos = torch.tensor([p for c, n in work for p in range(c - n, c)], dtype=torch.int32, device=dev())
+    seq = torch.tensor([i for i, (c, n) in enumerate(work) for _ in range(n)], dtype=torch.int32, device=dev())
+    q = rnd(pos.shape[0], hq, d, dtype=dtype, seed=7)
+    args = dict(positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5, window=window)
+    monkeypatch.setattr(ops, "PAIR_MIN_CTAS", 1 << 30)           # the one-tile kernel takes everything
+    split = ops.paged_attention(q, kv, **args)
+    monkeypatch.setattr(ops, "KEY_SPLIT_MAX_CTAS", 0)
+    whole = ops.paged_attention(q, kv, **args)
+    assert torch.isfinite(split.float()).all()
+    close(split, ref.paged_attention(q, kv, **args), dtype)
+    close(split, whole, dtype)
+    ops.check_kernel_status()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("d,page,window,ctx,far", [(64, 16, None, 700, 3), (128, 64, None, 900, 64),
                                                    (32, 8, 100, 500, 400), (128, 64, 256, 1000, 744),

@@ -32,6 +32,9 @@ struct PrefillParams {
     const int* block_table;
     int max_blocks, hq, hkv, page_size, num_pages, window;
     int halves;                      // 1: a tile entry has up to 256 rows and two CTAs take 128 each
+    int splits, split_keys;          // > 1: CTA z of a tile takes keys z * split_keys .. (a multiple of 128) and leaves a partial
+    float* part_o;                   // [128-row tile][split][head][row][D] unnormalised outputs
+    float* part_ml;                  // [128-row tile][split][head][row][2] maximum (log2 domain) and sum
     float scale_log2;
     int* status;
 };
@@ -114,12 +117,19 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int kvh = head / (p.hq / p.hkv);
     const int hi = pos0 + nrows;                                   // one past the last key any query sees
     const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0; // first key the first query sees
-    const int tile0 = lo / KT, tile1 = (hi + KT - 1) / KT;
+    // With a split of the keys (few query tiles behind long prefixes: too few CTAs otherwise) this CTA takes the
+    // key tiles of its share only and leaves an unnormalised partial result for the merge kernel.
+    int tile0 = lo / KT, tile1 = (hi + KT - 1) / KT;
+    if (p.splits > 1) {
+        tile0 = max(tile0, (int)blockIdx.z * (p.split_keys / KT));
+        tile1 = min(tile1, ((int)blockIdx.z + 1) * (p.split_keys / KT));
+    }
     const int num_tiles = tile1 - tile0;
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
 
-    if (nrows <= 0) {
-        // the second half of an entry of at most 128 rows: nothing to do but the common exit
+    if (nrows <= 0 || num_tiles <= 0) {
+        // the second half of an entry of at most 128 rows, or a share of the keys this tile has none of:
+        // nothing to do but the common exit
     } else if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         // A tile is KT / piece_rows pieces (a piece lies in one page) x head halves x (keys, values): up to
@@ -328,10 +338,21 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 const float l_all = l_run + sum_xch[half ^ 1][r];
                 const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
                 __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.hq + head) * D + half * DH;
+                const size_t part = (((size_t)blockIdx.y * p.splits + blockIdx.z) * p.hq + head) * QM + r;
+                if (p.splits > 1 && half == 0 && r < nrows)
+                    *reinterpret_cast<float2*>(p.part_ml + part * 2) = make_float2(m_run, l_all);
 #pragma unroll
                 for (int c = 0; c < DH; c += 32) {
                     tmem_ld32(lane_addr + 2 * KT + half * DH + c, v);
-                    if (r < nrows) {
+                    if (p.splits > 1) {
+                        if (r < nrows) {
+                            float4* po = reinterpret_cast<float4*>(p.part_o + part * D + half * DH + c);
+#pragma unroll
+                            for (int q4 = 0; q4 < 8; ++q4)
+                                po[q4] = make_float4(o[c + q4 * 4] + v[q4 * 4], o[c + q4 * 4 + 1] + v[q4 * 4 + 1],
+                                                     o[c + q4 * 4 + 2] + v[q4 * 4 + 2], o[c + q4 * 4 + 3] + v[q4 * 4 + 3]);
+                        }
+                    } else if (r < nrows) {
 #pragma unroll
                         for (int q8 = 0; q8 < 4; ++q8) {
                             uint4 w;
@@ -356,6 +377,36 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     }
 }
 
+// Merges the partial results of a split of the keys: one block per (query row of a tile, head), one thread
+// per feature, the shares in key order. A share the tile has no keys in was not computed and is not read.
+template <int D>
+__global__ void prefill_merge_kernel(const PrefillParams p) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int slot = blockIdx.x / QM, r = blockIdx.x % QM, head = blockIdx.y, d = threadIdx.x;
+    const int4 td = reinterpret_cast<const int4*>(p.tiles)[p.halves ? slot >> 1 : slot];
+    const int half_off = p.halves ? (slot & 1) * QM : 0;
+    const int row0 = td.y + half_off, pos0 = td.w + half_off;
+    const int nrows = min(td.z - half_off, QM);
+    if (r >= nrows) return;
+    const int hi = pos0 + nrows;
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int tile0 = lo / KT, tile1 = (hi + KT - 1) / KT, per = p.split_keys / KT;
+    float m_run = -INFINITY, acc = 0.f, l_all = 0.f;
+    for (int z = tile0 / per; z < p.splits && z * per < tile1; ++z) {
+        const size_t part = (((size_t)slot * p.splits + z) * p.hq + head) * QM + r;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + part * 2));
+        const float ov = __ldcg(p.part_o + part * D + d);
+        const float m_new = fmaxf(m_run, ml.x);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float keep = ex2(m_run - m_use), f = ex2(ml.x - m_use);      // 0 while nothing has been merged yet
+        acc = acc * keep + f * ov;
+        l_all = l_all * keep + f * ml.y;
+        m_run = m_new;
+    }
+    p.out[((size_t)(row0 + r) * p.hq + head) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+}
+
 }  // namespace
 
 TI_API int ti_attention_prefill_tile_rows() { return QM; }
@@ -365,10 +416,22 @@ TI_API int ti_attention_prefill_tile_rows() { return QM; }
 // out [T, Hq * D], kv_cache [2, num_pages, Hkv, page_size, D]; page_size 16, 32 or a multiple of 64.
 // With `halves` a tile entry has up to 256 rows (the form the two-tile kernel takes) and two CTAs take
 // 128 rows each: for steps whose entries are too few to fill the machine with one CTA each.
+// splits > 1: the keys are shared out too, split_keys (a multiple of 128) to a CTA, for few query tiles behind long
+// prefixes; the partial results go through `scratch` (scratch_floats >= ti_attention_prefill_scratch_floats(...))
+// and a second kernel merges them in key order.
+TI_API long long ti_attention_prefill_scratch_floats(int num_tiles, int halves, int splits, int hq, int d) {
+    return (long long)num_tiles * (halves ? 2 : 1) * splits * hq * QM * (d + 2);
+}
 TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
                                         int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
-                                        int page_size, int num_pages, float scale, int window, int halves, int* status,
+                                        int page_size, int num_pages, float scale, int window, int halves, int splits,
+                                        int split_keys, float* scratch, long long scratch_floats, int* status,
                                         cudaStream_t stream) {
+    TI_REQUIRE(splits >= 1 && splits <= 65535, "attention_prefill_tc: %d shares of the keys", splits);
+    TI_REQUIRE(splits == 1 || (split_keys > 0 && split_keys % KT == 0 && scratch != nullptr &&
+                               scratch_floats >= ti_attention_prefill_scratch_floats(num_tiles, halves, splits, hq, d)),
+               "attention_prefill_tc: a split of the keys needs shares of a multiple of %d keys and %lld floats of scratch",
+               KT, ti_attention_prefill_scratch_floats(num_tiles, halves, splits, hq, d));
     TI_REQUIRE(d == 64 || d == 128, "attention_prefill_tc: head_dim %d is not 64 or 128", d);
     TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_tc: bad head counts");
     TI_REQUIRE(num_tiles <= 32767, "attention_prefill_tc: more than 32767 tiles in one step");
@@ -382,7 +445,10 @@ TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
     p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.halves = halves ? 1 : 0;
-    dim3 grid(hq, halves ? 2 * num_tiles : num_tiles);
+    const int slots = halves ? 2 * num_tiles : num_tiles;
+    p.splits = splits; p.split_keys = split_keys;
+    p.part_o = scratch; p.part_ml = scratch ? scratch + (long long)slots * splits * hq * QM * d : nullptr;
+    dim3 grid(hq, slots, splits);
     if (d == 128) {
         static bool once = false;
         if (!once) {
@@ -401,5 +467,10 @@ TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv
         ti_launch(prefill_attention_tc_kernel<64>, grid, PF_THREADS, PfSmem<64>::BYTES, stream, q_map, kv_map, p);
     }
     TI_CHECK_LAUNCH("attention_prefill_tc");
+    if (splits > 1) {
+        if (d == 128) ti_launch(prefill_merge_kernel<128>, dim3(slots * QM, hq), 128, 0, stream, p);
+        else ti_launch(prefill_merge_kernel<64>, dim3(slots * QM, hq), 64, 0, stream, p);
+        TI_CHECK_LAUNCH("attention_prefill_merge");
+    }
     return 0;
 }

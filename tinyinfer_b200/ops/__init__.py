@@ -74,9 +74,10 @@ _SIGNATURES["sm100"]["ti_attention_prefill_pair_bf16"] = [
     c_float, c_int, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_prefill_tc_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-    c_float, c_int, c_int, c_void_p, c_void_p]
+    c_float, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p]
 PREFILL_TILE = 256        # most query rows per CTA of the prefill attention kernels (two tiles of 128)
 PAIR_MIN_CTAS = 148       # fewer CTAs than this of the two-tile kernel: its tiles run as halves, one a CTA
+KEY_SPLIT_MAX_CTAS = 148  # at most half as many CTAs of the one-tile kernel: the keys are shared out over CTAs as well
 _bound = {}
 _status = {}
 
@@ -599,18 +600,31 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
              scratch.data_ptr(), scratch.numel(), decode_rows.data_ptr(), num_decode, positions.data_ptr(),
              token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), int(max_context), kstatus, _stream())
+    def one_tile_kernel(first: int, count: int, halves: int) -> None:
+        # Few query tiles behind a long prefix: the keys are shared out over CTAs too (at least 1,024 to a CTA),
+        # so that most SMs have a CTA; their partial results meet in a merge kernel.
+        ctas = count * (2 if halves else 1) * hq
+        splits = 1
+        if ctas * 2 <= KEY_SPLIT_MAX_CTAS and max_context >= 2048:
+            splits = max(1, min(KEY_SPLIT_MAX_CTAS // ctas, int(max_context) // 1024))
+        split_keys = -(-(-(-int(max_context) // splits)) // 128) * 128 if splits > 1 else 0
+        scratch_ptr, scratch_floats = None, 0
+        if splits > 1:
+            scratch = _decode_scratch(q.device, count * (2 if halves else 1) * splits * hq * 128 * (d + 2))
+            scratch_ptr, scratch_floats = scratch.data_ptr(), scratch.numel()
+        _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
+             tiles.data_ptr() + 16 * first, count, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
+             num_pages, float(scale), int(window or 0), halves, splits, split_keys, scratch_ptr, scratch_floats, kstatus,
+             _stream())
+
     if num_pairs * hq >= PAIR_MIN_CTAS:             # two query tiles a CTA
         _run("sm100", "ti_attention_prefill_pair_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              tiles.data_ptr(), num_pairs, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), kstatus, _stream())
     elif num_pairs:                                 # too few of them to fill the machine: one query tile a CTA
-        _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
-             tiles.data_ptr(), num_pairs, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
-             num_pages, float(scale), int(window or 0), 1, kstatus, _stream())
+        one_tile_kernel(0, num_pairs, 1)
     if num_tiles > num_pairs:                       # ends of portions of at most 128 rows
-        _run("sm100", "ti_attention_prefill_tc_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
-             tiles.data_ptr() + 16 * num_pairs, num_tiles - num_pairs, t, block_table.data_ptr(), block_table.shape[1],
-             hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), 0, kstatus, _stream())
+        one_tile_kernel(num_pairs, num_tiles - num_pairs, 0)
     return out
 
 
