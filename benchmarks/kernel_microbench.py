@@ -6,6 +6,7 @@ few layers: the workload for per-kernel rooflines and for profiler captures.
     python benchmarks/kernel_microbench.py --kernel gated_gemm --m 2048 --n 12288 --k 4096
     python benchmarks/kernel_microbench.py --kernel attention_decode --batch 8 --context 4096
     python benchmarks/kernel_microbench.py --kernel attention_prefill --tokens 2048
+    python benchmarks/kernel_microbench.py --kernel rope_append --tokens 2048
     python benchmarks/kernel_microbench.py --kernel decode_step --batch 8 --context 4096 --layers 4
     python benchmarks/kernel_microbench.py --kernel prefill_step --tokens 2048 --layers 4
 
@@ -62,7 +63,7 @@ def graph_time(fn, iters, use_graph=True):
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--kernel", required=True, choices=["gemm", "gated_gemm", "attention_decode", "attention_prefill",
-                                                       "rmsnorm", "decode_step", "prefill_step"])
+                                                       "rmsnorm", "rope_append", "decode_step", "prefill_step"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -116,6 +117,20 @@ def main():
         w = torch.ones(a.n, device=dev)
         us = graph_time(lambda: ops.rmsnorm(x, w, 1e-6), a.iters, not a.no_graph)
         out.update(rows=a.m, size=a.n, us=us, gbs=2 * a.m * a.n * 2 / us / 1e3, tflops=0.0)
+    elif a.kernel == "rope_append":
+        hq, hkv, d, page, t = a.heads, a.kv_heads, a.head_dim, a.page_size, a.tokens
+        qkv = torch.randn(t, (hq + 2 * hkv) * d, device=dev).bfloat16()
+        pages = (t + page - 1) // page
+        kv = torch.zeros(2, pages + 1, hkv, page, d, device=dev).bfloat16()
+        bt = torch.arange(pages, dtype=torch.int32, device=dev)[None, :].contiguous()
+        pos = torch.arange(t, dtype=torch.int32, device=dev)
+        seq = torch.zeros(t, dtype=torch.int32, device=dev)
+        w = torch.ones(d, device=dev)
+        inv_freq = (1e6 ** (-torch.arange(0, d, 2, device=dev).float() / d)).contiguous()
+        us = graph_time(lambda: ops.qk_norm_rope_append(
+            qkv, num_heads=hq, num_kv_heads=hkv, head_dim=d, q_norm_weight=w, k_norm_weight=w, eps=1e-6, positions=pos,
+            token_seq=seq, kv_cache=kv, block_table=bt, inv_freq=inv_freq, rotary_dim=d), a.iters, not a.no_graph)
+        out.update(tokens=t, us=us, gbs=2 * t * (hq + 2 * hkv) * d * 2 / us / 1e3, tflops=0.0)
     elif a.kernel in ("attention_decode", "attention_prefill"):
         hq, hkv, d, page = a.heads, a.kv_heads, a.head_dim, a.page_size
         if a.kernel == "attention_decode":
