@@ -29,7 +29,9 @@
 // two tiles at the exponentials, an issuing warp per tile (polling or sleeping), sleeping between polls; and
 // steps of 64 keys with two score buffers a query tile, so that the next scores are ready before a step's
 // softmax ends (8,192 tokens 753 us against 560: the score products of 64 keys take in 192 bytes of
-// operands a cycle from shared memory, which gives 128, and every step pays its hand-overs twice).
+// operands a cycle from shared memory, which gives 128, and every step pays its hand-overs twice); and a
+// share of the exponentials as a polynomial of degree 5 on the FMA pipe (every fourth: 547 us, every
+// eighth: 576, every second: 690; the softmax warps are short of issue slots as much as of the XU pipe).
 //
 // Masked scores never reach an exponential (P is assigned 0 there), rows of V that no query of the CTA
 // may see are zeroed in shared memory before the second product (pages never written or given back cannot
