@@ -195,6 +195,47 @@ def test_widths_of_the_benchmark_model_in_every_cut(benchmark_sized_model, dtype
         del got, session
 
 
+LONG = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=1031, hidden_size=1024,
+    num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+    intermediate_size=3072, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_bias=False,
+    tie_word_embeddings=False, max_position_embeddings=4096)
+
+
+def test_long_prompts_on_the_kernels_for_many_tokens(tmp_path):
+    """Prompts of hundreds and thousands of tokens in large portions, in bfloat16: the steps in which the products
+    run in the pair form (512 tokens and more), prompt attention with two query tiles a CTA (1,290 tokens x 32
+    heads of 64), its tiles as halves (590 tokens), and with the keys shared out over CTAs (250 tokens behind
+    1,950), next to single decoded tokens. Logits at the ends of the portions and of every decoded token
+    against the plain implementation."""
+    from tinyinfer_b200.engine.replay import TraceSession
+    folder = helpers.make_model_folder(tmp_path / "m", LONG, seed=9, dtype="float32", std=0.03)
+    requests = helpers.random_requests(LONG, [1300, 600, 2200], seed=5)
+    want = helpers.plain_logits(folder, requests, matrices_as=torch.bfloat16)
+    a, b, c = (requests[r] for r in requests)
+    ra, rb, rc = list(requests)
+    ends = lambda n: [n - 2, n - 1]
+    steps = [
+        {"step": 0, "entries": [{"id": ra, "tokens": a[:1290], "want": [0, 511, 1000, 1289]}], "end": []},
+        {"step": 1, "entries": [{"id": ra, "tokens": a[1290:1291], "want": [0]},
+                                {"id": rb, "tokens": b[:590], "want": [5, 589]}], "end": []},
+        {"step": 2, "entries": [{"id": ra, "tokens": a[1291:1292], "want": [0]},
+                                {"id": rb, "tokens": b[590:591], "want": [0]},
+                                {"id": rc, "tokens": c[:1950], "want": [1949]}], "end": []},
+        {"step": 3, "entries": [{"id": rc, "tokens": c[1950:], "want": [0, 100, 249]},
+                                {"id": ra, "tokens": a[1292:1293], "want": [0]}], "end": []},
+        {"step": 4, "entries": [{"id": ra, "tokens": a[1293:], "want": ends(7)},
+                                {"id": rb, "tokens": b[591:], "want": ends(9)}], "end": [ra, rb, rc]},
+    ]
+    session = TraceSession(folder, "bfloat16", helpers.peak_tokens(steps), page_size=64, poison_cache=True)
+    got = helpers.collect(session, steps)
+    session.runner.check_status()
+    bad = helpers.first_bad(got, want, TOL["bfloat16"])
+    assert bad is None, bad
+    assert sum(len(v) for v in got.values()) == sum(len(e["want"]) for st in steps for e in st["entries"])
+    session.runner.manager.check_consistency()
+
+
 def run_trace_program(folder, dtype, out, steps, max_tokens, page_size=16):
     cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
            "--out", str(out), "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
