@@ -7,6 +7,7 @@ few layers: the workload for per-kernel rooflines and for profiler captures.
     python benchmarks/kernel_microbench.py --kernel attention_decode --batch 8 --context 4096
     python benchmarks/kernel_microbench.py --kernel attention_prefill --tokens 2048
     python benchmarks/kernel_microbench.py --kernel rope_append --tokens 2048
+    python benchmarks/kernel_microbench.py --kernel sample --batch 64 --topk 100
     python benchmarks/kernel_microbench.py --kernel decode_step --batch 8 --context 4096 --layers 4
     python benchmarks/kernel_microbench.py --kernel prefill_step --tokens 2048 --layers 4
 
@@ -63,7 +64,9 @@ def graph_time(fn, iters, use_graph=True):
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--kernel", required=True, choices=["gemm", "gated_gemm", "attention_decode", "attention_prefill",
-                                                       "rmsnorm", "rope_append", "decode_step", "prefill_step"])
+                                                       "rmsnorm", "rope_append", "sample", "decode_step", "prefill_step"])
+    ap.add_argument("--topk", type=int, default=0, help="sample: top-k of every row (0: none; -1: every row greedy)")
+    ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -117,6 +120,17 @@ def main():
         w = torch.ones(a.n, device=dev)
         us = graph_time(lambda: ops.rmsnorm(x, w, 1e-6), a.iters, not a.no_graph)
         out.update(rows=a.m, size=a.n, us=us, gbs=2 * a.m * a.n * 2 / us / 1e3, tflops=0.0)
+    elif a.kernel == "sample":
+        n, v = a.batch, a.vocab
+        logits = torch.randn(n, v, device=dev) * 3.0
+        temp = torch.full((n,), 0.7, device=dev)
+        topk = torch.full((n,), max(a.topk, 0), dtype=torch.int32, device=dev)
+        greedy = torch.full((n,), 1 if a.topk < 0 else 0, dtype=torch.int32, device=dev)
+        seed = torch.arange(n, dtype=torch.int64, device=dev)
+        stream_id = torch.arange(n, dtype=torch.int32, device=dev)
+        step = torch.zeros(n, dtype=torch.int32, device=dev)
+        us = graph_time(lambda: ops.sample(logits, temp, topk, greedy, seed, stream_id, step), a.iters, not a.no_graph)
+        out.update(rows=n, vocab=v, topk=a.topk, us=us, gbs=n * v * 4 / us / 1e3, tflops=0.0)
     elif a.kernel == "rope_append":
         hq, hkv, d, page, t = a.heads, a.kv_heads, a.head_dim, a.page_size, a.tokens
         qkv = torch.randn(t, (hq + 2 * hkv) * d, device=dev).bfloat16()

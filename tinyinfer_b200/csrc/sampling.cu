@@ -105,7 +105,10 @@ __device__ __forceinline__ void for_each_logit(const float* x, int vocab, int be
 
 // Radix select, one byte per pass from the top: the k-th largest of the keys that `each` hands out (it calls
 // its argument once per key; every thread of the block calls select_kth with the same k). 0 if k <= 0.
-// hist: 256 shared words; sel: 2 shared words.
+// hist: 256 shared words; sel: 2 shared words. The counts of a pass go into the histogram warp by warp: lanes
+// that hold the same byte count themselves once together (most logits share their sign and exponent, so a
+// plain atomic per key would make a warp wait for itself 32 times over); the bin that holds the k-th largest
+// is found by the first warp together (a suffix sum over lanes of eight bins each), not by one thread.
 template <typename Each>
 __device__ __forceinline__ unsigned select_kth(int k, unsigned* hist, unsigned* sel, Each each) {
     if (k <= 0) return 0u;
@@ -116,17 +119,45 @@ __device__ __forceinline__ unsigned select_kth(int k, unsigned* hist, unsigned* 
         __syncthreads();
         const unsigned prefix = sel[0];
         const unsigned mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-        each([&](unsigned key) { if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u); });
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned remaining = sel[1];
-            int b = 255;
-            for (; b > 0; --b) {
-                if (hist[b] >= remaining) break;
-                remaining -= hist[b];
+        each([&](unsigned key) {
+            if ((key & mask) == prefix) {
+                const unsigned bin = (key >> shift) & 0xFFu;
+                const unsigned same = __match_any_sync(__activemask(), bin);
+                if ((threadIdx.x & 31) == (unsigned)(__ffs(same) - 1)) atomicAdd(&hist[bin], (unsigned)__popc(same));
             }
-            sel[0] = prefix | ((unsigned)b << shift);
-            sel[1] = remaining;
+        });
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            const int lane = threadIdx.x;
+            unsigned mine[8], sum = 0u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { mine[i] = hist[8 * lane + i]; sum += mine[i]; }
+            unsigned above = sum;                                  // keys in this lane's bins and all higher ones
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const unsigned v = __shfl_down_sync(0xffffffffu, above, off);
+                if (lane + off < 32) above += v;
+            }
+            const unsigned remaining = sel[1];
+            // the highest lane whose bins, with all above them, reach the k-th largest; lane 0 if none does
+            const unsigned reach = __ballot_sync(0xffffffffu, above >= remaining);
+            const int owner = reach ? 31 - __clz(reach) : 0;
+            if (lane == owner) {
+                unsigned left = remaining - (above - sum);         // still to find inside this lane's bins
+                int b = 7;
+                if (reach) {
+                    for (; b > 0; --b) {
+                        if (mine[b] >= left) break;
+                        left -= mine[b];
+                    }
+                } else {
+                    b = 0;                                         // fewer keys than k: bin 0, as the plain walk does
+                    left = remaining;
+                    for (int i = 255; i > 0; --i) left -= hist[i];
+                }
+                sel[0] = prefix | ((unsigned)(8 * lane + b) << shift);
+                sel[1] = left;
+            }
         }
         __syncthreads();
     }
@@ -268,17 +299,31 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_parts_kernel(
     if (is_greedy || !top) {
         if (tid < SMP_PARTS) m = Best{__ldcg(part_val + row * SMP_PARTS + tid), __ldcg(part_idx + row * SMP_PARTS + tid)};
     } else {
-        bool whole = k > SMP_CAP;
-        int total = 0;
-        if (!whole) {
+        // all parts' counts in one trip, then all candidates in one
+        __shared__ int start_sh[SMP_PARTS + 1];
+        if (tid == 0) {
+            int n[SMP_PARTS];
+#pragma unroll
+            for (int pp = 0; pp < SMP_PARTS; ++pp) n[pp] = k > SMP_CAP ? -1 : __ldcg(cand_cnt + row * SMP_PARTS + pp);
+            int total0 = 0;
+            bool over = false;
+#pragma unroll
             for (int pp = 0; pp < SMP_PARTS; ++pp) {
-                const int n = __ldcg(cand_cnt + row * SMP_PARTS + pp);
-                if (n < 0) { whole = true; break; }
-                for (int i = tid; i < n; i += SMP_THREADS) {
-                    keys_sh[total + i] = __ldcg(cand_key + ((size_t)row * SMP_PARTS + pp) * SMP_CAP + i);
-                    idx_sh[total + i] = __ldcg(cand_idx + ((size_t)row * SMP_PARTS + pp) * SMP_CAP + i);
+                start_sh[pp] = total0;
+                if (n[pp] < 0) over = true; else total0 += n[pp];
+            }
+            start_sh[SMP_PARTS] = over ? -1 : total0;
+        }
+        __syncthreads();
+        const int total = start_sh[SMP_PARTS];
+        const bool whole = total < 0;
+        if (!whole) {
+            for (int i = tid; i < SMP_PARTS * SMP_CAP; i += SMP_THREADS) {
+                const int pp = i / SMP_CAP, at = i % SMP_CAP;
+                if (at < start_sh[pp + 1 < SMP_PARTS ? pp + 1 : SMP_PARTS] - start_sh[pp]) {
+                    keys_sh[start_sh[pp] + at] = __ldcg(cand_key + ((size_t)row * SMP_PARTS + pp) * SMP_CAP + at);
+                    idx_sh[start_sh[pp] + at] = __ldcg(cand_idx + ((size_t)row * SMP_PARTS + pp) * SMP_CAP + at);
                 }
-                total += n;
             }
         }
         __syncthreads();
