@@ -473,6 +473,79 @@ def test_decode_attention_shares_the_keys_out_evenly(ops, hq, hkv, d, page, wind
     ops.check_kernel_status()
 
 
+def test_attention_at_random_sizes(ops):
+    """Thirty batches drawn at random (a fixed seed): head counts and groups, head size, page size, windows,
+    contexts from one key to a few thousand, single decoded tokens next to prompt portions of every length, more
+    decoded rows than the decode kernel has threads: every one against the plain attention."""
+    import random
+    rng = random.Random(20)
+    dtype = torch.bfloat16
+    for case in range(30):
+        d = rng.choice([64, 128])
+        hkv = rng.choice([1, 2, 3, 8])
+        group = rng.choice([1, 2, 4, 5, 8, 16])
+        hq = hkv * group
+        page = rng.choice([16, 32, 64, 128])
+        window = rng.choice([None, None, rng.randrange(1, 700)])
+        work = []
+        if case % 5 == 0:                                   # many decoded rows
+            work += [(rng.randrange(1, 400), 1) for _ in range(rng.choice([170, 200, 330]))]
+        else:
+            for _ in range(rng.randrange(1, 7)):
+                ctx = rng.choice([1, 2, 63, 64, 65, 127, 128, 129, 255, 256, 257, rng.randrange(1, 3000)])
+                n = rng.choice([1, 1, 1, ctx, min(ctx, 2), min(ctx, 128), min(ctx, 129), min(ctx, 256), min(ctx, 257),
+                                rng.randrange(1, ctx + 1)])
+                work.append((ctx, n))
+        lens = [c for c, _ in work]
+        bt, kv = paged_setup(dtype, lens, hq, hkv, d, page, seed=case)
+        fill_cache(kv, bt, lens, hkv, d, page, dtype)
+        pos = torch.tensor([p for c, n in work for p in range(c - n, c)], dtype=torch.int32, device=dev())
+        seq = torch.tensor([i for i, (c, n) in enumerate(work) for _ in range(n)], dtype=torch.int32, device=dev())
+        q = rnd(pos.shape[0], hq, d, dtype=dtype, seed=100 + case)
+        args = dict(positions=pos, token_seq=seq, block_table=bt, scale=d ** -0.5, window=window)
+        for pair_min in (0, 148):
+            ops.PAIR_MIN_CTAS = pair_min
+            try:
+                out = ops.paged_attention(q, kv, **args)
+            finally:
+                ops.PAIR_MIN_CTAS = 148
+            assert torch.isfinite(out.float()).all(), (case, work[:6], hq, hkv, d, page, window)
+            want = ref.paged_attention(q, kv, **args)
+            err = (out.float() - want.float()).abs().max().item()
+            assert err < 3e-2, (case, err, work[:6], hq, hkv, d, page, window, pair_min)
+    ops.check_kernel_status()
+
+
+def test_products_at_random_sizes(ops):
+    """Forty products drawn at random (a fixed seed), plain and gated, with and without bias and residual, in
+    whichever form the library chooses and in the pair form: against the plain product."""
+    import random
+    rng = random.Random(21)
+    dtype = torch.bfloat16
+    for case in range(40):
+        m = rng.choice([1, 7, 16, 33, 64, 65, 100, 128, 129, 300, 511, 512, 513, 700, 1024, 1300, 2050])
+        n = rng.choice([128, 136, 256, 264, 520, 1000, 1024, 2048, 3080])
+        k = rng.choice([8, 64, 72, 136, 512, 1096])
+        gated = case % 3 == 0
+        x = rnd(m, k, dtype=dtype, seed=case)
+        w = rnd(2 * n if gated else n, k, dtype=dtype, seed=1000 + case, std=k ** -0.5)
+        for force_pair in (False, True):
+            if force_pair and (2 * n if gated else n) < 256:
+                continue
+            ops.PAIR_MIN_TOKENS = 1 if force_pair else 1 << 30
+            try:
+                if gated:
+                    got, want = ops.gated_linear(x, w), ref.gated_linear(x, w)
+                else:
+                    bias = rnd(n, dtype=torch.float32, seed=2) if case % 2 else None
+                    res = rnd(m, n, dtype=dtype, seed=3) if case % 4 < 2 else None
+                    got, want = ops.linear(x, w, bias=bias, residual=res), ref.linear(x, w, bias=bias, residual=res)
+            finally:
+                ops.PAIR_MIN_TOKENS = 1 << 30
+            close(got, want, dtype)
+    ops.check_kernel_status()
+
+
 @pytest.mark.parametrize("hq,hkv,d,page,window,work", [
     (4, 2, 128, 64, None, [(5000, 200), (2300, 129)]),          # halves of a 200-row tile and a 129-row tile, shares of 1,024+ keys
     (2, 1, 64, 16, None, [(9000, 100)]),                         # one tile of 100 rows on 2 CTAs: many shares
