@@ -23,7 +23,9 @@
 // cycles): a tile's softmax takes 2,200 cycles (scores in 90, maxima 280, exponentials 1,300 against 1,024
 // at the rate of the XU pipe, P out and fenced 300), its two products 1,100 (1,024 at the tensor rate), and
 // 400 go by before the issuing thread notices that P is there (a look at an mbarrier whose phase is not
-// complete costs it that much). The two tiles run out of step by themselves. Tried on this form, none
+// complete costs it that much). The two tiles run out of step by themselves. Those figures are from before
+// the issuing thread's descriptors were made once instead of per MMA: its own instructions were a good part
+// of the 1,100 (8,192 tokens 560 -> 530 us). Tried on this form, none
 // faster: the issuing thread watching plain counters instead of mbarriers (the tiles then fall into step:
 // both in their exponentials, then both waiting for products), P handed over in two halves, turns of the
 // two tiles at the exponentials, an issuing warp per tile (polling or sleeping), sleeping between polls; and
@@ -221,25 +223,34 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
             auto users = [&](int j) { return (j >= t0x[0] && j < t1x[0] ? 1 : 0) + (j >= t0x[1] && j < t1x[1] ? 1 : 0); };
             auto issued = [&](const int* next, int j) { return (j >= t0x[0] && j < t1x[0] && next[0] > j ? 1 : 0) +
                                                                (j >= t0x[1] && j < t1x[1] && next[1] > j ? 1 : 0); };
+            // This one thread's instructions are what the tensor cores wait for between products (a descriptor made
+            // from an address costs it as much as the MMA it describes costs the tensor pipe), so the descriptors
+            // of the two query tiles and of the four key/value buffers are made once: a k step then is an addition.
+            const uint64_t q_desc[2] = {make_sw128_desc(smem_u32(q_tiles)), make_sw128_desc(smem_u32(q_tiles) + S::Q_BYTES)};
+            uint64_t k_desc[NBUF], v_desc[NBUF];
+#pragma unroll
+            for (int b = 0; b < NBUF; ++b) {
+                k_desc[b] = make_sw128_desc(smem_u32(kv_ring + b * S::KV_TILE));
+                v_desc[b] = make_sw128_desc_mn(smem_u32(kv_ring + b * S::KV_TILE), KT * 128, 1024);
+            }
+            auto pick = [&](const uint64_t* d, int b) { return b == 0 ? d[0] : (b == 1 ? d[1] : (b == 2 ? d[2] : d[3])); };
             while (ok && (jp[0] < t1x[0] || jp[1] < t1x[1])) {
                 bool moved = false;
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
-                    const uint32_t q_addr = smem_u32(q_tiles) + x * S::Q_BYTES;
                     const uint32_t s_tmem = tmem_base + x * KT, o_tmem = tmem_base + 2 * KT + x * D;
                     if (jp[x] < js[x]) {                                   // P V of tile jp: P written, V landed
                         const int j = jp[x], li = 2 * (j - tmin) + 1, b = li % NBUF;
                         if (mbar_test_wait(p_full(x), (j - t0x[x]) & 1u) && mbar_test_wait(kv_full(b), (li / NBUF) & 1u)) {
                             tmem_fence_after();
-                            const uint32_t v_addr = smem_u32(kv_ring + b * S::KV_TILE);
+                            const uint64_t vd = pick(v_desc, b);
+                            // A: 16 keys = 8 columns of packed bfloat16 pairs (P lies over the first 64 of the
+                            // tile's 128 score columns); B: 16 key rows of V = 2048 bytes further on (128 in the
+                            // descriptor's 16-byte units)
+                            umma_bf16_tmem_a(o_tmem, s_tmem, vd, idesc_o, j > t0x[x] ? 1u : 0u);
 #pragma unroll
-                            for (int ks = 0; ks < KT / 16; ++ks) {
-                                // A: 16 keys = 8 columns of packed bfloat16 pairs (P lies over the first 64 of the
-                                // tile's 128 score columns); B: 16 key rows of V = 2048 bytes
-                                const uint64_t bdesc = make_sw128_desc_mn(v_addr + ks * 16 * 128, KT * 128, 1024);
-                                umma_bf16_tmem_a(o_tmem, s_tmem + ks * 8, bdesc, idesc_o,
-                                                 (j > t0x[x] || ks > 0) ? 1u : 0u);
-                            }
+                            for (int ks = 1; ks < KT / 16; ++ks)
+                                umma_bf16_tmem_a(o_tmem, s_tmem + ks * 8, vd + (uint64_t)(ks * 128), idesc_o, 1u);
                             umma_commit(o_full(x));
                             ++jp[x];
                             if (issued(jp, j) == users(j)) umma_commit(kv_empty(b));   // both tiles have read these values
@@ -250,11 +261,12 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
                         const int j = js[x], li = 2 * (j - tmin), b = li % NBUF;
                         if (mbar_test_wait(kv_full(b), (li / NBUF) & 1u)) {
                             tmem_fence_after();
-                            const uint32_t k_addr = smem_u32(kv_ring + b * S::KV_TILE);
+                            const uint64_t kd = pick(k_desc, b), qd = q_desc[x];
 #pragma unroll
                             for (int ks = 0; ks < D / 16; ++ks) {
-                                const uint32_t off = (ks >> 2) * (QM * 128) + (ks & 3) * 32;     // half, then 32 bytes a step
-                                umma_bf16(s_tmem, make_sw128_desc(q_addr + off), make_sw128_desc(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
+                                // half of the head, then 32 bytes a step: in the descriptor's 16-byte units
+                                const uint64_t off = (uint64_t)(((ks >> 2) * (QM * 128) + (ks & 3) * 32) >> 4);
+                                umma_bf16(s_tmem, qd + off, kd + off, idesc_s, ks > 0 ? 1u : 0u);
                             }
                             umma_commit(s_full(x));
                             ++js[x];
