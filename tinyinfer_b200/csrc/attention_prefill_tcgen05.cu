@@ -173,19 +173,27 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc(QM, KT);               // S = Q K^T: both operands K-major
             constexpr uint32_t idesc_o = make_idesc(QM, D, true);          // O = P V: V is MN-major (features contiguous)
-            const uint32_t q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
+            // the descriptors are made once (this one thread's instructions are what the tensor cores wait for
+            // between products): a k step is an addition to them, in the descriptors' 16-byte units
+            const uint64_t q_desc = make_sw128_desc(smem_u32(q_tile)), p_desc = make_sw128_desc(smem_u32(p_tile));
+            static_assert(KV_STAGES == 2, "the descriptors below are picked for two stages");
+            uint64_t k_desc[KV_STAGES], v_desc[KV_STAGES];
+#pragma unroll
+            for (int st = 0; st < KV_STAGES; ++st) {
+                k_desc[st] = make_sw128_desc(smem_u32(kv_ring + st * S::STAGE));
+                v_desc[st] = make_sw128_desc_mn(smem_u32(kv_ring + st * S::STAGE) + S::KV_TILE, KT * 128, 1024);
+            }
             bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 32);
             auto issue_s = [&](int j) {                                    // scores of tile j into buffer j % 2
                 const int s = j % KV_STAGES, b = j & 1;
                 if (!mbar_wait(kv_full(s), (j / KV_STAGES) & 1u, abort_flag, p.status, 33)) return false;
                 if (!mbar_wait(s_empty(b), ((j >> 1) & 1u) ^ 1u, abort_flag, p.status, 34)) return false;
                 tmem_fence_after();
-                const uint32_t k_addr = smem_u32(kv_ring + s * S::STAGE);
+                const uint64_t kd = s == 0 ? k_desc[0] : k_desc[KV_STAGES - 1];
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * (QM * 128) + (ks & 3) * 32;     // half, then 32 bytes a step
-                    umma_bf16(tmem_base + b * KT, make_sw128_desc(q_addr + off), make_sw128_desc(k_addr + off),
-                              idesc_s, ks > 0 ? 1u : 0u);
+                    const uint64_t off = (uint64_t)(((ks >> 2) * (QM * 128) + (ks & 3) * 32) >> 4);   // half, then 32 bytes a step
+                    umma_bf16(tmem_base + b * KT, q_desc + off, kd + off, idesc_s, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(s_full(b));
                 return true;
@@ -197,13 +205,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 if (!mbar_wait(p_full, j & 1u, abort_flag, p.status, 35)) { ok = false; break; }
                 tmem_fence_after();
                 const int s = j % KV_STAGES;
-                const uint32_t v_addr = smem_u32(kv_ring + s * S::STAGE) + S::KV_TILE;
+                const uint64_t vd = s == 0 ? v_desc[0] : v_desc[KV_STAGES - 1];
 #pragma unroll
                 for (int ks = 0; ks < KT / 16; ++ks) {
                     // A: 16 keys = 32 bytes along the swizzled row of P; B: 16 key rows of V = 2048 bytes
-                    const uint64_t adesc = make_sw128_desc(p_addr + (ks >> 2) * (QM * 128) + (ks & 3) * 32);
-                    const uint64_t bdesc = make_sw128_desc_mn(v_addr + ks * 16 * 128, KT * 128, 1024);
-                    umma_bf16(tmem_base + 2 * KT, adesc, bdesc, idesc_o, ks > 0 ? 1u : 0u);
+                    const uint64_t aoff = (uint64_t)(((ks >> 2) * (QM * 128) + (ks & 3) * 32) >> 4);
+                    umma_bf16(tmem_base + 2 * KT, p_desc + aoff, vd + (uint64_t)(ks * 128), idesc_o, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(o_full);             // O_j is complete (and P and this stage have been read)
                 umma_commit(kv_empty(s));
