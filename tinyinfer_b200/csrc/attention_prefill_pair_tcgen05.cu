@@ -28,7 +28,9 @@
 // of the 1,100 (8,192 tokens 560 -> 530 us). Tried on this form, none
 // faster: the issuing thread watching plain counters instead of mbarriers (the tiles then fall into step:
 // both in their exponentials, then both waiting for products), P handed over in two halves, turns of the
-// two tiles at the exponentials, an issuing warp per tile (polling or sleeping), sleeping between polls; and
+// two tiles at the exponentials, an issuing warp per tile (polling, or sleeping on its barriers with its
+// descriptors made once: 682 us; the products of two issuing threads share the tensor pipe, those of one take
+// turns at it), sleeping between polls; and
 // steps of 64 keys with two score buffers a query tile, so that the next scores are ready before a step's
 // softmax ends (8,192 tokens 753 us against 560: the score products of 64 keys take in 192 bytes of
 // operands a cycle from shared memory, which gives 128, and every step pays its hand-overs twice); and a
