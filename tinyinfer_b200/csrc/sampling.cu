@@ -109,11 +109,11 @@ __device__ __forceinline__ void for_each_logit(const float* x, int vocab, int be
 // that hold the same byte count themselves once together (most logits share their sign and exponent, so a
 // plain atomic per key would make a warp wait for itself 32 times over); the bin that holds the k-th largest
 // is found by the first warp together (a suffix sum over lanes of eight bins each), not by one thread.
+// One pass: sel[0] holds the bytes found so far (from the top), sel[1] which of the keys that begin with them,
+// counted from the largest, is looked for; afterwards one byte more and the rank among those.
 template <typename Each>
-__device__ __forceinline__ unsigned select_kth(int k, unsigned* hist, unsigned* sel, Each each) {
-    if (k <= 0) return 0u;
-    if (threadIdx.x == 0) { sel[0] = 0u; sel[1] = (unsigned)k; }
-    for (int pass = 0; pass < 4; ++pass) {
+__device__ __forceinline__ void radix_pass(int pass, unsigned* hist, unsigned* sel, Each each) {
+    {
         const int shift = 24 - 8 * pass;
         for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
         __syncthreads();
@@ -161,6 +161,12 @@ __device__ __forceinline__ unsigned select_kth(int k, unsigned* hist, unsigned* 
         }
         __syncthreads();
     }
+}
+template <typename Each>
+__device__ __forceinline__ unsigned select_kth(int k, unsigned* hist, unsigned* sel, Each each) {
+    if (k <= 0) return 0u;
+    if (threadIdx.x == 0) { sel[0] = 0u; sel[1] = (unsigned)k; }
+    for (int pass = 0; pass < 4; ++pass) radix_pass(pass, hist, sel, each);
     return sel[0];
 }
 
@@ -236,7 +242,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_parts_kernel(
     __shared__ Best sh_best[SMP_THREADS / 32];
     __shared__ unsigned hist[256];
     __shared__ unsigned sel[2];
-    __shared__ int count_sh, last_sh;
+    __shared__ int count_sh, aside_sh, last_sh;
     __shared__ unsigned keys_sh[SMP_PARTS * SMP_CAP];
     __shared__ int idx_sh[SMP_PARTS * SMP_CAP];
     ti_grid_launch_dependents();
@@ -260,23 +266,61 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_parts_kernel(
     } else if (!top) {
         b = gumbel_best<SMP_THREADS>(x, vocab, begin, end, temp, 0u, c1, c2, key2);
     } else if (k <= SMP_CAP) {
-        const unsigned local = select_kth(k, hist, sel, [&](auto count) {
+        // The slice's k-th largest scaled logit. The first byte from a scan of the slice; then the logits that share
+        // that byte with it (a few hundred of some ten thousand, as a rule) are set aside in shared memory, those
+        // above it are candidates already, and the other three bytes come from what was set aside: two scans of
+        // the slice, each with its division, instead of five.
+        auto slice_keys = [&](auto count) {
             for_each_logit<SMP_THREADS>(x, vocab, begin, end, [&](float raw, int) {
                 const float v = raw / temp;
                 if (v == v) count(order_key(v));
             });
-        });
-        if (tid == 0) count_sh = 0;
-        __syncthreads();
+        };
         unsigned* ck = cand_key + ((size_t)row * SMP_PARTS + part) * SMP_CAP;
         int* ci = cand_idx + ((size_t)row * SMP_PARTS + part) * SMP_CAP;
+        if (tid == 0) { sel[0] = 0u; sel[1] = (unsigned)k; count_sh = 0; aside_sh = 0; }
+        radix_pass(0, hist, sel, slice_keys);               // (its first barrier also publishes the words just set)
+        const unsigned first_byte = sel[0] >> 24;
+        constexpr int ASIDE = SMP_PARTS * SMP_CAP;          // the candidate arrays of the last block: free until then
         for_each_logit<SMP_THREADS>(x, vocab, begin, end, [&](float raw, int i) {
             const float v = raw / temp;
-            if (v == v && order_key(v) >= local) {
-                const int at = atomicAdd(&count_sh, 1);
-                if (at < SMP_CAP) { ck[at] = order_key(v); ci[at] = i; }
+            if (v == v) {
+                const unsigned key = order_key(v);
+                if ((key >> 24) > first_byte) {
+                    const int at = atomicAdd(&count_sh, 1);
+                    if (at < SMP_CAP) { ck[at] = key; ci[at] = i; }
+                } else if ((key >> 24) == first_byte) {
+                    const int at = atomicAdd(&aside_sh, 1);
+                    if (at < ASIDE) { keys_sh[at] = key; idx_sh[at] = i; }
+                }
             }
         });
+        __syncthreads();
+        const int aside = aside_sh;
+        if (aside <= ASIDE) {
+            const int above = count_sh;                     // logits above the first byte's bin: all among the k largest
+            const unsigned local = select_kth(k - above, hist, sel, [&](auto count) {
+                for (int i = tid; i < aside; i += SMP_THREADS) count(keys_sh[i]);
+            });
+            for (int i = tid; i < aside; i += SMP_THREADS) {
+                if (keys_sh[i] >= local) {
+                    const int at = atomicAdd(&count_sh, 1);
+                    if (at < SMP_CAP) { ck[at] = keys_sh[i]; ci[at] = idx_sh[i]; }
+                }
+            }
+        } else {
+            // more logits share the first byte than shared memory holds: the other bytes from scans of the slice
+            if (tid == 0) count_sh = 0;
+            for (int pass = 1; pass < 4; ++pass) radix_pass(pass, hist, sel, slice_keys);
+            const unsigned local = sel[0];
+            for_each_logit<SMP_THREADS>(x, vocab, begin, end, [&](float raw, int i) {
+                const float v = raw / temp;
+                if (v == v && order_key(v) >= local) {
+                    const int at = atomicAdd(&count_sh, 1);
+                    if (at < SMP_CAP) { ck[at] = order_key(v); ci[at] = i; }
+                }
+            });
+        }
         __syncthreads();
         if (tid == 0) cand_cnt[row * SMP_PARTS + part] = count_sh <= SMP_CAP ? count_sh : -1;
     }
