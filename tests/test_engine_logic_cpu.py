@@ -95,6 +95,34 @@ def test_patching_the_last_decode_step_needs_the_same_admissions():
     assert buffers.advance_decode([1, 2], 0, [11, 12], [4, 10], [[[7, 3], [2, 4, 8]]]) is None
 
 
+def test_rows_that_fill_a_batch_up_hold_a_page_and_a_state_slot_of_their_own():
+    """A decode batch is filled up to the size of its captured graph with rows of a request that is
+    none: its one page and its state slot are ones that no request holds, so a part that writes keys
+    or state for every row of the step alike spoils nothing."""
+    from tinyinfer_b200.engine.batch import BatchBuffers, StepEntry
+    buffers = BatchBuffers("cpu", max_tokens=8, max_seqs=4, max_blocks=4, num_groups=1)
+    entries = [StepEntry("a", [5], [0]), StepEntry("b", [6], [0]), StepEntry("c", [7], [0])]
+    ctx = buffers.build(entries, [3, 9, 1], [2, 0, 1], [[[7], [2, 4, 8], [6]]], fixed_layout=True, pad_to=4,
+                        pad_pages=[99], pad_slot=3)
+    assert ctx.num_seqs == 4 and ctx.num_real_seqs == 3
+    assert ctx.state_slots.tolist() == [2, 0, 1, 3]
+    assert ctx.block_tables[0][3].tolist() == [99, -1, -1, -1] and ctx.positions.tolist() == [3, 9, 1, 0]
+
+
+def test_the_cache_keeps_a_state_slot_for_the_rows_that_fill_up():
+    from tinyinfer_b200.cache import CacheManager, CacheStorage
+    from tinyinfer_b200.parts import StateNeed
+    needs = [(None, StateNeed((5,), torch.float32))]
+    manager = CacheManager(needs, 8, 4, 3)
+    storage = CacheStorage(needs, manager, torch.float32, "cpu")
+    slots = []
+    for rid in "abc":
+        manager.admit(rid)
+        slots.append(manager.get(rid).state_slot)
+    assert sorted(slots) == [0, 1, 2] and CacheStorage.dump_slot(manager) == 3
+    assert storage.state[0].shape == (4, 5)
+
+
 def test_an_id_that_comes_back_is_another_admission(tmp_path, cpu_ops):
     from tinyinfer_b200.engine.batch import StepEntry
     folder = helpers.make_model_folder(tmp_path / "m", helpers.TINY_A, seed=3)

@@ -57,6 +57,25 @@ class RunningMeanMixer(Mixer):
 register_mixer("toy_running_mean", RunningMeanMixer)
 
 
+class RunningMeanOnDevice(RunningMeanMixer):
+    """The same mixer with nothing read on the host: the state slots, the rows' requests and positions
+    are used where they lie, on the device, so a step of single tokens can be captured in a CUDA graph
+    and replayed (``graph_safe``). Rows that only fill a batch up to its graph's size carry a slot of
+    their own that no request holds."""
+    graph_safe = True
+
+    def forward(self, x, step, cache):
+        y = (x.float() @ self.w.float().T).double()
+        seq, slots, cu = step.token_seq.long(), step.state_slots.long(), step.cu_seqlens.long()
+        sums = torch.cat((torch.zeros_like(y[:1]), torch.cumsum(y, dim=0)))       # sums[r]: of the rows before r
+        running = cache.state.index_select(0, slots).double()[seq] + sums[1:] - sums[cu[:-1]][seq]
+        cache.state.index_copy_(0, slots, running[cu[1:] - 1].float())
+        return (running / (step.positions.double() + 1.0)[:, None]).to(x.dtype)
+
+
+register_mixer("toy_running_mean_on_device", RunningMeanOnDevice)
+
+
 @dataclass(frozen=True)
 class RoutedSpec:
     hidden_size: int
@@ -97,6 +116,26 @@ class RoutedFeedForward(FeedForward):
 
 
 register_feed_forward("toy_top1_experts", RoutedFeedForward)
+
+
+class RoutedOnDevice(RoutedFeedForward):
+    """The same feed-forward with no row picked on the host: every expert runs on every token and each
+    token keeps its own expert's answer (a row of a product does not depend on the rows beside it), which
+    is wasteful and may be captured in a CUDA graph."""
+    graph_safe = True
+
+    def forward(self, x, step):
+        from tinyinfer_b200 import ops
+        logits = x.float() @ self.w["router.weight"].T
+        weight, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+        out = torch.zeros_like(x)
+        for k in range(self.spec.num_experts):
+            y = ops.linear(ops.gated_linear(x, self.w[f"experts.{k}.gate_up.weight"]), self.w[f"experts.{k}.down.weight"])
+            out = torch.where((choice == k)[:, None], (y.float() * weight[:, None]).to(x.dtype), out)
+        return out
+
+
+register_feed_forward("toy_top1_experts_on_device", RoutedOnDevice)
 
 
 @dataclass(frozen=True)
@@ -156,6 +195,8 @@ TOY = dict(architectures=["ToyForCausalLM"], vocab_size=97, hidden_size=48, head
            intermediate_size=80, eps=1e-5, theta=10000.0, max_positions=256, experts=3, expert_size=24, stretch=4.0,
            position="stretched")
 TOY_PAIRS = dict(TOY, position="pairs_from_table", rotary_dim=12)
+TOY_ON_DEVICE = dict(TOY, state="on_device")
+TOY_FRAMED = dict(TOY, architectures=["ToyFramedForCausalLM"], embedding_scale=3.0, logit_cap=2.5)
 
 
 class ToyConfig:
@@ -178,17 +219,37 @@ class ToyConfig:
         attn = AttentionSpec(h, d["heads"], d["kv_heads"], d["head_dim"], d["head_dim"] ** -0.5, position,
                              qk_norm=NormSpec(d["head_dim"], eps))
         ffn = GatedMLPSpec(h, d["intermediate_size"])
-        routed = RoutedSpec(h, d["expert_size"], d["experts"])
+        on_device = d.get("state") == "on_device"
+        routed = RoutedSpec(h, d["expert_size"], d["experts"], "toy_top1_experts_on_device" if on_device else "toy_top1_experts")
         norm = NormSpec(h, eps)
-        layers = (LayerSpec(attn, ffn, norm, norm), LayerSpec(RunningMeanSpec(h), routed, norm, norm))
+        mean = RunningMeanSpec(h, "toy_running_mean_on_device" if on_device else "toy_running_mean")
+        layers = (LayerSpec(attn, ffn, norm, norm), LayerSpec(mean, routed, norm, norm))
         # layer 0 runs three times: with a cache of its own, again with another cache, and at the
         # end reading the keys its first run wrote; the stateful toy layer sits in between
         execution = (ExecStep(0, 0), ExecStep(1, 1), ExecStep(0, 2), ExecStep(0, 0, writes_cache=False))
-        return ModelSpec("ToyForCausalLM", d["vocab_size"], h, layers, execution, norm,
+        return ModelSpec(d["architectures"][0], d["vocab_size"], h, layers, execution, norm,
                          tie_embeddings=True, max_positions=d["max_positions"], names=TensorNames())
 
 
 register_architecture("ToyForCausalLM", ToyConfig, lambda cfg, dtype, device: DecoderModel(cfg.model_spec(), dtype, device))
+
+
+class FramedToyModel(DecoderModel):
+    """Another frame around the same blocks: the embedding is scaled and the logits are capped smoothly.
+    The model class of an architecture is whatever its registration names."""
+
+    def __init__(self, cfg, dtype, device):
+        super().__init__(cfg.model_spec(), dtype, device)
+        self.scale, self.cap = cfg.d["embedding_scale"], cfg.d["logit_cap"]
+
+    def embed(self, step):
+        return (super().embed(step).float() * self.scale).to(self.dtype)
+
+    def logits(self, x, step):
+        return self.cap * torch.tanh(super().logits(x, step) / self.cap)
+
+
+register_architecture("ToyFramedForCausalLM", ToyConfig, FramedToyModel)
 
 
 # ------------------------------------------------------------------ its plain statement
@@ -222,7 +283,7 @@ def toy_plain(w, tokens, d=TOY):
         return x + plain.swiglu(hn2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                                 w[p + "mlp.down_proj.weight"]), hn
 
-    x = plain.embedding(tokens, w["model.embed_tokens.weight"])
+    x = plain.embedding(tokens, w["model.embed_tokens.weight"]) * d.get("embedding_scale", 1.0)
     x, first_normed = attn_layer(x)
     p = "model.layers.1."
     hn = plain.rmsnorm(x, w[p + "input_layernorm.weight"], d["eps"])
@@ -240,7 +301,21 @@ def toy_plain(w, tokens, d=TOY):
     x, _ = attn_layer(x)
     x, _ = attn_layer(x, kv_from=first_normed)          # reads the keys and values of the first run
     x = plain.rmsnorm(x, w["model.norm.weight"], d["eps"])
-    return x @ w["model.embed_tokens.weight"].T
+    logits = x @ w["model.embed_tokens.weight"].T
+    return d["logit_cap"] * torch.tanh(logits / d["logit_cap"]) if "logit_cap" in d else logits
+
+
+def trace_three_together(requests, tail=6):
+    """Three requests, each most of its prompt in a step of its own, then their last ``tail`` tokens
+    side by side: steps of three single tokens (which a graph of four rows serves, one row filled in)."""
+    rids = [rid for rid, toks in requests.items() if len(toks) > tail][:3]
+    steps = [{"step": k, "entries": [{"id": rid, "tokens": requests[rid][:-tail],
+                                      "want": list(range(len(requests[rid]) - tail))}], "end": []}
+             for k, rid in enumerate(rids)]
+    for j in range(tail):
+        steps.append({"step": len(steps), "end": rids if j == tail - 1 else [],
+                      "entries": [{"id": rid, "tokens": [requests[rid][j - tail]], "want": [0]} for rid in rids]})
+    return steps
 
 
 def run_toy(tmp_path, device, dtype_name, toy=TOY):
@@ -248,7 +323,7 @@ def run_toy(tmp_path, device, dtype_name, toy=TOY):
     from tinyinfer_b200.config import load_config
     from tinyinfer_b200.weights import load_weights, write_random_model
     folder = write_random_model(tmp_path / "toy", ToyConfig(toy), seed=11, std=0.08)
-    assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyForCausalLM"]
+    assert json.loads((folder / "config.json").read_text())["architectures"] == toy["architectures"]
     arch, cfg = load_config(folder)
     model = arch.model_factory(cfg, torch.float32, torch.device(device))
     load_weights(model, folder)
@@ -257,23 +332,33 @@ def run_toy(tmp_path, device, dtype_name, toy=TOY):
     _, w = plain.read_model_folder(folder, torch.float64)
     requests = helpers.random_requests(dict(vocab_size=97), [40, 9, 70, 33, 2, 50], seed=2)
     want = {rid: toy_plain(w, toks, toy).numpy() for rid, toks in requests.items()}
+    replays = 0
     for steps in (helpers.trace_whole(requests), helpers.trace_chunked(requests, seed=4),
-                  helpers.trace_mixed(requests, seed=5, max_live=3)):
+                  helpers.trace_mixed(requests, seed=5, max_live=3), trace_three_together(requests)):
         # three state slots for six requests: slots are used again and must start from zero
         session = TraceSession(None, dtype_name, helpers.peak_tokens(steps), page_size=8, model=model,
                                max_live=3, poison_cache=True)
         got = helpers.collect(session, steps)
         assert helpers.first_bad(got, want, 5e-5) is None
         session.runner.manager.check_consistency()
+        replays += session.runner.graph_replays
+    return replays
+
+
+TOYS = dict(argvalues=[TOY, TOY_PAIRS, TOY_ON_DEVICE, TOY_FRAMED],
+            ids=["stretched", "pairs_from_table", "state_on_device", "framed"])
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("toy", [TOY, TOY_PAIRS], ids=["stretched", "pairs_from_table"])
+@pytest.mark.parametrize("toy", **TOYS)
 def test_toy_architecture_steps_on_the_gpu(tmp_path, toy):
-    run_toy(tmp_path, "cuda:0", "float32", toy)
+    replays = run_toy(tmp_path, "cuda:0", "float32", toy)
+    # a mixer that reads its state slots on the host keeps the model's steps out of CUDA graphs; with the one
+    # that leaves them on the device the steps of single tokens are replayed, three requests in a graph of four rows
+    assert (replays > 0) == (toy is TOY_ON_DEVICE)
 
 
-@pytest.mark.parametrize("toy", [TOY, TOY_PAIRS], ids=["stretched", "pairs_from_table"])
+@pytest.mark.parametrize("toy", **TOYS)
 def test_toy_architecture_steps_with_plain_ops(tmp_path, monkeypatch, toy):
     from tinyinfer_b200 import ops
     for name in torch_ops.ALL:

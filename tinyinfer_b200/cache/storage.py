@@ -45,13 +45,20 @@ class CacheStorage:
             if state is None:
                 self.state.append(None)
             else:
-                self.state.append(torch.zeros((manager.max_requests, *state.shape),
+                # one slot more than requests can hold: the padding rows' (see dump_slot)
+                self.state.append(torch.zeros((manager.max_requests + 1, *state.shape),
                                               dtype=state.dtype, device=self.device))
 
     @staticmethod
     def dump_page(manager: CacheManager, group: int) -> int:
         """The page id no request ever holds: padding rows write their keys and values there."""
         return manager.groups[group].pool.num_pages
+
+    @staticmethod
+    def dump_slot(manager: CacheManager) -> int:
+        """The state slot no request ever holds: a mixer that updates its state on the device, for
+        every row of the step alike, updates this one for the padding rows."""
+        return manager.max_requests
 
     def reset_state_slot(self, slot: int) -> None:
         for t in self.state:

@@ -102,14 +102,15 @@ class BatchBuffers:
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
               tables: Sequence[Sequence[Sequence[int]]], fixed_layout: bool = False,
-              pad_to: int = 0, pad_pages: Sequence[int] = (),
+              pad_to: int = 0, pad_pages: Sequence[int] = (), pad_slot: int = 0,
               admissions: Optional[Sequence[int]] = None) -> StepContext:
         """``starts[i]``: tokens entry i's request already holds; ``slots[i]``: its state slot;
         ``tables[g][i]``: its block table in cache group g. ``fixed_layout`` pads every block
         table to the widest possible, so that two steps with the same numbers of tokens and
         requests put every array at the same address (what a captured CUDA graph needs).
         ``pad_to`` fills the step up to that many requests with padding rows (token 0 at position 0
-        of a request whose only page is ``pad_pages[g]``, a page no real request holds), so that one
+        of a request whose only page is ``pad_pages[g]`` and whose state slot is ``pad_slot``, a page
+        and a slot no real request holds), so that one
         captured graph serves a range of batch sizes; their logits come last and are dropped.
         ``admissions[i]``: a number that tells entry i's request from every other request there ever
         was (the cache manager's admission serial); with it a step of single decoded tokens can be
@@ -119,7 +120,7 @@ class BatchBuffers:
             extra = pad_to - num_real
             entries = list(entries) + [StepEntry(("pad", i), [0], [0]) for i in range(extra)]
             starts = list(starts) + [0] * extra
-            slots = list(slots) + [0] * extra
+            slots = list(slots) + [pad_slot] * extra
             tables = [list(tables[g]) + [[pad_pages[g]] if g < len(pad_pages) else []] * extra
                       for g in range(self.num_groups)]
         q_lens = [len(e.tokens) for e in entries]

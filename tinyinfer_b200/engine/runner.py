@@ -40,7 +40,7 @@ class ModelRunner:
                                     max(1, len(self.manager.groups)))
         self.steps_run = 0
         self.cuda_graphs = (cuda_graphs and self.device.type == "cuda"
-                            and all(b.mixer.graph_safe for b in model.blocks))
+                            and all(b.mixer.graph_safe and b.feed_forward.graph_safe for b in model.blocks))
         self._tables_only_grow = all(g.need.window is None for g in self.manager.groups)
         self._graphs = {}          # requests in the step -> (graph, static logits, kernels)
         self._graph_pool = None
@@ -114,7 +114,8 @@ class ModelRunner:
         if ctx is None:
             ctx = self.buffers.build(entries, starts, [rc.state_slot for rc in caches], tables,
                                      fixed_layout=decode_only, pad_to=pad_to, admissions=serials,
-                                     pad_pages=[CacheStorage.dump_page(self.manager, g) for g in range(num_groups)])
+                                     pad_pages=[CacheStorage.dump_page(self.manager, g) for g in range(num_groups)],
+                                     pad_slot=CacheStorage.dump_slot(self.manager))
             self._bind_views(ctx)
         if ctx.num_feeds:
             from .. import ops

@@ -95,16 +95,32 @@ class DecoderModel:
         return needs
 
     # ------------------------------------------------------------------ forward
+    # The frame around the blocks is three methods, so that a model whose frame differs (an embedding
+    # that is scaled, logits that are capped, a norm elsewhere) overrides one of them in a subclass and
+    # registers that class for its architecture; blocks, cache and step function stay as they are.
     def forward(self, step) -> torch.Tensor:
         """Runs the tokens of ``step`` (a StepContext) and returns float32 logits [N, V] at
         ``step.logit_rows``."""
-        x = ops.embedding(step.token_ids, self.embedding)
+        x = self.run_blocks(self.embed(step), step)
+        if step.num_logit_rows == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        return self.logits(x, step)
+
+    def embed(self, step) -> torch.Tensor:
+        """The residual stream [T, hidden] the first block starts from."""
+        return ops.embedding(step.token_ids, self.embedding)
+
+    def run_blocks(self, x: torch.Tensor, step) -> torch.Tensor:
+        """The blocks in the order the spec lists, each on its cache entry."""
         link = None        # what a block's last product leaves for the next block's first norm (see parts.base)
         order = self.spec.execution
         for i, entry in enumerate(order):
             after = self.blocks[order[i + 1].layer].mixer_norm if i + 1 < len(order) else None
             x, link = self.blocks[entry.layer].forward_linked(x, link, after, step, step.cache_view(entry))
-        if step.num_logit_rows == 0:
-            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        return x
+
+    def logits(self, x: torch.Tensor, step) -> torch.Tensor:
+        """Float32 logits [N, V] of the rows ``step.logit_rows`` (there is at least one) of the last
+        block's output."""
         h = self.final_norm.forward_rows(x, step.logit_rows)
         return ops.linear(h, self.head, out_float32=True)

@@ -119,6 +119,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    graph_safe = False      # as for a mixer: a feed-forward that picks its experts' rows on the host is not
+
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         raise NotImplementedError
 

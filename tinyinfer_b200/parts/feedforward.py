@@ -11,6 +11,7 @@ from .base import FeedForward, TensorSpec, register_feed_forward
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
         if spec.activation != "silu":
