@@ -85,6 +85,18 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"((unsigned short)3) : "memory");
 }
+// 32 columns of this warp's 32 accumulator lanes into registers; the values are there after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_in_cluster_window) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_in_cluster_window) : "memory");
 }
@@ -214,6 +226,45 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const int lane_group = warp & 3;                 // the 32 accumulator lanes this warp may read
         const int row_in_tile = lane_group * 32 + lane;
         const uint32_t acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
+        // bias, residual and store of 16 consecutive outputs n0.. of token row m (the general path: ragged edges,
+        // float32 output, rows that do not start on 16-byte boundaries)
+        auto finish16 = [&](int m, int n0, float* v) {
+            const size_t base = (size_t)m * p.N + n0;
+            if (p.bias) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) if (n0 + i < p.N) v[i] += p.bias[n0 + i];
+            }
+            if (p.residual) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) if (n0 + i < p.N) v[i] += __bfloat162float(p.residual[base + i]);
+            }
+            if (p.out_f32) {
+                float* o = reinterpret_cast<float*>(p.out) + base;
+                if (n0 + 16 <= p.N && (base & 3) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) if (n0 + i < p.N) o[i] = v[i];
+                }
+            } else {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + base;
+                if (n0 + 16 <= p.N && (base & 7) == 0) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint4 q;
+                        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) b2[i] = __floats2bfloat162_rn(v[h * 8 + 2 * i], v[h * 8 + 2 * i + 1]);
+                        reinterpret_cast<uint4*>(o)[h] = q;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) if (n0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
+                }
+            }
+        };
         uint32_t tile_i = 0;
         bool ok = true;
         for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++tile_i) {
@@ -225,77 +276,70 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const uint32_t t_addr = tmem_base + as * BN + ((uint32_t)(lane_group * 32) << 16);
             const int m = r0 + (int)rank * BM + row_in_tile;
             const bool row_ok = m < p.M;
-            float v[16], u[16];
+            // 64 columns at a time: two tensor-memory loads and the row's residual are asked for together and
+            // waited for once (the epilogue of a pair's last tile has no MMAs to hide behind: every wait of it
+            // is the kernel's time)
             if (!p.gated) {
-                for (int c = 0; c < BN; c += 16) {
-                    tmem_ld16(t_addr + c, v);
+                for (int c = 0; c < BN; c += 64) {
+                    uint32_t r[64];
+                    tmem_ld32_issue(t_addr + c, r);
+                    tmem_ld32_issue(t_addr + c + 32, r + 32);
                     const int n0 = c0 + c;
-                    if (!row_ok || n0 >= p.N) continue;
                     const size_t base = (size_t)m * p.N + n0;
-                    const bool full16 = n0 + 16 <= p.N;
-                    if (p.bias) {
+                    const bool whole = row_ok && !p.out_f32 && n0 + 64 <= p.N && (base & 7) == 0;
+                    uint4 res[8];
+                    if (whole && p.residual) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) if (n0 + i < p.N) v[i] += p.bias[n0 + i];
+                        for (int i = 0; i < 8; ++i) res[i] = reinterpret_cast<const uint4*>(p.residual + base)[i];
                     }
-                    if (p.residual) {
-                        if (full16 && (base & 7) == 0) {
-                            const uint4* r4 = reinterpret_cast<const uint4*>(p.residual + base);
+                    tmem_ld_wait();
+                    float* v = reinterpret_cast<float*>(r);
+                    if (whole) {
+                        if (p.bias) {
 #pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                const uint4 q = r4[h];
-                                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&q);
+                            for (int i = 0; i < 64; ++i) v[i] += p.bias[n0 + i];
+                        }
+                        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base);
+#pragma unroll
+                        for (int h = 0; h < 8; ++h) {
+                            uint4 q;
+                            __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&q);
+                            if (p.residual) {
+                                const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&res[h]);
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
-                                    const float2 f = __bfloat1622float2(b2[i]);
-                                    v[h * 8 + 2 * i] += f.x;
-                                    v[h * 8 + 2 * i + 1] += f.y;
+                                    const float2 f = __bfloat1622float2(r2[i]);
+                                    b2[i] = __floats2bfloat162_rn(v[h * 8 + 2 * i] + f.x, v[h * 8 + 2 * i + 1] + f.y);
                                 }
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) if (n0 + i < p.N) v[i] += __bfloat162float(p.residual[base + i]);
-                        }
-                    }
-                    if (p.out_f32) {
-                        float* o = reinterpret_cast<float*>(p.out) + base;
-                        if (full16 && (base & 3) == 0) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) if (n0 + i < p.N) o[i] = v[i];
-                        }
-                    } else {
-                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + base;
-                        if (full16 && (base & 7) == 0) {
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                uint4 q;
-                                __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&q);
+                            } else {
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) b2[i] = __floats2bfloat162_rn(v[h * 8 + 2 * i], v[h * 8 + 2 * i + 1]);
-                                reinterpret_cast<uint4*>(o)[h] = q;
                             }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) if (n0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
+                            o[h] = q;
                         }
+                    } else if (row_ok) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                            if (n0 + 16 * g < p.N) finish16(m, n0 + 16 * g, v + 16 * g);
                     }
                 }
             } else {
                 // columns [0, 128) hold the gate, [128, 256) the up projection of the same outputs
-                for (int c = 0; c < BN / 2; c += 16) {
-                    tmem_ld16(t_addr + c, v);
-                    tmem_ld16(t_addr + BN / 2 + c, u);
+                for (int c = 0; c < BN / 2; c += 32) {
+                    uint32_t rg[32], ru[32];
+                    tmem_ld32_issue(t_addr + c, rg);
+                    tmem_ld32_issue(t_addr + BN / 2 + c, ru);
+                    tmem_ld_wait();
                     const int j0 = c0 + c;
                     if (!row_ok || j0 >= p.N) continue;
+                    float* v = reinterpret_cast<float*>(rg);
+                    const float* u = reinterpret_cast<const float*>(ru);
                     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + j0;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = silu_mul(v[i], u[i]);
-                    if (j0 + 16 <= p.N && (((size_t)m * p.N + j0) & 7) == 0) {
+                    for (int i = 0; i < 32; ++i) v[i] = silu_mul(v[i], u[i]);
+                    if (j0 + 32 <= p.N && (((size_t)m * p.N + j0) & 7) == 0) {
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
+                        for (int h = 0; h < 4; ++h) {
                             uint4 q;
                             __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&q);
 #pragma unroll
@@ -304,7 +348,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         }
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) if (j0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
+                        for (int i = 0; i < 32; ++i) if (j0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
                     }
                 }
             }
