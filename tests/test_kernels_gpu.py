@@ -449,7 +449,13 @@ def test_paged_attention(ops, monkeypatch, dtype, hq, hkv, d, page, window, work
     (8, 4, 128, 128, 2500, [6000, 2501, 2500, 5121, 40, 4608, 3000, 5632, 5633, 6000, 2600, 4097, 777, 5120]),
     # many short requests: a CTA's run of four key tiles crosses kv heads and requests
     (6, 3, 128, 32, None, [1, 64, 65, 130, 7, 200, 63, 129, 2, 300, 64, 64, 1, 191, 192, 193] * 3),
-    (4, 1, 64, 16, 100, [1, 99, 100, 101, 164, 165, 230, 700, 3, 64] * 7)])
+    (4, 1, 64, 16, 100, [1, 99, 100, 101, 164, 165, 230, 700, 3, 64] * 7),
+    # 8 and 9 query heads a kv head at head size 128: the merge of a CTA's four warps through the smaller buffer;
+    # 12 and 16: one CTA an SM with a ring of six stages
+    (64, 8, 128, 64, None, [4096, 3000, 1, 257, 513, 4000, 2048, 1025, 64, 65]),
+    (18, 2, 128, 64, 1500, [5000, 1499, 1500, 1501, 1, 2900, 700, 64, 63, 4097, 333, 2048]),
+    (24, 2, 128, 32, None, [2600, 1, 129, 4000, 512, 77, 1024, 3001]),
+    (32, 2, 128, 128, None, [6000, 1, 64, 1300, 2049, 257, 4500])])
 def test_decode_attention_shares_the_keys_out_evenly(ops, hq, hkv, d, page, window, lens):
     """Long contexts are cut where a CTA's run ends, not at fixed positions, and short ones share a CTA: the
     same results wherever the cuts fall (inside a request, at its last key, across kv heads and requests, a

@@ -26,7 +26,7 @@ namespace {
 
 constexpr int TK = 64;            // keys per tile
 constexpr int MIN_RUN_TILES = 4;  // fewest key tiles of a CTA's run: a part pays about 52 keys' worth of time beyond its keys
-constexpr int STAGES = 3;
+constexpr int STAGES = 3;        // stages of the ring of key/value tiles (decode with one CTA an SM: twice as many)
 constexpr int CONSUMER_THREADS = 128;
 constexpr int THREADS = CONSUMER_THREADS + 32;
 
@@ -72,9 +72,12 @@ struct Smem {
     static constexpr int HALVES = D / 64;
     static constexpr int TILE_BYTES = HALVES * TK * 128;      // keys OR values of one tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int BYTES = 1024 + STAGES * STAGE_BYTES + 128;
-    // decode adds its merge buffer: [4 warps][query heads of a kv head <= 16][D + 2] floats
-    static int decode_bytes(int group) { return BYTES + 4 * group * (D + 2) * 4; }
+    // 1 KB to align the ring, the ring, its barriers, and the merge buffer [4 warps][query heads of a kv head <= 16]
+    // [D + 2] floats; slim: a warp finishes a quarter of the features and gets the other three warps' partials of
+    // them, [4 warps][3][query heads][D / 4 + 2] floats
+    static int decode_bytes(int group, int stages = STAGES, bool slim = false) {
+        return 1024 + stages * STAGE_BYTES + 128 + (slim ? 4 * 3 * group * (D / 4 + 2) * 4 : 4 * group * (D + 2) * 4);
+    }
 };
 
 // Issues the copies of tile `t` (keys t*TK .. t*TK+63 of the request) into a stage. Pieces whose
@@ -198,15 +201,24 @@ struct RunWalk {
 // so HBM does not idle at part boundaries. `rows`, `positions`, `token_seq`, the block tables and every key
 // tile but a row's last are read BEFORE the wait for the kernels ahead in the stream: they are inputs of the
 // step or older than it, never written by the kernels that lead up to this one.
-template <int D>
+// NS: stages of the ring. Three with two or more CTAs an SM; where the merge buffer of many query heads a kv
+// head leaves room for one CTA only, six, so that an SM has as many bytes on their way as with two CTAs.
+// SLIM: the merge of the four warps at the end of a part through a buffer of three quarters the size, which lets
+// two CTAs of 8 or 9 query heads a kv head (head size 128) share an SM (32 requests x 8,192 keys, 64 query heads
+// over 8: 193 -> 170 us); with fewer query heads, where two CTAs fit anyway, the whole buffer's merge is shorter
+// (8 x 4,096 keys, 32 over 8: 26.9 us against 30.0).
+template <int D, int NS, bool SLIM>
 __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                    const AttnParams p) {
     using S = Smem<D>;
-    constexpr int LD = D + 2;                              // merge buffer row: D outputs, maximum, sum
+    constexpr int STAGES = NS;                             // hides the file's constant in this kernel
+    constexpr int LDW = D + 2;                             // whole merge buffer row: D outputs, maximum, sum
+    constexpr int OWN = D / 4, NB_OWN = OWN / 8;           // slim: features (and 8-wide blocks of them) a warp finishes
+    constexpr int LD = OWN + 2;                            // slim merge buffer row: a warp's partial of OWN features, its maximum, its sum
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
-    float* mbuf = reinterpret_cast<float*>(smem + STAGES * S::STAGE_BYTES + 128);   // [4 warps][group][LD]
+    float* mbuf = reinterpret_cast<float*>(smem + STAGES * S::STAGE_BYTES + 128);   // [4 warps][group][LDW], slim: [4 owners][3 others][group][LD]
     const uint32_t bar0 = smem_u32(bars);
     __shared__ int abort_sh;
     __shared__ int warp_sums[THREADS / 32];
@@ -364,8 +376,59 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
             if (lane == 0) mbar_arrive(bar0 + 8u * (STAGES + s));
         }
 
-        // ---- merge the four warps (each saw a quarter of the keys) and write the part's partial.
-        // Only the rows that are real query heads travel through shared memory.
+        if constexpr (!SLIM) {
+            // ---- merge the four warps (each saw a quarter of the keys) and write the part's partial.
+            // Only the rows that are real query heads travel through shared memory.
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+                l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");       // the previous item's merge buffer has been read
+#pragma unroll
+            for (int nb = 0; nb < D / 8; ++nb) {
+                float* base = mbuf + ((size_t)warp * group) * LDW + nb * 8 + c;
+                if (g < group) { base[(size_t)g * LDW] = o[nb][0]; base[(size_t)g * LDW + 1] = o[nb][1]; }
+                if (g + 8 < group) { base[(size_t)(g + 8) * LDW] = o[nb][2]; base[(size_t)(g + 8) * LDW + 1] = o[nb][3]; }
+            }
+            if ((lane & 3) == 0) {
+                if (g < group) {
+                    mbuf[((size_t)warp * group + g) * LDW + D] = m_run[0];
+                    mbuf[((size_t)warp * group + g) * LDW + D + 1] = l_run[0];
+                }
+                if (g + 8 < group) {
+                    mbuf[((size_t)warp * group + g + 8) * LDW + D] = m_run[1];
+                    mbuf[((size_t)warp * group + g + 8) * LDW + D + 1] = l_run[1];
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int idx = threadIdx.x; idx < group * D; idx += CONSUMER_THREADS) {
+                const int hrow = idx / D, d = idx % D;
+                float mw[4], m_all = -INFINITY;
+#pragma unroll
+                for (int w4 = 0; w4 < 4; ++w4) { mw[w4] = mbuf[((size_t)w4 * group + hrow) * LDW + D]; m_all = fmaxf(m_all, mw[w4]); }
+                const float m_use = m_all == -INFINITY ? 0.f : m_all;
+                float acc = 0.f, l_all = 0.f;
+#pragma unroll
+                for (int w4 = 0; w4 < 4; ++w4) {
+                    const float f = exp2f(mw[w4] - m_use);
+                    acc += f * mbuf[((size_t)w4 * group + hrow) * LDW + d];
+                    l_all += f * mbuf[((size_t)w4 * group + hrow) * LDW + D + 1];
+                }
+                if (item.cta0 == item.cta1) {                      // the pair lies inside this run: this is its result
+                    p.out[((size_t)item.row * p.hq + (size_t)item.kvh * group + hrow) * D + d] =
+                        __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+                } else {
+                    const size_t slot = (size_t)item.slot * group + hrow;
+                    __stcg(p.part_o + slot * D + d, acc);
+                    if (d == 0) __stcg(reinterpret_cast<float2*>(p.part_ml + slot * 2), make_float2(m_all, l_all));
+                }
+            }
+        } else {
+        // ---- merge the four warps (each saw a quarter of the keys) and write the part's partial: warp w
+        // finishes features [w OWN, (w + 1) OWN) and gets the other warps' partials of them through shared
+        // memory, in the layout of the MMA's accumulator (a lane reads what it would hold itself). Only the
+        // rows that are real query heads travel. The four partials are added in the order of the warps.
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -374,43 +437,68 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
         asm volatile("bar.sync 1, 128;" ::: "memory");       // the previous item's merge buffer has been read
 #pragma unroll
         for (int nb = 0; nb < D / 8; ++nb) {
-            float* base = mbuf + ((size_t)warp * group) * LD + nb * 8 + c;
+            const int owner = nb / NB_OWN;
+            if (owner == warp) continue;
+            const int from = warp < owner ? warp : warp - 1;   // this warp's place among the owner's three others
+            float* base = mbuf + ((size_t)(owner * 3 + from) * group) * LD + (nb % NB_OWN) * 8 + c;
             if (g < group) { base[(size_t)g * LD] = o[nb][0]; base[(size_t)g * LD + 1] = o[nb][1]; }
             if (g + 8 < group) { base[(size_t)(g + 8) * LD] = o[nb][2]; base[(size_t)(g + 8) * LD + 1] = o[nb][3]; }
         }
         if ((lane & 3) == 0) {
-            if (g < group) {
-                mbuf[((size_t)warp * group + g) * LD + D] = m_run[0];
-                mbuf[((size_t)warp * group + g) * LD + D + 1] = l_run[0];
-            }
-            if (g + 8 < group) {
-                mbuf[((size_t)warp * group + g + 8) * LD + D] = m_run[1];
-                mbuf[((size_t)warp * group + g + 8) * LD + D + 1] = l_run[1];
+#pragma unroll
+            for (int owner = 0; owner < 4; ++owner) {
+                if (owner == warp) continue;
+                const int from = warp < owner ? warp : warp - 1;
+                float* ml = mbuf + ((size_t)(owner * 3 + from) * group) * LD + OWN;
+                if (g < group) { ml[(size_t)g * LD] = m_run[0]; ml[(size_t)g * LD + 1] = l_run[0]; }
+                if (g + 8 < group) { ml[(size_t)(g + 8) * LD] = m_run[1]; ml[(size_t)(g + 8) * LD + 1] = l_run[1]; }
             }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        for (int idx = threadIdx.x; idx < group * D; idx += CONSUMER_THREADS) {
-            const int hrow = idx / D, d = idx % D;
-            float mw[4], m_all = -INFINITY;
 #pragma unroll
-            for (int w4 = 0; w4 < 4; ++w4) { mw[w4] = mbuf[((size_t)w4 * group + hrow) * LD + D]; m_all = fmaxf(m_all, mw[w4]); }
-            const float m_use = m_all == -INFINITY ? 0.f : m_all;
-            float acc = 0.f, l_all = 0.f;
+        for (int h = 0; h < 2; ++h) {
+            const int hrow = g + 8 * h;
+            if (hrow >= group) continue;
+            // the four warps' maxima and sums, in the order of the warps (this warp's own from its registers)
+            const float* others = mbuf + ((size_t)(warp * 3) * group + hrow) * LD;
+            float mw[4], lw[4], m_all = -INFINITY;
 #pragma unroll
             for (int w4 = 0; w4 < 4; ++w4) {
-                const float f = exp2f(mw[w4] - m_use);
-                acc += f * mbuf[((size_t)w4 * group + hrow) * LD + d];
-                l_all += f * mbuf[((size_t)w4 * group + hrow) * LD + D + 1];
+                const int from = w4 < warp ? w4 : w4 - 1;
+                mw[w4] = w4 == warp ? m_run[h] : others[(size_t)from * group * LD + OWN];
+                lw[w4] = w4 == warp ? l_run[h] : others[(size_t)from * group * LD + OWN + 1];
+                m_all = fmaxf(m_all, mw[w4]);
             }
-            if (item.cta0 == item.cta1) {                      // the pair lies inside this run: this is its result
-                p.out[((size_t)item.row * p.hq + (size_t)item.kvh * group + hrow) * D + d] =
-                    __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
-            } else {
-                const size_t slot = (size_t)item.slot * group + hrow;
-                __stcg(p.part_o + slot * D + d, acc);
-                if (d == 0) __stcg(reinterpret_cast<float2*>(p.part_ml + slot * 2), make_float2(m_all, l_all));
+            const float m_use = m_all == -INFINITY ? 0.f : m_all;
+            float f[4], l_all = 0.f;
+#pragma unroll
+            for (int w4 = 0; w4 < 4; ++w4) { f[w4] = exp2f(mw[w4] - m_use); l_all += f[w4] * lw[w4]; }
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+#pragma unroll
+            for (int nb = 0; nb < D / 8; ++nb) {               // every block, so that the accumulator's index is a constant
+                if (nb / NB_OWN != warp) continue;
+                const int nbo = nb % NB_OWN, d = nb * 8 + c;
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int w4 = 0; w4 < 4; ++w4) {
+                    const int from = w4 < warp ? w4 : w4 - 1;
+                    const float x0 = w4 == warp ? o[nb][2 * h] : others[(size_t)from * group * LD + nbo * 8 + c];
+                    const float x1 = w4 == warp ? o[nb][2 * h + 1] : others[(size_t)from * group * LD + nbo * 8 + c + 1];
+                    a0 += f[w4] * x0;
+                    a1 += f[w4] * x1;
+                }
+                if (item.cta0 == item.cta1) {                  // the pair lies inside this run: this is its result
+                    *reinterpret_cast<__nv_bfloat162*>(p.out + ((size_t)item.row * p.hq + (size_t)item.kvh * group + hrow) * D + d) =
+                        __floats2bfloat162_rn(a0 * inv, a1 * inv);
+                } else {
+                    const size_t slot = (size_t)item.slot * group + hrow;
+                    __stcg(reinterpret_cast<float2*>(p.part_o + slot * D + d), make_float2(a0, a1));
+                }
             }
+            if (item.cta0 != item.cta1 && warp == 0 && (lane & 3) == 0)
+                __stcg(reinterpret_cast<float2*>(p.part_ml + ((size_t)item.slot * group + hrow) * 2), make_float2(m_all, l_all));
         }
+        }   // SLIM
     }
 }
 
@@ -497,19 +585,27 @@ TI_API int ti_attention_bf16_supported(int hq, int hkv, int d, int page_size) {
            ((page_size < TK && TK % page_size == 0) || page_size % TK == 0) ? 1 : 0;
 }
 namespace {
-// Shared memory that decode_attention_kernel<128> (which 0) or <64> (which 1) was last allowed on the
-// current device: the attribute is kept per device, so the record is too. nullptr: no current device.
+// Shared memory that decode_attention_kernel<128, 3, false> (which 0), <64, 3, false> (which 1), <128, 6, false> (which 2)
+// or <128, 3, true> (which 3) was last allowed on the current device: the attribute is kept per device, so the record
+// is too. nullptr: no current device.
 int* configured_bytes(int which) {
     constexpr int MAX_DEVICES = 64;
-    static int bytes[2][MAX_DEVICES] = {};
+    static int bytes[4][MAX_DEVICES] = {};
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
     return &bytes[which][dev];
 }
 
+// The form of the decode kernel at head size 128: 0, three stages and the whole merge buffer, two CTAs an SM;
+// 1, three stages and the slim buffer where that still lets two CTAs share an SM; 2, one CTA an SM with six stages.
+int decode_form(int group) {
+    if (Smem<128>::decode_bytes(group) <= 113 * 1024) return 0;
+    if (Smem<128>::decode_bytes(group, STAGES, true) <= 113 * 1024) return 1;
+    return 2;
+}
 // CTAs of the decode kernel that run side by side.
 int decode_slots(int d, int group) {
-    if (d == 128) return ti_sm_count() * (Smem<128>::decode_bytes(group) <= 113 * 1024 ? 2 : 1);
+    if (d == 128) return ti_sm_count() * (decode_form(group) == 2 ? 1 : 2);
     const int bytes = Smem<64>::decode_bytes(group);
     return ti_sm_count() * (bytes <= 56 * 1024 ? 4 : (bytes <= 75 * 1024 ? 3 : 2));
 }
@@ -563,20 +659,36 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
     p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
     p.num_rows = num_rows; p.num_ctas = ctas;
-    if (d == 128) {
+    if (d == 128 && decode_form(group) == 2) {
+        const int bytes = Smem<128>::decode_bytes(group, 2 * STAGES);
+        int* configured = configured_bytes(2);
+        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
+        if (*configured < bytes) { if (set_smem(decode_attention_kernel<128, 2 * STAGES, false>, bytes, "attention_decode")) return -1; *configured = bytes; }
+        ti_launch(decode_attention_kernel<128, 2 * STAGES, false>, ctas, THREADS, bytes, stream, map, p);
+        TI_CHECK_LAUNCH("attention_decode");
+        ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
+    } else if (d == 128 && decode_form(group) == 1) {
+        const int bytes = Smem<128>::decode_bytes(group, STAGES, true);
+        int* configured = configured_bytes(3);
+        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
+        if (*configured < bytes) { if (set_smem(decode_attention_kernel<128, STAGES, true>, bytes, "attention_decode")) return -1; *configured = bytes; }
+        ti_launch(decode_attention_kernel<128, STAGES, true>, ctas, THREADS, bytes, stream, map, p);
+        TI_CHECK_LAUNCH("attention_decode");
+        ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
+    } else if (d == 128) {
         const int bytes = Smem<128>::decode_bytes(group);
         int* configured = configured_bytes(0);
         TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
-        if (*configured < bytes) { if (set_smem(decode_attention_kernel<128>, bytes, "attention_decode")) return -1; *configured = bytes; }
-        ti_launch(decode_attention_kernel<128>, ctas, THREADS, bytes, stream, map, p);
+        if (*configured < bytes) { if (set_smem(decode_attention_kernel<128, STAGES, false>, bytes, "attention_decode")) return -1; *configured = bytes; }
+        ti_launch(decode_attention_kernel<128, STAGES, false>, ctas, THREADS, bytes, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
         ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
     } else {
         const int bytes = Smem<64>::decode_bytes(group);
         int* configured = configured_bytes(1);
         TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
-        if (*configured < bytes) { if (set_smem(decode_attention_kernel<64>, bytes, "attention_decode")) return -1; *configured = bytes; }
-        ti_launch(decode_attention_kernel<64>, ctas, THREADS, bytes, stream, map, p);
+        if (*configured < bytes) { if (set_smem(decode_attention_kernel<64, STAGES, false>, bytes, "attention_decode")) return -1; *configured = bytes; }
+        ti_launch(decode_attention_kernel<64, STAGES, false>, ctas, THREADS, bytes, stream, map, p);
         TI_CHECK_LAUNCH("attention_decode");
         ti_launch(decode_merge_kernel<64>, dim3(num_rows, hq), 64, 0, stream, p);
     }
