@@ -213,6 +213,8 @@ def test_rmsnorm_shared_between_two_products(ops, m, k0, h, inter, eps):
 
 
 @pytest.mark.parametrize("m,inter,k", [(1, 12288, 4096), (8, 1000, 512), (20, 448, 320), (64, 100, 96), (65, 176, 96),
+                                       # few tiles and a long k: the k loops are cut, from 16 tokens on the units add up together
+                                       (32, 6144, 2048), (64, 1000, 1024), (17, 3000, 768), (8, 6144, 2048), (16, 1028, 4096),
                                        (300, 448, 320), (2048, 1024, 256), (130, 72, 40), (1500, 2500, 136), (3100, 1300, 72)])
 def test_gated_linear_tensor_cores(ops, one_cta_form, m, inter, k):
     dtype = torch.bfloat16

@@ -313,13 +313,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     break;
                 }
                 if (arrived != p.splits - 1) continue;
-                // Swapped, not gated (the products of a decode step): the four warps share the columns
-                // (tokens), a lane takes four consecutive rows (output features). So every load is 16
-                // bytes and a warp reads a whole column of a partial at once; the partials of several
-                // columns and of all splits are in flight together and are added in split order.
-                if (p.swap && !p.gated && (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0 &&
-                    ((uintptr_t)p.residual & 7) == 0 && ((uintptr_t)p.bias & 15) == 0) {
-                    const int n0 = r0 + 4 * lane;
+                // Swapped (the products of a decode step): the four warps share the columns (tokens), a
+                // lane takes four consecutive rows (output features). So every load is 16 bytes and a
+                // warp reads a whole column of a partial at once; the partials of several columns and
+                // of all splits are in flight together and are added in split order. Gated: lanes 0..15
+                // hold gate rows j.., lanes 16..31 the up rows of the same outputs, which reach the
+                // gate's lanes by a shuffle.
+                if (p.swap && (p.N & 3) == 0 &&
+                    (p.gated ? ((uintptr_t)p.out & 7) == 0
+                             : ((uintptr_t)p.out & 15) == 0 && ((uintptr_t)p.residual & 7) == 0 && ((uintptr_t)p.bias & 15) == 0)) {
+                    const int n0 = r0 + 4 * (p.gated ? (lane & 15) : lane);
                     const bool n_ok = n0 < p.N;                        // N is a multiple of 4: all four rows or none
                     float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), g4 = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (p.bias && n_ok) b4 = *reinterpret_cast<const float4*>(p.bias + n0);
@@ -365,6 +368,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                         acc[i].z += part[sp][i].z; acc[i].w += part[sp][i].w;
                                     }
                                 }
+                            }
+                            if (p.gated) {
+#pragma unroll
+                                for (int i = 0; i < G; ++i) {
+                                    const int col = g0 + 4 * i * col_step;              // the same for the whole warp
+                                    float4 up;
+                                    up.x = __shfl_xor_sync(0xffffffffu, acc[i].x, 16); up.y = __shfl_xor_sync(0xffffffffu, acc[i].y, 16);
+                                    up.z = __shfl_xor_sync(0xffffffffu, acc[i].z, 16); up.w = __shfl_xor_sync(0xffffffffu, acc[i].w, 16);
+                                    if (lane >= 16 || !n_ok || col >= cols_real) continue;
+                                    const float sc = row_scale_sh[col];                 // gate and up alike
+                                    __nv_bfloat162 lo2 = __floats2bfloat162_rn(silu_mul(acc[i].x * sc, up.x * sc), silu_mul(acc[i].y * sc, up.y * sc));
+                                    __nv_bfloat162 hi2 = __floats2bfloat162_rn(silu_mul(acc[i].z * sc, up.z * sc), silu_mul(acc[i].w * sc, up.w * sc));
+                                    uint2 o2;
+                                    o2.x = *reinterpret_cast<uint32_t*>(&lo2);
+                                    o2.y = *reinterpret_cast<uint32_t*>(&hi2);
+                                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)(c0 + col) * p.N + n0) = o2;
+                                }
+                                continue;
                             }
 #pragma unroll
                             for (int i = 0; i < G; ++i) {
@@ -857,8 +878,9 @@ static int gemm_entry(void* out, const void* x, const void* w, const float* bias
         // last unit alone makes a trip to L2 per few tokens, one after the other; up to 8 tokens that is
         // one trip and sharing only adds the wait: measured). Needs every unit running at once, and the
         // 16-byte path of the sum.
-        const bool may_share = M >= 16 && !gated && (N & 3) == 0 && ((uintptr_t)out & 15) == 0 &&
-                               ((uintptr_t)residual & 7) == 0 && ((uintptr_t)bias & 15) == 0;
+        const bool may_share = M >= 16 && (N & 3) == 0 &&
+                               (gated ? ((uintptr_t)out & 7) == 0
+                                      : ((uintptr_t)out & 15) == 0 && ((uintptr_t)residual & 7) == 0 && ((uintptr_t)bias & 15) == 0);
         if (workspace && counters)
             p.splits = choose_splits(tiles, (K + BK - 1) / BK, bn, workspace_floats, num_counters, may_share);
         if (may_share && p.splits > 1 && (long long)tiles * p.splits <= (long long)ti_sm_count() * (bn <= 64 ? 2 : 1))
