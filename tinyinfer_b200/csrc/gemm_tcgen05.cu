@@ -86,7 +86,8 @@ struct Cfg {
     static_assert(CTAS_PER_SM * (SMEM_BYTES + 1024) <= 227 * 1024, "the CTAs of an SM do not fit its shared memory");
 };
 
-template <int BN, int TM>
+// SWAP: weights on the lanes (a compile-time choice, so that a decode step's kernels carry none of the code for many tokens).
+template <int BN, int TM, bool SWAP>
 __global__ void __launch_bounds__(NUM_THREADS, Cfg<BN, TM>::CTAS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     const GemmParams p) {
@@ -110,8 +111,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     ti_grid_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // tiles: gated normal tiles hold BN/2 gate and BN/2 up columns; gated swapped tiles 64 + 64 rows
-    const int rows_per_tile = (p.gated && p.swap) ? BM / 2 : TM * BM;
-    const int cols_per_tile = (p.gated && !p.swap) ? BN / 2 : BN;
+    const int rows_per_tile = (p.gated && SWAP) ? BM / 2 : TM * BM;
+    const int cols_per_tile = (p.gated && !SWAP) ? BN / 2 : BN;
     const int row_tiles = (p.rows_total + rows_per_tile - 1) / rows_per_tile;
     const int col_tiles = (p.cols_total + cols_per_tile - 1) / cols_per_tile;
     const int num_tiles = row_tiles * col_tiles;
@@ -145,12 +146,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 const uint32_t b_dst = a_dst + TM * BM * BK * 2;      // tall tiles: one copy of 256 rows
                 if (rows_side) {
                     tma_load_2d(a_dst, &map_rows, full_bar(s), kb * BK, r0);
-                    if (p.gated && p.swap)            // 64 gate rows, then 64 up rows
+                    if (p.gated && SWAP)            // 64 gate rows, then 64 up rows
                         tma_load_2d(a_dst + (BM / 2) * BK * 2, &map_rows, full_bar(s), kb * BK, p.N + r0);
                 }
                 if (cols_side) {
                     tma_load_2d(b_dst, &map_cols, full_bar(s), kb * BK, c0);
-                    if (p.gated && !p.swap)           // BN/2 gate rows, then BN/2 up rows
+                    if (p.gated && !SWAP)           // BN/2 gate rows, then BN/2 up rows
                         tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_cols, full_bar(s), kb * BK, p.N + c0);
                 }
             };
@@ -164,7 +165,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             // Before waiting for the kernels ahead of this one in the stream: the weights do not
             // depend on them, so their copies for the first ring of stages start right away and
             // HBM stays busy while the previous kernel drains. The activations follow after the wait.
-            const bool weights_are_rows = p.swap != 0;
+            const bool weights_are_rows = SWAP;
             uint32_t pre = 0;
             for (int unit = blockIdx.x; unit < num_units && pre < (uint32_t)C::STAGES; unit += gridDim.x) {
                 int r0, c0, kb0, kb1;
@@ -242,7 +243,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         const int row_in_tile = lane_group * 32 + lane;
         uint32_t tile_i = 0;
         bool ok = true;
-        if (p.swap) {                                    // tokens are columns: at most BN <= 128 of them, one column tile
+        if (SWAP) {                                    // tokens are columns: at most BN <= 128 of them, one column tile
             float sc = 1.f;
             if (p.scale_sums != nullptr && row_in_tile < p.M) {
                 float ss = 0.f;
@@ -267,7 +268,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             // arrives last sums all partials of the tile in split order (so the result does not
             // depend on who was last) and runs the epilogue.
             float* tile_partials = nullptr;
-            if (p.splits > 1 && p.swap) {
+            if (p.splits > 1 && SWAP) {
                 tile_partials = p.partials + (size_t)tile * p.splits * BN * BM;
                 float* mine = tile_partials + (size_t)split * BN * BM + row_in_tile;
                 for (int c = 0; c < BN; c += 16) {
@@ -319,7 +320,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 // of all splits are in flight together and are added in split order. Gated: lanes 0..15
                 // hold gate rows j.., lanes 16..31 the up rows of the same outputs, which reach the
                 // gate's lanes by a shuffle.
-                if (p.swap && (p.N & 3) == 0 &&
+                if (SWAP && (p.N & 3) == 0 &&
                     (p.gated ? ((uintptr_t)p.out & 7) == 0
                              : ((uintptr_t)p.out & 15) == 0 && ((uintptr_t)p.residual & 7) == 0 && ((uintptr_t)p.bias & 15) == 0)) {
                     const int n0 = r0 + 4 * (p.gated ? (lane & 15) : lane);
@@ -456,7 +457,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     float acc[COLS];
 #pragma unroll
                     for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
-                    if (!p.swap || c0 + c + i0 < p.M) {
+                    if (!SWAP || c0 + c + i0 < p.M) {
                         for (int sp0 = 0; sp0 < p.splits; sp0 += SPLITS) {
                             float part[SPLITS][COLS];
 #pragma unroll
@@ -540,7 +541,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     }
                 }
             };
-            if (!p.swap && p.splits > 1) {
+            if (!SWAP && p.splits > 1) {
                 // Tokens on the lanes with a cut k loop (few tiles, many tokens): every unit of a tile
                 // leaves its partial accumulator in scratch, waits until the other units of the tile have
                 // done so (they all run at once: the host launches one CTA per unit and no more units than
@@ -615,7 +616,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 }
                 continue;
             }
-            if (!p.swap) {
+            if (!SWAP) {
               for (int hm = 0; hm < TM; ++hm) {                 // the tile's accumulators of 128 rows, one after the other
                 const uint32_t t_addr = t_addr0 + hm * BN;
                 const int m = r0 + hm * BM + row_in_tile;
@@ -759,19 +760,19 @@ int choose_splits(int tiles, int num_kb, int bn, long long workspace_floats, int
     return best;
 }
 
-template <int BN, int TM = 1>
+template <int BN, int TM = 1, bool SWAP = false>
 int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmParams& p, int num_tiles, cudaStream_t stream) {
     using C = Cfg<BN, TM>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, TM, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) { ti_set_error("gemm_tcgen05: cannot get %d bytes of shared memory: %s", C::SMEM_BYTES, cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
     num_tiles *= p.splits;
     const int slots = ti_sm_count() * C::CTAS_PER_SM;
     const int grid = num_tiles < slots ? num_tiles : slots;
-    ti_launch(gemm_tcgen05_kernel<BN, TM>, grid, NUM_THREADS, C::SMEM_BYTES, stream, rows_map, cols_map, p);
+    ti_launch(gemm_tcgen05_kernel<BN, TM, SWAP>, grid, NUM_THREADS, C::SMEM_BYTES, stream, rows_map, cols_map, p);
     TI_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }
@@ -892,10 +893,10 @@ static int gemm_entry(void* out, const void* x, const void* w, const float* bias
             p.emit_g = link.emit_g; p.emit_xg = (__nv_bfloat16*)link.emit_xg; p.emit_sums = link.emit_sums;
             if (link.emitted_parts) *link.emitted_parts = tiles;
         }
-        if (bn == 16) return launch<16>(rows_map, cols_map, p, tiles, stream);
-        if (bn == 32) return launch<32>(rows_map, cols_map, p, tiles, stream);
-        if (bn == 64) return launch<64>(rows_map, cols_map, p, tiles, stream);
-        return launch<128>(rows_map, cols_map, p, tiles, stream);
+        if (bn == 16) return launch<16, 1, true>(rows_map, cols_map, p, tiles, stream);
+        if (bn == 32) return launch<32, 1, true>(rows_map, cols_map, p, tiles, stream);
+        if (bn == 64) return launch<64, 1, true>(rows_map, cols_map, p, tiles, stream);
+        return launch<128, 1, true>(rows_map, cols_map, p, tiles, stream);
     }
     p.swap = 0;
     p.rows_total = M; p.cols_total = N;
