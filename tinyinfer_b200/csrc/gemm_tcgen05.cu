@@ -432,9 +432,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                             }
                         }
                     };
-                    if (p.splits <= 4) wide(std::integral_constant<int, 4>{}, std::integral_constant<int, 4>{});
-                    else if (p.splits <= 8) wide(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{});
-                    else wide(std::integral_constant<int, 1>{}, std::integral_constant<int, 16>{});
+                    // two columns and eight splits a trip to L2, whatever the number of splits (one form: see the note on the kernel's length below)
+                    wide(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{});
                     if (p.share_sum) {
                         // second arrival: when every unit has read what it needs, the last one clears the counter
                         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -445,11 +444,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     continue;
                 }
             }
-            // The last arriver's sum: the partials of a group of columns and of all splits (16 at a time)
-            // are requested together, 64 independent loads, then added in split order: one trip to L2
-            // per group instead of one per split; the order of the additions, and so the result, is the
-            // same. The fewer the splits, the more columns share a trip. Swapped tiles skip the columns
-            // beyond the last token: nothing of them is stored.
+            // The last arriver's sum on the path of odd sizes (the 16-byte path above takes the sizes of real
+            // models): the partials of 16 columns and of two splits are requested together, 32 independent
+            // loads, then added in split order. Kept short on purpose: with three forms of it (64 loads each, by
+            // number of splits) the kernel for 16 tokens was 143 KB of code and every decode product paid for
+            // fetching it (8 x 6144 x 4096: 11.4 -> 10.5 us with 75 KB). Swapped tiles skip the columns beyond
+            // the last token: nothing of them is stored.
             auto sum_group = [&](int c, float* dst, auto cols_tag, auto splits_tag) {
                 constexpr int COLS = decltype(cols_tag)::value, SPLITS = decltype(splits_tag)::value;
 #pragma unroll
@@ -479,10 +479,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 }
             };
             auto load_chunk = [&](int c, float* dst) {
-                if (p.splits > 1) {
-                    if (p.splits <= 4) sum_group(c, dst, std::integral_constant<int, 16>{}, std::integral_constant<int, 4>{});
-                    else if (p.splits <= 8) sum_group(c, dst, std::integral_constant<int, 8>{}, std::integral_constant<int, 8>{});
-                    else sum_group(c, dst, std::integral_constant<int, 4>{}, std::integral_constant<int, 16>{});
+                if (p.splits > 1) {       // (one form for every number of splits: this is the path of odd sizes, and the kernel's code is long as it is)
+                    sum_group(c, dst, std::integral_constant<int, 16>{}, std::integral_constant<int, 2>{});
                 } else {
                     tmem_ld16(t_addr + c, dst);
                 }
