@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
 // The pairs that several CTAs share: one block per (decode row, query head), one thread per feature, merges
 // the pair's parts in key order (a pair that lay inside one run was finished there: its blocks leave at
 // once). The block works out which CTAs' runs hold the pair the way the split kernel does, before it waits
-// for that kernel. The partials of sixteen parts are requested together and folded into a running maximum,
+// for that kernel. The partials of eight parts are requested together and folded into a running maximum,
 // sum and output. (Merging inside the split kernel, by the CTA that counts itself in last, was slower by
 // 3 to 5 us at 1 to 8 long requests: while the kernel streams, the release that publishes a CTA's
 // partials waits microseconds for its stores.)
@@ -533,10 +533,10 @@ __global__ void decode_merge_kernel(const AttnParams p) {
     const int pair = r * p.hkv + kvh;
     ti_grid_wait();
     float m_run = -INFINITY, acc = 0.f, l_all = 0.f;
-    for (int cb = c0; cb <= c1; cb += 16) {
-        float ms[16], ls[16], os[16];
+    for (int cb = c0; cb <= c1; cb += 8) {
+        float ms[8], ls[8], os[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < 8; ++j) {
             const bool in = cb + j <= c1;
             const size_t slot = (size_t)(cb + j + pair) * group + hrow;
             const float2 ml = in ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + slot * 2)) : make_float2(-INFINITY, 0.f);
@@ -546,13 +546,13 @@ __global__ void decode_merge_kernel(const AttnParams p) {
         }
         float m_new = m_run;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) m_new = fmaxf(m_new, ms[j]);
+        for (int j = 0; j < 8; ++j) m_new = fmaxf(m_new, ms[j]);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
         const float keep = exp2f(m_run - m_use);          // 0 while nothing has been merged yet
         acc *= keep;
         l_all *= keep;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < 8; ++j) {
             const float f = exp2f(ms[j] - m_use);          // 0 for a part that is not there
             acc += f * os[j];
             l_all += f * ls[j];
