@@ -114,7 +114,9 @@ TC_SHAPES = [(1, 4096, 4096), (8, 6144, 4096), (16, 1000, 512), (17, 520, 264), 
              # with ragged edges in every direction
              (100, 4096, 4096), (128, 1000, 2048), (1500, 5000, 136), (3100, 2600, 72),
              # 16 tokens and more: the units of a cut k loop add up together (9 and 12 cuts)
-             (16, 4096, 4096), (48, 2048, 12288), (64, 4096, 4096)]
+             (16, 4096, 4096), (48, 2048, 12288), (64, 4096, 4096),
+             # 149 to 295 tiles of 128 outputs: more than half the CTA slots, fewer than all
+             (8, 25600, 1024), (40, 30000, 520), (1, 19200, 4096)]
 
 
 @pytest.fixture
@@ -215,6 +217,8 @@ def test_rmsnorm_shared_between_two_products(ops, m, k0, h, inter, eps):
 @pytest.mark.parametrize("m,inter,k", [(1, 12288, 4096), (8, 1000, 512), (20, 448, 320), (64, 100, 96), (65, 176, 96),
                                        # few tiles and a long k: the k loops are cut, from 16 tokens on the units add up together
                                        (32, 6144, 2048), (64, 1000, 1024), (17, 3000, 768), (8, 6144, 2048), (16, 1028, 4096),
+                                       # more tiles (of 64 outputs) than half the CTA slots and fewer than all: not cut
+                                       (8, 12288, 4096), (1, 12288, 1024), (64, 12288, 512), (33, 9700, 2056), (16, 18000, 640),
                                        (300, 448, 320), (2048, 1024, 256), (130, 72, 40), (1500, 2500, 136), (3100, 1300, 72)])
 def test_gated_linear_tensor_cores(ops, one_cta_form, m, inter, k):
     dtype = torch.bfloat16

@@ -118,6 +118,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     const int num_tiles = row_tiles * col_tiles;
     const int num_kb = (p.K + BK - 1) / BK;
     const int num_units = num_tiles * p.splits;     // unit = tile * splits + split: a tile's splits run side by side
+    // A CTA's i-th piece of work: k blocks kb0 .. kb1 of a tile, as part `split` of `nsplits` parts of the tile.
+    // (32-bit arithmetic: splits x k blocks of a tile stays far below 2^31; with 64-bit divisions here the loading
+    // thread, whose work per unit is on a decode step's critical path, made the step 1 % slower.)
+    struct Work { int tile, split, nsplits, kb0, kb1; };
+    auto work_at = [&](int i, Work& w) -> bool {
+        const int unit = (int)blockIdx.x + i * (int)gridDim.x;
+        if (unit >= num_units) return false;
+        w.tile = unit / p.splits; w.split = unit % p.splits; w.nsplits = p.splits;
+        w.kb0 = w.split * num_kb / p.splits;
+        w.kb1 = (w.split + 1) * num_kb / p.splits;
+        return true;
+    };
 
     if (threadIdx.x == 0) {
         abort_sh = 0;
@@ -155,21 +167,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                         tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_cols, full_bar(s), kb * BK, p.N + c0);
                 }
             };
-            auto unit_range = [&](int unit, int& r0, int& c0, int& kb0, int& kb1) {
-                const int tile = unit / p.splits, split = unit % p.splits;
-                r0 = (tile % row_tiles) * rows_per_tile;
-                c0 = (tile / row_tiles) * cols_per_tile;
-                kb0 = (int)((long long)split * num_kb / p.splits);
-                kb1 = (int)((long long)(split + 1) * num_kb / p.splits);
+            auto unit_range = [&](int i, int& r0, int& c0, int& kb0, int& kb1) -> bool {
+                Work w;
+                if (!work_at(i, w)) return false;
+                r0 = (w.tile % row_tiles) * rows_per_tile;
+                c0 = (w.tile / row_tiles) * cols_per_tile;
+                kb0 = w.kb0; kb1 = w.kb1;
+                return true;
             };
             // Before waiting for the kernels ahead of this one in the stream: the weights do not
             // depend on them, so their copies for the first ring of stages start right away and
             // HBM stays busy while the previous kernel drains. The activations follow after the wait.
             const bool weights_are_rows = SWAP;
             uint32_t pre = 0;
-            for (int unit = blockIdx.x; unit < num_units && pre < (uint32_t)C::STAGES; unit += gridDim.x) {
+            for (int i = 0; pre < (uint32_t)C::STAGES; ++i) {
                 int r0, c0, kb0, kb1;
-                unit_range(unit, r0, c0, kb0, kb1);
+                if (!unit_range(i, r0, c0, kb0, kb1)) break;
                 for (int kb = kb0; kb < kb1 && pre < (uint32_t)C::STAGES; ++kb, ++pre) {
                     mbar_expect_tx(full_bar(pre), C::STAGE_BYTES);
                     issue(r0, c0, kb, pre, weights_are_rows, !weights_are_rows);
@@ -178,9 +191,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             ti_grid_wait();
             uint32_t it = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+            for (int i = 0; ok; ++i) {
                 int r0, c0, kb0, kb1;
-                unit_range(unit, r0, c0, kb0, kb1);
+                if (!unit_range(i, r0, c0, kb0, kb1)) break;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % C::STAGES;
                     if (it < pre) {                   // its weights are already on their way
@@ -206,10 +219,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             constexpr uint32_t idesc = make_idesc(BM, BN);
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++tile_i) {
-                const int split = unit % p.splits;
-                const int kb0 = (int)((long long)split * num_kb / p.splits);
-                const int kb1 = (int)((long long)(split + 1) * num_kb / p.splits);
+            Work wk;
+            for (; ok && work_at((int)tile_i, wk); ++tile_i) {
+                const int kb0 = wk.kb0, kb1 = wk.kb1;
                 // tall tiles own all of tensor memory: one accumulator buffer, a phase per tile
                 const uint32_t as = TM == 2 ? 0u : (tile_i & 1u), aph = TM == 2 ? (tile_i & 1u) : ((tile_i >> 1) & 1u);
                 if (!mbar_wait(acc_empty_bar(as), aph ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
@@ -253,8 +265,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             row_scale_sh[row_in_tile] = sc;
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-        for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++tile_i) {
-            const int tile = unit / p.splits, split = unit % p.splits;
+        Work wk;
+        for (; ok && work_at((int)tile_i, wk); ++tile_i) {
+            const int tile = wk.tile, split = wk.split, nsplits = wk.nsplits;
             const int rt = tile % row_tiles, ct = tile / row_tiles;
             const int r0 = rt * rows_per_tile, c0 = ct * cols_per_tile;
             const uint32_t as = TM == 2 ? 0u : (tile_i & 1u), aph = TM == 2 ? (tile_i & 1u) : ((tile_i >> 1) & 1u);
@@ -268,8 +281,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             // arrives last sums all partials of the tile in split order (so the result does not
             // depend on who was last) and runs the epilogue.
             float* tile_partials = nullptr;
-            if (p.splits > 1 && SWAP) {
-                tile_partials = p.partials + (size_t)tile * p.splits * BN * BM;
+            if (nsplits > 1 && SWAP) {
+                tile_partials = p.partials + (size_t)tile * nsplits * BN * BM;
                 float* mine = tile_partials + (size_t)split * BN * BM + row_in_tile;
                 for (int c = 0; c < BN; c += 16) {
                     tmem_ld16(t_addr + c, v);
@@ -292,13 +305,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     if (p.share_sum) {
                         // every unit of the tile takes a share of the sum: wait for the others (they all
                         // run at once: the host launches one CTA per unit, no more than fit the SMs)
-                        arrived = p.splits - 1;
+                        arrived = nsplits - 1;
                         const long long t_start = clock64();
-                        for (uint32_t spin = 1; *reinterpret_cast<volatile int*>(p.counters + tile) < p.splits; ++spin) {
+                        for (uint32_t spin = 1; *reinterpret_cast<volatile int*>(p.counters + tile) < nsplits; ++spin) {
                             __nanosleep(64);
                             if ((spin & 63u) == 0u && (*abort_flag || clock64() - t_start > 4000000000ll)) { arrived = -1; break; }
                         }
-                    } else if (arrived == p.splits - 1) {
+                    } else if (arrived == nsplits - 1) {
                         p.counters[tile] = 0;     // leave the counter ready for the next launch
                     }
                     if (p.share_sum) __threadfence();          // after the wait: the other units' partials may be read
@@ -313,7 +326,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     ok = false;
                     break;
                 }
-                if (arrived != p.splits - 1) continue;
+                if (arrived != nsplits - 1) continue;
                 // Swapped (the products of a decode step): the four warps share the columns (tokens), a
                 // lane takes four consecutive rows (output features). So every load is 16 bytes and a
                 // warp reads a whole column of a partial at once; the partials of several columns and
@@ -331,7 +344,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     const int cols_real = min(BN, p.M - c0);
                     // the tokens this unit finishes: all of them, or with a shared sum those with
                     // token mod splits == split
-                    const int col_first = p.share_sum ? split : 0, col_step = p.share_sum ? p.splits : 1;
+                    const int col_first = p.share_sum ? split : 0, col_step = p.share_sum ? nsplits : 1;
                     auto wide = [&](auto cols_tag, auto splits_tag) {
                         constexpr int G = decltype(cols_tag)::value, SP = decltype(splits_tag)::value;
                         for (int g0 = col_first + lane_group * col_step; g0 < cols_real; g0 += 4 * G * col_step) {
@@ -348,14 +361,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                 if (p.residual && n_ok && col < cols_real)
                                     res[i] = *reinterpret_cast<const uint2*>(p.residual + (size_t)(c0 + col) * p.N + n0);
                             }
-                            for (int sp0 = 0; sp0 < p.splits; sp0 += SP) {
+                            for (int sp0 = 0; sp0 < nsplits; sp0 += SP) {
                                 float4 part[SP][G];
 #pragma unroll
                                 for (int sp = 0; sp < SP; ++sp) {
 #pragma unroll
                                     for (int i = 0; i < G; ++i) {
                                         const int col = g0 + 4 * i * col_step;
-                                        const bool in = sp0 + sp < p.splits && col < cols_real;
+                                        const bool in = sp0 + sp < nsplits && col < cols_real;
                                         part[sp][i] = in ? __ldcg(reinterpret_cast<const float4*>(
                                                                tile_partials + ((size_t)(sp0 + sp) * BN + col) * BM + 4 * lane))
                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -438,7 +451,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                         // second arrival: when every unit has read what it needs, the last one clears the counter
                         asm volatile("bar.sync 1, 128;" ::: "memory");
                         if (threadIdx.x == 64) {
-                            if (atomicAdd(p.counters + tile, 1) == 2 * p.splits - 1) p.counters[tile] = 0;
+                            if (atomicAdd(p.counters + tile, 1) == 2 * nsplits - 1) p.counters[tile] = 0;
                         }
                     }
                     continue;
@@ -458,11 +471,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 #pragma unroll
                     for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
                     if (!SWAP || c0 + c + i0 < p.M) {
-                        for (int sp0 = 0; sp0 < p.splits; sp0 += SPLITS) {
+                        for (int sp0 = 0; sp0 < nsplits; sp0 += SPLITS) {
                             float part[SPLITS][COLS];
 #pragma unroll
                             for (int sp = 0; sp < SPLITS; ++sp) {
-                                const bool in = sp0 + sp < p.splits;
+                                const bool in = sp0 + sp < nsplits;
                                 const float* src = tile_partials + (size_t)(in ? sp0 + sp : 0) * BN * BM + row_in_tile;
 #pragma unroll
                                 for (int i = 0; i < COLS; ++i) part[sp][i] = in ? __ldcg(src + (size_t)(c + i0 + i) * BM) : 0.f;
@@ -479,7 +492,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 }
             };
             auto load_chunk = [&](int c, float* dst) {
-                if (p.splits > 1) {       // (one form for every number of splits: this is the path of odd sizes, and the kernel's code is long as it is)
+                if (nsplits > 1) {       // (one form for every number of splits: this is the path of odd sizes, and the kernel's code is long as it is)
                     sum_group(c, dst, std::integral_constant<int, 16>{}, std::integral_constant<int, 2>{});
                 } else {
                     tmem_ld16(t_addr + c, dst);
