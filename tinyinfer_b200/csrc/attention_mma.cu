@@ -140,10 +140,17 @@ __device__ __forceinline__ RowTiles row_tiles(const AttnParams& p, int r) {
     t.n = (t.ctx + TK - 1) / TK - t.lo_tile;
     return t;
 }
-// Tiles per run for `total` tiles (all kv heads) on `ctas` CTAs.
-__device__ __forceinline__ int run_tiles(long long total, int ctas) {
-    const long long per = (total + ctas - 1) / ctas;
-    return (int)(per < MIN_RUN_TILES ? MIN_RUN_TILES : per);
+// Tiles per run for `total` tiles (all kv heads) on `ctas` CTAs. (The tiles of a step are counted in 32 bits: a
+// step with 2^31 of them, 137 G keys, is refused with a status word. Divisions of 64-bit counts in every part's
+// walk were a measurable share of a short kernel.)
+__device__ __forceinline__ int run_tiles(int total, int ctas) {
+    const int per = (int)(((unsigned)total + (unsigned)ctas - 1u) / (unsigned)ctas);
+    return per < MIN_RUN_TILES ? MIN_RUN_TILES : per;
+}
+// All tiles of the step for all kv heads, or -1 if they cannot be counted in 32 bits.
+__device__ __forceinline__ int all_tiles_of(int per_head, int hkv) {
+    const long long all = (long long)per_head * hkv;
+    return all < (1ll << 31) - 65536 ? (int)all : -1;
 }
 // Sum over the block of `mine` (all of it) and over the threads before this one. NT threads, all call it.
 template <int NT>
@@ -169,18 +176,18 @@ __device__ __forceinline__ void block_scan(int mine, int* warp_sums /* [NT / 32]
 // A CTA's walk over the parts of its run: the loading warp and the consumers step through the same parts.
 struct Part { int r, row, kvh, tile0, tile1, tile_new, k_begin, k_end, slot, pair, cta0, cta1; };   // tile_new: the tile of the row's own token; cta0..cta1: the CTAs whose runs hold the pair's tiles
 struct RunWalk {
-    long long cur, end, base;      // global tile indices; base: that of (row r, kv head 0, its first tile)
+    int cur, end, base;            // global tile indices; base: that of (row r, kv head 0, its first tile)
     int r, per;
     RowTiles rt;
     __device__ __forceinline__ bool next(const AttnParams& p, Part& part) {
         if (cur >= end) return false;
-        while (cur - base >= (long long)p.hkv * rt.n) {        // on to the next decoded row
-            base += (long long)p.hkv * rt.n;
+        while (cur - base >= p.hkv * rt.n) {                   // on to the next decoded row
+            base += p.hkv * rt.n;
             rt = row_tiles(p, ++r);
         }
-        const int off = (int)(cur - base);
+        const int off = cur - base;
         const int kvh = off / rt.n, tl = off % rt.n;
-        const int cnt = (int)min((long long)(rt.n - tl), end - cur);
+        const int cnt = min(rt.n - tl, end - cur);
         part.r = r; part.row = rt.row; part.kvh = kvh;
         part.tile0 = rt.lo_tile + tl; part.tile1 = part.tile0 + cnt;
         part.tile_new = (rt.ctx - 1) / TK;
@@ -188,9 +195,9 @@ struct RunWalk {
         part.k_end = min(rt.ctx, part.tile1 * TK);
         part.pair = r * p.hkv + kvh;
         part.slot = (int)blockIdx.x + part.pair;               // CTA and pair both only grow along the walk: no two parts share a slot
-        const long long first = base + (long long)kvh * rt.n;  // the pair's first tile
-        part.cta0 = (int)(first / per);
-        part.cta1 = (int)((first + rt.n - 1) / per);
+        const int first = base + kvh * rt.n;                   // the pair's first tile
+        part.cta0 = first / per;
+        part.cta1 = (first + rt.n - 1) / per;
         cur += cnt;
         return true;
     }
@@ -241,14 +248,20 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
     for (int r = my_r0; r < my_r1; ++r) mine += row_tiles(p, r).n;
     int before, total;
     block_scan<THREADS>(mine, warp_sums, before, total);
-    const long long all_tiles = (long long)total * p.hkv;
+    const int all_tiles = all_tiles_of(total, p.hkv);
+    if (all_tiles < 0) {                                   // more tiles than 32 bits count: refused, loudly
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, 23);
+        return;
+    }
     const int per = run_tiles(all_tiles, p.num_ctas);
-    const long long run_begin = (long long)blockIdx.x * per, run_end = min(all_tiles, run_begin + per);
-    if (run_begin < all_tiles && run_begin >= (long long)before * p.hkv && run_begin < (long long)(before + mine) * p.hkv) {
+    const long long run_begin_ll = (long long)blockIdx.x * per;
+    const int run_begin = run_begin_ll < all_tiles ? (int)run_begin_ll : all_tiles;
+    const int run_end = min(all_tiles, run_begin + per);
+    if (run_begin < all_tiles && run_begin >= before * p.hkv && run_begin < (before + mine) * p.hkv) {
         int acc = before;
         for (int r = my_r0; r < my_r1; ++r) {
             const int n = row_tiles(p, r).n;
-            if (run_begin < (long long)(acc + n) * p.hkv) { start_sh[0] = r; start_sh[1] = acc; break; }
+            if (run_begin < (acc + n) * p.hkv) { start_sh[0] = r; start_sh[1] = acc; break; }
             acc += n;
         }
     }
@@ -256,7 +269,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
     if (run_begin >= all_tiles) return;                    // more CTAs than runs
     RunWalk walk;
     walk.cur = run_begin; walk.end = run_end; walk.r = start_sh[0]; walk.per = per;
-    walk.base = (long long)start_sh[1] * p.hkv;
+    walk.base = start_sh[1] * p.hkv;
     walk.rt = row_tiles(p, walk.r);
 
     if (warp == 4) {
@@ -526,9 +539,11 @@ __global__ void decode_merge_kernel(const AttnParams p) {
     block_scan<D>(mine_before, warp_sums, skip, tiles_before);
     const RowTiles rt = row_tiles(p, r);
     const int group = p.hq / p.hkv, kvh = h / group, hrow = h % group;
-    const int per = run_tiles((long long)total * p.hkv, p.num_ctas);
-    const long long first = (long long)tiles_before * p.hkv + (long long)kvh * rt.n;      // the pair's tiles, globally
-    const int c0 = (int)(first / per), c1 = (int)((first + rt.n - 1) / per);
+    const int all_tiles = all_tiles_of(total, p.hkv);
+    if (all_tiles < 0) return;                             // the split kernel has said so
+    const int per = run_tiles(all_tiles, p.num_ctas);
+    const int first = tiles_before * p.hkv + kvh * rt.n;                                   // the pair's tiles, globally
+    const int c0 = first / per, c1 = (first + rt.n - 1) / per;
     if (c0 == c1) return;
     const int pair = r * p.hkv + kvh;
     ti_grid_wait();

@@ -106,7 +106,10 @@ def page_status(device) -> torch.Tensor:
 def status_message(wait_code: int, page_code: int) -> Optional[str]:
     """What two status words say, or None if both are zero."""
     said = []
-    if wait_code:
+    if wait_code == 23:
+        said.append("a decode step has more key tiles than its attention kernel counts (2^31: about 137 G keys); "
+                    "the step's results are not to be used")
+    elif wait_code:
         said.append(f"a kernel gave up waiting on a barrier (status {wait_code}); the step's results are not to be used")
     if page_code:
         said.append(f"a kernel met a token or key without a page (status {page_code})")
