@@ -131,10 +131,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         return true;
     };
 
-    if (threadIdx.x == 0) {
-        abort_sh = 0;
-        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 4); }
+    // a thread a barrier (up to 28 of them: one thread alone spent a third of a microsecond of every launch here)
+    if (threadIdx.x == 0) abort_sh = 0;
+    if (threadIdx.x < 2 * C::STAGES + 4) {
+        const int b = threadIdx.x;                       // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+        mbar_init(bar0 + 8u * b, b >= 2 * C::STAGES + 2 ? 4 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
