@@ -139,6 +139,13 @@ __global__ void __launch_bounds__(RA_WARPS * 32) qk_norm_rope_append_vec_kernel(
     }
     __syncthreads();
     if (head0 >= heads_total) return;
+    // The page of the token's keys and values, for a warp that has a key or value head: block tables and
+    // token_seq are inputs of the step like the positions, so the two dependent loads happen before the wait.
+    int page = -2;
+    if (k_cache != nullptr && head0 + HPW > hq) {
+        const int logical = pos / page_size;
+        page = logical < max_blocks ? block_table[(size_t)token_seq[t] * max_blocks + logical] : -1;
+    }
     ti_grid_wait();
     // all of the warp's loads first: with many tokens the kernel lives on the bytes it has in flight
     Pack in[HPW];
@@ -149,7 +156,6 @@ __global__ void __launch_bounds__(RA_WARPS * 32) qk_norm_rope_append_vec_kernel(
         live[hh] = head < heads_total && (head < hq || k_cache != nullptr);
         if (live[hh]) in[hh] = *reinterpret_cast<const Pack*>(qkv + ((size_t)t * heads_total + head) * D + lane * VEC);
     }
-    int page = -2;                                                  // looked up when the first key or value head comes
 #pragma unroll
     for (int hh = 0; hh < HPW; ++hh) {
         if (!live[hh]) continue;
@@ -191,10 +197,6 @@ __global__ void __launch_bounds__(RA_WARPS * 32) qk_norm_rope_append_vec_kernel(
         if (is_q) {
             dst = q_out + ((size_t)t * hq + head) * D;
         } else {
-            if (page == -2) {
-                const int logical = pos / page_size;
-                page = logical < max_blocks ? block_table[(size_t)token_seq[t] * max_blocks + logical] : -1;
-            }
             if (page < 0 || page >= num_pages) {
                 if (lane == 0 && status) atomicExch(status, 1);
                 return;
