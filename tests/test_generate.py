@@ -241,7 +241,7 @@ def test_a_kernel_status_that_is_set_stops_generation(tmp_path, monkeypatch):
     folder = helpers.make_model_folder(tmp_path / "m", helpers.TINY_A, seed=3)
     words = ops.status_words(torch.device("cpu"))
     for overlap in (False, True):
-        for word, code, text in ((0, 15, "gave up waiting"), (1, 1, "without a page")):
+        for word, code, text in ((0, 15, "gave up waiting"), (1, 1, "without a page"), (0, 23, "more key tiles")):
             llm = llm_mod.LLM(folder, dtype="float32", device="cpu", max_num_batched_tokens=24, max_num_seqs=3,
                               kvcache_block_size=4, num_kvcache_blocks=30, max_model_len=128, overlap_steps=overlap)
             llm.add_request([5, 6, 7], SamplingParams(greedy=True, max_tokens=6))
