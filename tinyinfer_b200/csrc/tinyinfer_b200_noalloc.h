@@ -10,7 +10,7 @@
  * that loads it, held until exit), so
  *     ti_attention_decode_scratch_floats(num_rows, hq, hkv, d, max_context, window)
  *         <=  ti_attention_decode_noalloc_capacity()
- * must hold (about (2 * SMs + num_rows * hkv) * (hq / hkv) * (d + 2) floats: 467 requests with
+ * must hold (about (1.75 * SMs + num_rows * hkv) * (hq / hkv) * (d + 2) floats: 471 requests with
  * Qwen3-8B's 32 query and 8 kv heads of size 128); larger calls are refused with a message (return value
  * != 0, text from ti_last_error()).
  * The first call on a device does set-up work that later calls do not: it resolves the array's device
